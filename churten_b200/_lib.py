@@ -1,0 +1,120 @@
+"""ctypes binding of libchurten_b200.so (the C ABI declared in include/churten_b200.h).
+
+The library is the product: there is no CPU or PyTorch fallback.  If it has not
+been built, importing this module raises with the command that builds it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libchurten_b200.so"
+PROBE_LIB_PATH = _PKG / "libchurten_b200_probe.so"
+
+OK = 0
+ERR_INVALID_ARGUMENT = 1
+ERR_WORKSPACE = 2
+ERR_CUDA = 3
+ERR_UNSUPPORTED = 4
+
+# name -> (restype, argtypes); mirrors include/churten_b200.h line for line.
+_P = c_void_p
+SIGNATURES = {
+    "cb200_version": (c_int, []),
+    "cb200_last_error": (c_char_p, []),
+    "cb200_workspace_bytes": (c_size_t, [c_int64]),
+    "cb200_adam_step": (
+        c_int,
+        # params grads exp_avgs exp_avg_sqs max_exp_avg_sqs state_steps
+        [_P, _P, _P, _P, _P, _P,
+         # lr beta1 beta2 eps weight_decay active_mask
+         _P, _P, _P, _P, _P, _P,
+         # n_rows row_len strides amsgrad maximize decoupled
+         c_int64, c_int64, _P, c_int, c_int, c_int,
+         # workspace workspace_bytes stream
+         _P, c_size_t, _P],
+    ),
+    "cb200_sgd_step": (
+        c_int,
+        # params grads momentum_buffers state_steps lr momentum dampening weight_decay
+        [_P, _P, _P, _P, _P, _P, _P, _P,
+         # active_mask nesterov_rows n_rows row_len strides nesterov maximize
+         _P, _P, c_int64, c_int64, _P, c_int, c_int,
+         _P, c_size_t, _P],
+    ),
+    "cb200_adagrad_step": (
+        c_int,
+        # params grads state_sums state_steps lr lr_decay weight_decay eps active_mask
+        [_P, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_int64, c_int64, _P, c_int, _P, c_size_t, _P],
+    ),
+    "cb200_set_launch_geometry": (c_int, [c_int, c_int, c_int]),
+    "cb200_launch_count": (c_int64, []),
+}
+
+PROBE_SIGNATURES = {
+    "cb200_probe_adam": (
+        c_int,
+        [c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int64,
+         c_float, c_float, c_float, c_float, c_float, c_float, _P],
+    ),
+    "cb200_probe_sgd": (
+        c_int,
+        [c_int, c_int, c_int, c_int, _P, _P, _P, c_int64,
+         c_float, c_float, c_float, c_float, c_float, _P],
+    ),
+    "cb200_probe_adagrad": (
+        c_int,
+        [c_int, c_int, _P, _P, _P, c_int64, c_float, c_float, c_float, c_float, c_float, _P],
+    ),
+    "cb200_probe_powf": (c_int, [_P, _P, _P, c_int64, _P]),
+}
+
+
+class LibraryMissing(ImportError):
+    pass
+
+
+def _open(path: Path, signatures: dict) -> ctypes.CDLL:
+    if not path.exists():
+        raise LibraryMissing(
+            f"{path.name} has not been built (looked in {path.parent}). Build it with "
+            "`python -m churten_b200.csrc.build`; there is no fallback implementation."
+        )
+    lib = ctypes.CDLL(str(path))
+    for name, (restype, argtypes) in signatures.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is missing
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+_lib: ctypes.CDLL | None = None
+_probe: ctypes.CDLL | None = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = _open(LIB_PATH, SIGNATURES)
+    return _lib
+
+
+def probe_lib() -> ctypes.CDLL:
+    global _probe
+    if _probe is None:
+        _probe = _open(PROBE_LIB_PATH, PROBE_SIGNATURES)
+    return _probe
+
+
+def last_error() -> str:
+    return lib().cb200_last_error().decode("utf-8", "replace")
+
+
+def check(status: int, op: str) -> None:
+    """Turn a non-zero status into the RuntimeError the reference's TORCH_CHECKs raise."""
+    if status != OK:
+        raise RuntimeError(f"{op}: {last_error()} (cb200 status {status})")

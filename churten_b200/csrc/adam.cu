@@ -1,0 +1,88 @@
+// cb200_adam_step: fused Adam / AdamW (+AMSGrad) over consolidated (N, T) buffers.
+// Behaviour follows adam_step_cuda / adam_step_kernel of the reference
+// (src/torchstrap/kernels/csrc/cuda/adam.cu:250-331, :70-205).
+#include "../../include/churten_b200.h"
+#include "contraction.h"
+#include "stream.cuh"
+
+namespace cb200 {
+namespace {
+
+struct AdamHyper {
+  const float* lr;
+  const float* beta1;
+  const float* beta2;
+  const float* eps;
+  const float* weight_decay;
+};
+
+// Buffer order: params, grads, exp_avgs, exp_avg_sqs, [max_exp_avg_sqs].
+template <bool AMSGRAD, bool ADAMW, int FUSE>
+struct AdamOp {
+  static constexpr int kBufs = AMSGRAD ? 5 : 4;
+  static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;  // grads are read-only
+  using Row = AdamRow;
+  using Hyper = AdamHyper;
+
+  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, float step) {
+    return adam_row(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
+  }
+  __device__ static __forceinline__ void apply(float (&x)[kBufs], const Row& c, int flags) {
+    float mx = 0.0f;
+    if constexpr (AMSGRAD) mx = x[4];
+    adam_elem<AMSGRAD, ADAMW, FUSE>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
+    if constexpr (AMSGRAD) x[4] = mx;
+  }
+};
+
+template <bool AMSGRAD, bool ADAMW>
+int adam_dispatch(const AdamHyper& hyper, float* state_steps, const uint8_t* mask,
+                  float* const* ptrs, const int64_t* strides, int64_t n_rows, int64_t row_len,
+                  int flags, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  using VecOp = AdamOp<AMSGRAD, ADAMW, kAdamFuseVec>;
+  using ElemOp = AdamOp<AMSGRAD, ADAMW, kAdamFuseElem>;
+  static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs",
+                                       "max_exp_avg_sqs"};
+  Bufs<VecOp::kBufs> bufs;
+  if (int rc = fill_bufs(&bufs, ptrs, strides, row_len, names)) return rc;
+  return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags,
+                                 workspace, workspace_bytes, stream);
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" int cb200_adam_step(float* params, const float* grads, float* exp_avgs,
+                               float* exp_avg_sqs, float* max_exp_avg_sqs, float* state_steps,
+                               const float* lr, const float* beta1, const float* beta2,
+                               const float* eps, const float* weight_decay,
+                               const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                               const int64_t* strides, int amsgrad, int maximize,
+                               int decoupled_weight_decay, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  using namespace cb200;
+  if (amsgrad && !max_exp_avg_sqs) {
+    return fail(CB200_ERR_INVALID_ARGUMENT, "amsgrad=True requires max_exp_avg_sqs");
+  }
+  if (n_rows > 0 && (!lr || !beta1 || !beta2 || !eps || !weight_decay)) {
+    return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
+  }
+  const AdamHyper hyper{lr, beta1, beta2, eps, weight_decay};
+  float* ptrs[5] = {params, const_cast<float*>(grads), exp_avgs, exp_avg_sqs, max_exp_avg_sqs};
+  const int flags = maximize ? 1 : 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (amsgrad) {
+    if (decoupled_weight_decay) {
+      return adam_dispatch<true, true>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
+                                       row_len, flags, workspace, workspace_bytes, s);
+    }
+    return adam_dispatch<true, false>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
+                                      row_len, flags, workspace, workspace_bytes, s);
+  }
+  if (decoupled_weight_decay) {
+    return adam_dispatch<false, true>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
+                                      row_len, flags, workspace, workspace_bytes, s);
+  }
+  return adam_dispatch<false, false>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
+                                     row_len, flags, workspace, workspace_bytes, s);
+}

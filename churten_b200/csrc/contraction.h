@@ -1,0 +1,41 @@
+// Which `a * b + c` sites of the update math are single fma instructions.
+//
+// PyTorch's CUDA fused optimizers are compiled with nvcc's default -fmad=true, so
+// the compiler decided, site by site, whether a product feeding a sum became one
+// fma.  Bit-exact agreement with `torch.optim.<Opt>(fused=True)` needs the same
+// decisions.  They are found empirically: `contraction_search.py` (this folder)
+// runs every combination of the masks in rowmath.cuh against torch._fused_adam_ /
+// _fused_adamw_ / _fused_sgd_ / _fused_adagrad_ on the GPU, separately for
+// torch's 128-bit vector path (numel % 4 == 0, 16-byte aligned) and its
+// element-wise path, and prints the masks that reproduce torch on every element.
+//
+// Values below: the result of that search against torch 2.11.0+cu128 on B200
+// (1 Mi elements per case; Adam 72 cases, SGD 108 + 18, Adagrad 144 per path).
+// The search left exactly one mask for Adam (3), SGD with a buffer (29: the
+// momentum blend is fma(1 - dampening, g, momentum * buf)) and SGD without (17).
+// For Adagrad it fixed the fp32 accumulator site (fused); the two fp64 sites
+// (weight decay, corrected learning rate) change the fp32 result only when a
+// double rounding falls on a tie, which no case hit: they are set to nvcc's
+// default, fused.  powf(beta, step) matched torch.pow for 1.8 M arguments.
+// *_VEC is used by the 128-bit streaming kernels, *_ELEM by the element-wise
+// kernels (ragged row length, misaligned or strided buffers), mirroring which of
+// its two paths torch itself takes for the same layout.
+#pragma once
+
+#include "rowmath.cuh"
+
+namespace cb200 {
+
+constexpr int kAdamFuseVec = kAdamFuseAll;
+constexpr int kAdamFuseElem = kAdamFuseAll;
+
+// SGD with a momentum buffer (torch depth 3) and without (depth 2).
+constexpr int kSgdFuseVecBuf = kSgdFuseWd | (2 << kSgdBlendShift) | kSgdFuseNesterov | kSgdFuseUpdate;
+constexpr int kSgdFuseElemBuf = kSgdFuseWd | (2 << kSgdBlendShift) | kSgdFuseNesterov | kSgdFuseUpdate;
+constexpr int kSgdFuseVecPlain = kSgdFuseWd | kSgdFuseUpdate;
+constexpr int kSgdFuseElemPlain = kSgdFuseWd | kSgdFuseUpdate;
+
+constexpr int kAdagradFuseVec = kAdagradFuseAll;
+constexpr int kAdagradFuseElem = kAdagradFuseAll;
+
+}  // namespace cb200

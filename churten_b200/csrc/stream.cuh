@@ -1,0 +1,490 @@
+// Shared machinery of the three fused steps: workspace layout, the per-step
+// prologue (step bump + active-row compaction + per-row scalar records), the
+// persistent streaming kernel (128-bit path) and the element-wise kernel
+// (ragged / strided path), and the host-side launcher.
+//
+// Design, B200-first (the reference maps one 512-thread block to each
+// (replica, 65536-element chunk) pair and lets blocks of frozen replicas exit,
+// src/torchstrap/kernels/csrc/cuda/consolidated.cuh:63-69, cuda/adam.cu:86-89):
+//
+//  * Launch 1, `prologue_kernel`, one 1024-thread block: for every replica row
+//    add the mask to its step counter, and for ACTIVE rows append the row index
+//    to a compacted list (order preserved, ballot + prefix sum) together with a
+//    32-byte record of that row's scalars (bias corrections, 1 - dampening, the
+//    fp64 corrected learning rate ...).  The number of active rows stays on the
+//    device; the host never waits for it.
+//  * Launch 2, `stream_kernel`, a persistent grid of (SM count x resident CTAs)
+//    blocks striding over the flat list of (active row, tile) work items.  Frozen
+//    rows generate no work items, so they move zero bytes and the active rows are
+//    spread evenly over all SMs whatever the mask looks like.  A tile is
+//    blockDim x UNROLL 16-byte vectors per buffer; every load of a tile is issued
+//    before the first dependent instruction so each thread keeps
+//    UNROLL x (number of buffers) 16-byte requests in flight.  Loads and stores
+//    carry the streaming (evict-first) hint when the working set exceeds L2.
+//  * Launch 2 is issued with programmatic dependent launch: its blocks become
+//    resident while the prologue runs and wait on `griddepcontrol.wait` before
+//    they read the workspace, which hides the second launch latency.
+//
+// No shared memory, no TMA and no tensor cores: the update has no reuse and no
+// contraction; it is bound by HBM bandwidth (12-36 bytes per element).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+
+#include "rowmath.cuh"
+
+namespace cb200 {
+
+// ---------------------------------------------------------------------------
+// Host-side state shared by the entry points (abi.cu owns the definitions).
+// ---------------------------------------------------------------------------
+struct LaunchGeometry {
+  int threads;      // block size of the streaming kernels
+  int unroll;       // 16-byte accesses per thread per buffer per tile; 0 = by size
+  int ctas_per_sm;  // persistent CTAs per SM; 0 = what the occupancy query says
+};
+LaunchGeometry geometry();
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t err, const char* what);
+void count_launches(int n);
+// SM count and L2 size of the current device (cached per device ordinal).
+int device_info(int* sm_count, size_t* l2_bytes);
+
+constexpr int kPrologueThreads = 1024;
+constexpr size_t kWsAlign = 256;
+constexpr int kMaxBufs = 5;
+
+// ---------------------------------------------------------------------------
+// Workspace: [header 256 B][row ids: n_rows x int32, padded to 256 B][records:
+// n_rows x 32 B].  Only the first n_active ids / records are meaningful.
+// ---------------------------------------------------------------------------
+struct WsHeader {
+  int32_t n_active;
+  int32_t n_rows;
+};
+
+inline size_t ws_ids_bytes(int64_t n_rows) {
+  const size_t raw = static_cast<size_t>(n_rows) * sizeof(int32_t);
+  return (raw + kWsAlign - 1) / kWsAlign * kWsAlign;
+}
+inline size_t ws_bytes(int64_t n_rows) {
+  if (n_rows < 0) n_rows = 0;
+  return kWsAlign + ws_ids_bytes(n_rows) + static_cast<size_t>(n_rows) * 32;
+}
+
+struct WsView {
+  WsHeader* header;
+  int32_t* ids;
+  void* rows;  // Op::Row[n_rows]
+};
+inline WsView ws_view(void* workspace, int64_t n_rows) {
+  char* base = static_cast<char*>(workspace);
+  WsView v;
+  v.header = reinterpret_cast<WsHeader*>(base);
+  v.ids = reinterpret_cast<int32_t*>(base + kWsAlign);
+  v.rows = base + kWsAlign + ws_ids_bytes(n_rows);
+  return v;
+}
+
+// ---------------------------------------------------------------------------
+// Buffer table passed by value to the kernels.
+// ---------------------------------------------------------------------------
+template <int NB>
+struct Bufs {
+  float* ptr[NB];
+  int64_t stride_r[NB];
+  int64_t stride_t[NB];
+};
+
+// ---------------------------------------------------------------------------
+// Device helpers.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <bool STREAM>
+__device__ __forceinline__ float4 load4(const float* p) {
+  if (STREAM) return __ldcs(reinterpret_cast<const float4*>(p));
+  return *reinterpret_cast<const float4*>(p);
+}
+template <bool STREAM>
+__device__ __forceinline__ void store4(float* p, const float4& v) {
+  if (STREAM) {
+    __stcs(reinterpret_cast<float4*>(p), v);
+  } else {
+    *reinterpret_cast<float4*>(p) = v;
+  }
+}
+template <bool STREAM>
+__device__ __forceinline__ float load1(const float* p) {
+  if (STREAM) return __ldcs(p);
+  return *p;
+}
+template <bool STREAM>
+__device__ __forceinline__ void store1(float* p, float v) {
+  if (STREAM) {
+    __stcs(p, v);
+  } else {
+    *p = v;
+  }
+}
+
+__device__ __forceinline__ float& lane(float4& v, int i) {
+  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// ---------------------------------------------------------------------------
+// Launch 1: the prologue.
+//
+// Op supplies:  struct Hyper (device pointers to the (n_rows,) vectors + flags),
+//               using Row, and
+//               __device__ static Row make_row(const Hyper&, int r, float step).
+// ---------------------------------------------------------------------------
+template <class Op>
+__global__ void __launch_bounds__(kPrologueThreads)
+prologue_kernel(typename Op::Hyper hyper, float* __restrict__ state_steps,
+                const uint8_t* __restrict__ active_mask, int n_rows, WsView ws) {
+  // Let the streaming grid become resident now; it blocks in pdl_wait() until
+  // this grid has finished and its writes are visible.
+  pdl_launch_dependents();
+
+  using Row = typename Op::Row;
+  Row* rows = static_cast<Row*>(ws.rows);
+
+  __shared__ int warp_count[kPrologueThreads / 32];
+  __shared__ int warp_offset[kPrologueThreads / 32];
+  __shared__ int chunk_total;
+
+  const int tid = threadIdx.x;
+  const int lane_id = tid & 31;
+  const int warp_id = tid >> 5;
+  int running = 0;
+
+  for (int base = 0; base < n_rows; base += kPrologueThreads) {
+    const int r = base + tid;
+    const bool active = (r < n_rows) && (active_mask[r] != 0);
+    const unsigned ballot = __ballot_sync(0xffffffffu, active);
+    if (lane_id == 0) warp_count[warp_id] = __popc(ballot);
+    __syncthreads();
+    if (warp_id == 0) {
+      const int mine = warp_count[lane_id];
+      int incl = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane_id >= d) incl += up;
+      }
+      warp_offset[lane_id] = incl - mine;
+      if (lane_id == 31) chunk_total = incl;
+    }
+    __syncthreads();
+    if (active) {
+      const int slot = running + warp_offset[warp_id] + __popc(ballot & ((1u << lane_id) - 1u));
+      // The reference bumps with `state_steps.add_(mask.to(float))`
+      // (cuda/adam.cu:277): an fp32 add of 1.0f.
+      const float step = __fadd_rn(state_steps[r], 1.0f);
+      state_steps[r] = step;
+      ws.ids[slot] = r;
+      rows[slot] = Op::make_row(hyper, r, step);
+    }
+    running += chunk_total;
+    __syncthreads();
+  }
+  if (tid == 0) {
+    ws.header->n_active = running;
+    ws.header->n_rows = n_rows;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Launch 2a: persistent 128-bit streaming kernel.
+//
+// Op supplies:  kBufs, kWriteMask (bit b set: buffer b is written back), Row,
+//               __device__ static void apply(float (&x)[kBufs], const Row&, int flags)
+//               for ONE element (x[b] = that element of buffer b).
+// Requires element stride 1, 16-byte aligned rows, row_len % 4 == 0.
+// ---------------------------------------------------------------------------
+template <class Op, int UNROLL, bool STREAM>
+__global__ void __launch_bounds__(512)
+stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
+              int flags) {
+  constexpr int NB = Op::kBufs;
+  using Row = typename Op::Row;
+
+  pdl_wait();
+
+  const int n_active = ws.header->n_active;
+  const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
+  const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * 4 * UNROLL;
+  const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * 4;
+  const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
+
+  for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    int64_t a, tile;
+    if (total <= 0x7fffffffLL) {
+      const uint32_t it = static_cast<uint32_t>(item);
+      const uint32_t tpr = static_cast<uint32_t>(tiles_per_row);
+      a = it / tpr;
+      tile = it - static_cast<uint32_t>(a) * tpr;
+    } else {
+      a = item / tiles_per_row;
+      tile = item - a * tiles_per_row;
+    }
+    const int64_t r = ws.ids[a];
+    const Row c = rows[a];
+    const int64_t e0 = tile * tile_elems + static_cast<int64_t>(threadIdx.x) * 4;
+
+    float* base[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) base[b] = bufs.ptr[b] + r * bufs.stride_r[b] + e0;
+
+    float4 x[UNROLL][NB];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (e0 + u * lane_elems < row_len) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) x[u][b] = load4<STREAM>(base[b] + u * lane_elems);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (e0 + u * lane_elems < row_len) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float e[NB];
+#pragma unroll
+          for (int b = 0; b < NB; ++b) e[b] = lane(x[u][b], k);
+          Op::apply(e, c, flags);
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            if ((Op::kWriteMask >> b) & 1) lane(x[u][b], k) = e[b];
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          if ((Op::kWriteMask >> b) & 1) store4<STREAM>(base[b] + u * lane_elems, x[u][b]);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Launch 2b: element-wise kernel for any strides, alignment and row length.
+// Same work-item scheme; a tile is blockDim x UNROLL elements.
+// ---------------------------------------------------------------------------
+template <class Op, int UNROLL, bool STREAM>
+__global__ void __launch_bounds__(512)
+element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
+               int flags) {
+  constexpr int NB = Op::kBufs;
+  using Row = typename Op::Row;
+
+  pdl_wait();
+
+  const int n_active = ws.header->n_active;
+  const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
+  const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * UNROLL;
+  const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
+
+  for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    const int64_t a = item / tiles_per_row;
+    const int64_t tile = item - a * tiles_per_row;
+    const int64_t r = ws.ids[a];
+    const Row c = rows[a];
+    const int64_t e0 = tile * tile_elems + threadIdx.x;
+
+    float x[UNROLL][NB];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x;
+      if (e < row_len) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          x[u][b] = load1<STREAM>(bufs.ptr[b] + r * bufs.stride_r[b] + e * bufs.stride_t[b]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x;
+      if (e < row_len) {
+        Op::apply(x[u], c, flags);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          if ((Op::kWriteMask >> b) & 1) {
+            store1<STREAM>(bufs.ptr[b] + r * bufs.stride_r[b] + e * bufs.stride_t[b], x[u][b]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host launcher.
+// ---------------------------------------------------------------------------
+struct StepShape {
+  int64_t n_rows;
+  int64_t row_len;
+  bool vector_ok;       // every buffer dense-in-row, 16-byte aligned, row_len % 4 == 0
+  size_t bytes_per_elem;  // algorithmic traffic per element (for the cache-policy choice)
+};
+
+template <int NB>
+inline bool vector_layout_ok(const Bufs<NB>& b, int64_t row_len) {
+  if (row_len % 4 != 0) return false;
+  for (int i = 0; i < NB; ++i) {
+    if (b.stride_t[i] != 1) return false;
+    if (b.stride_r[i] % 4 != 0) return false;
+    if (reinterpret_cast<uintptr_t>(b.ptr[i]) % 16 != 0) return false;
+  }
+  return true;
+}
+
+template <class Kernel, class... Args>
+inline cudaError_t launch_dependent(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+template <class Kernel>
+inline int resident_ctas(Kernel kernel, int threads) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+    (void)cudaGetLastError();
+    n = 1;
+  }
+  return n;
+}
+
+// Runs the two launches of one step.  VecOp / ElemOp are the same optimizer with
+// the fusion masks of torch's vector and element-wise paths.
+template <class VecOp, class ElemOp>
+inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
+                    const uint8_t* active_mask, const Bufs<VecOp::kBufs>& bufs, int64_t n_rows,
+                    int64_t row_len, int flags, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream) {
+  static_assert(VecOp::kBufs == ElemOp::kBufs, "same optimizer");
+  if (n_rows < 0 || row_len < 0) return fail(1, "n_rows and row_len must be >= 0");
+  if (n_rows > 0x7fffffffLL) return fail(1, "n_rows must fit in 31 bits");
+  if (n_rows == 0) return 0;
+  if (!state_steps || !active_mask) return fail(1, "state_steps and active_mask must not be NULL");
+  if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kWsAlign != 0) {
+    return fail(2, "workspace must be a 256-byte aligned device pointer");
+  }
+  if (workspace_bytes < ws_bytes(n_rows)) {
+    return fail(2, "workspace too small: need " + std::to_string(ws_bytes(n_rows)) + " bytes, got " +
+                       std::to_string(workspace_bytes));
+  }
+  int sm_count = 0;
+  size_t l2_bytes = 0;
+  if (int rc = device_info(&sm_count, &l2_bytes)) return rc;
+
+  const WsView ws = ws_view(workspace, n_rows);
+  const bool vec = vector_layout_ok(bufs, row_len);
+
+  // The row records are built with the fusion mask of the path that reads them.
+  if (vec) {
+    prologue_kernel<VecOp><<<1, kPrologueThreads, 0, stream>>>(hyper, state_steps, active_mask,
+                                                                static_cast<int>(n_rows), ws);
+  } else {
+    prologue_kernel<ElemOp><<<1, kPrologueThreads, 0, stream>>>(hyper, state_steps, active_mask,
+                                                                 static_cast<int>(n_rows), ws);
+  }
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return cuda_fail(err, "prologue launch");
+  count_launches(1);
+  // The reference returns after the bump when there is nothing to update
+  // (cuda/adam.cu:279-281).
+  if (row_len == 0) return 0;
+
+  const LaunchGeometry geo = geometry();
+  const int threads = geo.threads;
+  const int64_t per_thread = vec ? 4 : 1;
+  // Streaming hints once the step's traffic no longer fits in L2.
+  const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) * 4.0 *
+                           VecOp::kBufs;
+  const bool stream_hint = footprint > 0.75 * static_cast<double>(l2_bytes);
+
+  // Unroll: as deep as possible while every SM still gets several tiles.
+  int unroll = geo.unroll;
+  if (unroll == 0) {
+    unroll = 4;
+    while (unroll > 1) {
+      const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
+      const int64_t items = n_rows * ((row_len + tile - 1) / tile);
+      if (items >= static_cast<int64_t>(sm_count) * 8) break;
+      unroll >>= 1;
+    }
+  }
+  const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
+  const int64_t tiles_per_row = (row_len + tile - 1) / tile;
+  const double max_items = static_cast<double>(n_rows) * static_cast<double>(tiles_per_row);
+
+  auto go = [&](auto kernel) -> int {
+    int per_sm = geo.ctas_per_sm > 0 ? geo.ctas_per_sm : resident_ctas(kernel, threads);
+    double want = static_cast<double>(sm_count) * per_sm;
+    if (want > max_items) want = max_items;
+    if (want < 1) want = 1;
+    const unsigned grid = static_cast<unsigned>(want);
+    cudaError_t e = launch_dependent(kernel, dim3(grid), dim3(threads), stream, bufs, ws, row_len,
+                                     tiles_per_row, flags);
+    if (e != cudaSuccess) return cuda_fail(e, "step kernel launch");
+    count_launches(1);
+    return 0;
+  };
+
+#define CB200_PICK(KERNEL, OP)                                            \
+  do {                                                                    \
+    if (stream_hint) {                                                    \
+      if (unroll == 4) return go(KERNEL<OP, 4, true>);                    \
+      if (unroll == 2) return go(KERNEL<OP, 2, true>);                    \
+      return go(KERNEL<OP, 1, true>);                                     \
+    } else {                                                              \
+      if (unroll == 4) return go(KERNEL<OP, 4, false>);                   \
+      if (unroll == 2) return go(KERNEL<OP, 2, false>);                   \
+      return go(KERNEL<OP, 1, false>);                                    \
+    }                                                                     \
+  } while (0)
+
+  if (vec) {
+    CB200_PICK(stream_kernel, VecOp);
+  } else {
+    CB200_PICK(element_kernel, ElemOp);
+  }
+#undef CB200_PICK
+  return 0;
+}
+
+// Fills a buffer table from the C-ABI arguments.
+template <int NB>
+inline int fill_bufs(Bufs<NB>* out, float* const* ptrs, const int64_t* strides, int64_t row_len,
+                     const char* const* names) {
+  for (int i = 0; i < NB; ++i) {
+    if (!ptrs[i]) return fail(1, std::string(names[i]) + " must not be NULL");
+    out->ptr[i] = ptrs[i];
+    out->stride_r[i] = strides ? strides[2 * i] : row_len;
+    out->stride_t[i] = strides ? strides[2 * i + 1] : 1;
+  }
+  return 0;
+}
+
+}  // namespace cb200

@@ -1,0 +1,274 @@
+"""`torchstrap::{adam,sgd,adagrad}_step_` on the CUDA dispatch key, backed by libchurten_b200.so.
+
+This module stands where the reference's compiled extension `torchstrap.kernels._C`
+stands (src/torchstrap/kernels/csrc/stubs.cpp:19-85 plus the `*_step_cuda` host
+wrappers, cuda/adam.cu:250-331, cuda/sgd.cu:295-359, cuda/adagrad.cu:238-283):
+importing it makes the three operators exist and claims their CUDA key.  The
+schemas are the reference's, verbatim.  If a library that already defines the
+`torchstrap` operators is loaded first (the reference's own extension), only the
+CUDA kernels are attached to the existing operators.
+
+No CPU kernel is registered here: a CPU tensor reaches the dispatcher's
+"no kernel for this backend" NotImplementedError, as in a reference build
+without its CPU sources.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from churten_b200 import _lib
+
+SCHEMAS = {
+    "adam_step_": (
+        "(Tensor(a!) params, Tensor grads, Tensor(b!) exp_avgs, Tensor(c!) exp_avg_sqs, "
+        "Tensor(d!)? max_exp_avg_sqs, Tensor(e!) state_steps, Tensor lr, Tensor beta1, "
+        "Tensor beta2, Tensor eps, Tensor weight_decay, Tensor active_mask, bool amsgrad, "
+        "bool maximize, bool decoupled_weight_decay) -> Tensor"
+    ),
+    "sgd_step_": (
+        "(Tensor(a!) params, Tensor grads, Tensor(b!)? momentum_buffers, Tensor(c!) state_steps, "
+        "Tensor lr, Tensor momentum, Tensor dampening, Tensor weight_decay, Tensor active_mask, "
+        "bool nesterov, bool maximize) -> Tensor"
+    ),
+    "adagrad_step_": (
+        "(Tensor(a!) params, Tensor grads, Tensor(b!) state_sums, Tensor(c!) state_steps, "
+        "Tensor lr, Tensor lr_decay, Tensor weight_decay, Tensor eps, Tensor active_mask, "
+        "bool maximize) -> Tensor"
+    ),
+}
+
+# Fails here, loudly, if the CUDA library has not been built.
+_cb = _lib.lib()
+
+_library = torch.library.Library("torchstrap", "FRAGMENT")
+
+
+def _already_defined(name: str) -> bool:
+    try:
+        torch._C._dispatch_find_schema_or_throw(f"torchstrap::{name}", "")
+        return True
+    except RuntimeError:
+        return False
+
+
+DEFINED_HERE = []
+for _name, _schema in SCHEMAS.items():
+    if not _already_defined(_name):
+        _library.define(_name + _schema)
+        DEFINED_HERE.append(_name)
+
+
+# ---------------------------------------------------------------------------
+# Host wrappers
+# ---------------------------------------------------------------------------
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, stream_id: int, n_rows: int) -> torch.Tensor:
+    """Scratch for the prologue, one per (device, stream), grown on demand.
+
+    It comes from torch's caching allocator so it lives in the same pool as the
+    state it serves.  Keyed by stream because two steps on different streams may
+    overlap on the GPU.
+    """
+    need = _cb.cb200_workspace_bytes(n_rows)
+    key = (device.index, stream_id)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_consolidated(params: torch.Tensor, op: str) -> None:
+    # The reference also rejects R > 65535 (cuda/consolidated.cuh:72-81) because
+    # it maps rows onto blockIdx.y; the flat work list here has no such limit.
+    if params.dim() != 2:
+        raise RuntimeError(f"{op}: params must be a 2-D (R, T) buffer")
+    if params.dtype != torch.float32:
+        raise RuntimeError(
+            f"{op}: only float32 storage is implemented on sm_100a, got {params.dtype}"
+        )
+
+
+def _hyper(t: torch.Tensor, device: torch.device) -> torch.Tensor:
+    # cuda/consolidated.cuh:87-89 `to_hyper`: compute dtype + contiguous; no-ops normally.
+    if t.dtype is not torch.float32:
+        t = t.to(torch.float32)
+    if t.device != device:
+        raise RuntimeError(f"hyper-parameter on {t.device}, params on {device}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _mask(t: torch.Tensor) -> torch.Tensor:
+    # cuda/consolidated.cuh:91-93 `to_mask`.
+    if t.dtype is not torch.bool:
+        t = t.to(torch.bool)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _same_layout_args(op: str, params: torch.Tensor, others: list[tuple[str, torch.Tensor]]):
+    """Pointers and the strides table for the (R, T) buffers."""
+    shape = params.shape
+    tensors = [("params", params), *others]
+    dense = True
+    for name, t in tensors:
+        if t.shape != shape:
+            raise RuntimeError(f"{op}: {name} has shape {tuple(t.shape)}, params {tuple(shape)}")
+        if t.dtype != torch.float32 or t.device != params.device:
+            raise RuntimeError(f"{op}: {name} must be float32 on {params.device}")
+        if shape[0] > 0 and shape[1] > 0 and (t.stride(1) != 1 or (shape[0] > 1 and t.stride(0) != shape[1])):
+            dense = False
+    if dense:
+        return None
+    flat = []
+    for _, t in tensors:
+        flat += [t.stride(0), t.stride(1)]
+    return (ctypes.c_int64 * len(flat))(*flat)
+
+
+class _Call:
+    """What every wrapper does around the C call: guard, steps, mask, workspace."""
+
+    def __init__(self, op: str, params: torch.Tensor, state_steps: torch.Tensor, active_mask: torch.Tensor):
+        self.op = op
+        self.device = params.device
+        self.n_rows, self.row_len = params.shape
+        if state_steps.numel() != self.n_rows or active_mask.numel() != self.n_rows:
+            raise RuntimeError(f"{op}: state_steps and active_mask must have one entry per row")
+        # The bump lands in the caller's storage (a declared mutation).  A counter
+        # that is not dense fp32 is bumped through a dense copy and written back.
+        self.steps_out = state_steps
+        if state_steps.dtype is torch.float32 and state_steps.is_contiguous():
+            self.steps = state_steps
+        else:
+            self.steps = state_steps.to(torch.float32).contiguous()
+            if self.steps.data_ptr() == state_steps.data_ptr():
+                self.steps = self.steps.clone()
+        self.mask = _mask(active_mask)
+        self.guard = None
+        if torch.cuda.current_device() != self.device.index:
+            self.guard = torch.cuda.device(self.device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+        stream = torch.cuda.current_stream(self.device)
+        self.stream = stream.cuda_stream
+        self.ws = _workspace(self.device, self.stream, self.n_rows)
+        return self
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+        return False
+
+    def finish(self, status: int, params: torch.Tensor) -> torch.Tensor:
+        _lib.check(status, self.op)
+        if self.steps is not self.steps_out:
+            self.steps_out.copy_(self.steps)
+        # Fresh 0-dim tensor aliasing nothing: vmap rejects a function that returns
+        # no Tensor (stubs.cpp:20-24).  Its value is unspecified.
+        return params.new_empty(())
+
+
+def adam_step_cuda(
+    params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, state_steps,
+    lr, beta1, beta2, eps, weight_decay, active_mask,
+    amsgrad, maximize, decoupled_weight_decay,
+):
+    op = "torchstrap::adam_step_"
+    _check_consolidated(params, op)
+    if amsgrad and max_exp_avg_sqs is None:
+        raise RuntimeError("amsgrad=True requires max_exp_avg_sqs")
+    others = [("grads", grads), ("exp_avgs", exp_avgs), ("exp_avg_sqs", exp_avg_sqs)]
+    if amsgrad:
+        others.append(("max_exp_avg_sqs", max_exp_avg_sqs))
+    strides = _same_layout_args(op, params, others)
+    if strides is not None and not amsgrad:
+        strides = (ctypes.c_int64 * 10)(*strides, 0, 0)
+    dev = params.device
+    with _Call(op, params, state_steps, active_mask) as call:
+        lr_c, b1_c, b2_c = _hyper(lr, dev), _hyper(beta1, dev), _hyper(beta2, dev)
+        eps_c, wd_c = _hyper(eps, dev), _hyper(weight_decay, dev)
+        status = _cb.cb200_adam_step(
+            params.data_ptr(), grads.data_ptr(), exp_avgs.data_ptr(), exp_avg_sqs.data_ptr(),
+            max_exp_avg_sqs.data_ptr() if amsgrad else None,
+            call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
+            eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(),
+            call.n_rows, call.row_len, strides,
+            int(amsgrad), int(maximize), int(decoupled_weight_decay),
+            call.ws.data_ptr(), call.ws.numel(), call.stream,
+        )
+        return call.finish(status, params)
+
+
+def sgd_step_cuda(
+    params, grads, momentum_buffers, state_steps,
+    lr, momentum, dampening, weight_decay, active_mask,
+    nesterov, maximize, *, nesterov_rows=None,
+):
+    op = "torchstrap::sgd_step_"
+    _check_consolidated(params, op)
+    if (nesterov or nesterov_rows is not None) and momentum_buffers is None:
+        raise RuntimeError("nesterov=True requires momentum_buffers")
+    others = [("grads", grads)]
+    if momentum_buffers is not None:
+        others.append(("momentum_buffers", momentum_buffers))
+    strides = _same_layout_args(op, params, others)
+    if strides is not None and momentum_buffers is None:
+        strides = (ctypes.c_int64 * 6)(*strides, 0, 0)
+    dev = params.device
+    with _Call(op, params, state_steps, active_mask) as call:
+        lr_c, mom_c = _hyper(lr, dev), _hyper(momentum, dev)
+        damp_c, wd_c = _hyper(dampening, dev), _hyper(weight_decay, dev)
+        nrows_c = _mask(nesterov_rows) if nesterov_rows is not None else None
+        status = _cb.cb200_sgd_step(
+            params.data_ptr(), grads.data_ptr(),
+            momentum_buffers.data_ptr() if momentum_buffers is not None else None,
+            call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(),
+            wd_c.data_ptr(), call.mask.data_ptr(),
+            nrows_c.data_ptr() if nrows_c is not None else None,
+            call.n_rows, call.row_len, strides, int(nesterov), int(maximize),
+            call.ws.data_ptr(), call.ws.numel(), call.stream,
+        )
+        return call.finish(status, params)
+
+
+def adagrad_step_cuda(
+    params, grads, state_sums, state_steps,
+    lr, lr_decay, weight_decay, eps, active_mask, maximize,
+):
+    op = "torchstrap::adagrad_step_"
+    _check_consolidated(params, op)
+    strides = _same_layout_args(op, params, [("grads", grads), ("state_sums", state_sums)])
+    dev = params.device
+    with _Call(op, params, state_steps, active_mask) as call:
+        lr_c, lrd_c = _hyper(lr, dev), _hyper(lr_decay, dev)
+        wd_c, eps_c = _hyper(weight_decay, dev), _hyper(eps, dev)
+        status = _cb.cb200_adagrad_step(
+            params.data_ptr(), grads.data_ptr(), state_sums.data_ptr(),
+            call.steps.data_ptr(), lr_c.data_ptr(), lrd_c.data_ptr(), wd_c.data_ptr(),
+            eps_c.data_ptr(), call.mask.data_ptr(),
+            call.n_rows, call.row_len, strides, int(maximize),
+            call.ws.data_ptr(), call.ws.numel(), call.stream,
+        )
+        return call.finish(status, params)
+
+
+_library.impl("adam_step_", adam_step_cuda, "CUDA")
+_library.impl("sgd_step_", lambda *a: sgd_step_cuda(*a), "CUDA")
+_library.impl("adagrad_step_", adagrad_step_cuda, "CUDA")
+
+
+def launch_count() -> int:
+    """Kernels launched by the step entry points in this process."""
+    return int(_cb.cb200_launch_count())
+
+
+def set_launch_geometry(threads: int = 0, unroll: int = 0, ctas_per_sm: int = 0) -> None:
+    _lib.check(_cb.cb200_set_launch_geometry(threads, unroll, ctas_per_sm), "cb200_set_launch_geometry")

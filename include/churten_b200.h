@@ -1,0 +1,140 @@
+/*
+ * churten_b200 -- C ABI of the B200 (sm_100a) fused batched optimizer step.
+ *
+ * One shared library, libchurten_b200.so, replaces the CUDA half of the
+ * reference's `torchstrap.kernels._C` extension: the three device launchers
+ * behind `torchstrap::adam_step_`, `torchstrap::sgd_step_` and
+ * `torchstrap::adagrad_step_`.  It links against the CUDA runtime only (no
+ * libtorch, no Python), so any host language with a C FFI can bind it.
+ *
+ * Conventions shared by every entry point
+ * ---------------------------------------
+ *  - All buffer pointers are DEVICE pointers on the CURRENT CUDA device.
+ *    `params`, `grads` and the state buffers are fp32 `(n_rows, row_len)`
+ *    matrices: row r is replica r, consolidated over all of its tensors.
+ *  - `strides` is NULL for dense row-major buffers (row stride = row_len,
+ *    element stride = 1); otherwise it points at HOST memory holding, for each
+ *    buffer in argument order, the pair {row stride, element stride} counted in
+ *    elements.  Dense, 16-byte aligned rows with `row_len % 4 == 0` take the
+ *    128-bit streaming kernel; anything else takes the element-wise kernel.
+ *  - `state_steps`, the hyper-parameter vectors and `active_mask` are dense
+ *    `(n_rows,)` device vectors: fp32, and one byte per row (0 = frozen) for
+ *    the mask.
+ *  - `state_steps[r]` is incremented by 1.0f iff `active_mask[r]`, BEFORE the
+ *    update math reads it, so a replica's first update sees step 1.  Frozen
+ *    rows are never read or written: they stay byte-identical.
+ *  - `workspace` is device scratch of at least `cb200_workspace_bytes(n_rows)`
+ *    bytes, 256-byte aligned, owned by the caller.  It holds the compacted list
+ *    of active rows and one 32-byte record of per-row scalars per active row.
+ *    Two calls that may overlap on the GPU (different streams) need two
+ *    workspaces.
+ *  - `stream` is a `cudaStream_t` passed as `void*` (NULL = legacy default
+ *    stream).  Calls are asynchronous: they enqueue two kernels and return;
+ *    nothing synchronises with the host.
+ *  - Return value: CB200_OK or an error code; the text of the last error on
+ *    the calling thread is returned by `cb200_last_error()`.  No entry point
+ *    aborts, throws or prints.
+ */
+#ifndef CHURTEN_B200_H_
+#define CHURTEN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum cb200_status {
+  CB200_OK = 0,
+  CB200_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, bad flag mix */
+  CB200_ERR_WORKSPACE = 2,        /* workspace missing, misaligned or too small */
+  CB200_ERR_CUDA = 3,             /* CUDA runtime / launch error                */
+  CB200_ERR_UNSUPPORTED = 4       /* device is not compute capability 10.x      */
+};
+
+/* Library version as major * 10000 + minor * 100 + patch. */
+int cb200_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* cb200_last_error(void);
+
+/*
+ * Scratch bytes the step entry points need for `n_rows` replicas.
+ * Replaces nothing in the reference (its kernels use no scratch: frozen rows
+ * are skipped by a per-block test, cuda/adam.cu:86-89); here the row test is
+ * done once per step by a prologue kernel that writes this scratch.
+ */
+size_t cb200_workspace_bytes(int64_t n_rows);
+
+/*
+ * Fused Adam / AdamW (+AMSGrad) step over all replicas.
+ * Replaces `adam_step_cuda` + `adam_step_kernel`
+ * (src/torchstrap/kernels/csrc/cuda/adam.cu:250-331, :70-205) behind the schema
+ * `torchstrap::adam_step_` (src/torchstrap/kernels/csrc/stubs.cpp:25-41).
+ * `max_exp_avg_sqs` must be non-NULL iff `amsgrad`.  Strides order: params,
+ * grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs (5 pairs; the last is ignored
+ * without amsgrad).
+ */
+int cb200_adam_step(float* params, const float* grads, float* exp_avgs,
+                    float* exp_avg_sqs, float* max_exp_avg_sqs,
+                    float* state_steps, const float* lr, const float* beta1,
+                    const float* beta2, const float* eps,
+                    const float* weight_decay, const uint8_t* active_mask,
+                    int64_t n_rows, int64_t row_len, const int64_t* strides,
+                    int amsgrad, int maximize, int decoupled_weight_decay,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Fused SGD step (momentum / dampening / nesterov / maximize / weight decay).
+ * Replaces `sgd_step_cuda` + `sgd_step_kernel` + `sgd_math`
+ * (src/torchstrap/kernels/csrc/cuda/sgd.cu:295-359, :134-254, :90-132) behind
+ * `torchstrap::sgd_step_` (stubs.cpp:45-57).  `momentum_buffers` may be NULL
+ * (plain SGD, 12 bytes per element); `nesterov` then must be 0.  A row's first
+ * step (state_steps[r] == 1 after the bump) copies the gradient into its
+ * momentum buffer instead of blending.  `nesterov_rows`, if non-NULL, is a
+ * dense `(n_rows,)` byte vector that overrides the call-level `nesterov` flag
+ * row by row (an extension: the reference schema has one flag per call).
+ * Strides order: params, grads, momentum_buffers (3 pairs).
+ */
+int cb200_sgd_step(float* params, const float* grads, float* momentum_buffers,
+                   float* state_steps, const float* lr, const float* momentum,
+                   const float* dampening, const float* weight_decay,
+                   const uint8_t* active_mask, const uint8_t* nesterov_rows,
+                   int64_t n_rows, int64_t row_len, const int64_t* strides,
+                   int nesterov, int maximize, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
+ * Fused Adagrad step; fp32 storage and accumulator, fp64 parameter update.
+ * Replaces `adagrad_step_cuda` + `adagrad_step_kernel`
+ * (src/torchstrap/kernels/csrc/cuda/adagrad.cu:238-283, :69-198) behind
+ * `torchstrap::adagrad_step_` (stubs.cpp:61-72).
+ * Strides order: params, grads, state_sums (3 pairs).
+ */
+int cb200_adagrad_step(float* params, const float* grads, float* state_sums,
+                       float* state_steps, const float* lr,
+                       const float* lr_decay, const float* weight_decay,
+                       const float* eps, const uint8_t* active_mask,
+                       int64_t n_rows, int64_t row_len, const int64_t* strides,
+                       int maximize, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/*
+ * Launch geometry of the streaming kernels, for benchmarking sweeps.
+ * `threads` in {128, 256, 512, 1024}, `unroll` in {1, 2, 4} 16-byte accesses
+ * per thread per buffer, `ctas_per_sm` >= 1 (persistent grid = SMs x this,
+ * capped by the work available).  0 keeps a field at its default.  Process-wide
+ * and not synchronised: set it before launching, not concurrently with a step.
+ * No counterpart in the reference (fixed 512-thread blocks over 65536-element
+ * chunks, cuda/consolidated.cuh:63-69).
+ */
+int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm);
+
+/* Number of kernels the step entry points have launched in this process. */
+int64_t cb200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHURTEN_B200_H_ */
