@@ -1,0 +1,447 @@
+"""Benchmark of the fused batched optimizer step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  Under torchrun (N > 1) every rank owns a
+contiguous block of replicas and steps it with no collective on the step; the
+per-replica loss vector is all-gathered over NCCL on a side stream each step.
+
+Workload (default `c5_shard`): each GPU's share of the large sharded ensemble --
+Adam (decoupled weight decay 0.01), 1024 replicas x 2,097,152 parameters per GPU
+(8192 replicas on 8 GPUs), per-replica learning rate log-uniform in [1e-5, 1e-3],
+a fixed seeded 10 % of the replicas frozen, parameters ~ N(0, 0.02), gradients
+~ N(0, 1e-3), moments zero.  Synthetic data, seeded.  The working set (34 GB per
+GPU) is far larger than L2, so no flush is needed between steps.
+
+A "step" is one `Adam.update(state)` through the public front-end: two kernel
+launches of libchurten_b200.so.  `value` is whole-job parameter-updates per second
+(active replicas x row length x steps / time, summed over GPUs) with everything
+resident in HBM; `e2e` is the same with that step's gradients copied from pinned
+host memory and the step counters read back inside the timed region.
+
+`--impl reference` times the reference's own CPU kernel (oracle/_ref, built from
+its sources; the plain-C restatement if that is absent) on the host cores, on a
+bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+FALLBACK_HBM_GBS = 6650.0
+
+WORKLOADS = {
+    # name: optimizer, rows per GPU, row length, frozen fraction, bytes per active element
+    "c5_shard": dict(opt="adam", rows=1024, row_len=2_097_152, frozen=0.10, amsgrad=False,
+                     desc="Adam (AdamW wd=0.01), 1024 replicas/GPU x T=2,097,152, lr log-uniform "
+                          "[1e-5,1e-3], 10% frozen: one GPU's share of the 8192-replica ensemble"),
+    "c1": dict(opt="adam", rows=8, row_len=264_580, frozen=0.0, amsgrad=False, l2_wd=True,
+               desc="Adam wd=0, 8 replicas x 264,580 (3-layer MLP), all active"),
+    "c2": dict(opt="adam", rows=100, row_len=264_580, frozen=0.30, amsgrad=True,
+               desc="AdamW+AMSGrad wd=0.01, 100 replicas x 264,580, lr log-uniform [1e-4,1e-2], "
+                    "Bernoulli(0.7) mask"),
+    "c3": dict(opt="sgd", rows=1024, row_len=1_147_468, frozen=0.0,
+               desc="SGD momentum in {0,0.5,0.9}, wd=1e-4, 1024 replicas x 1,147,468 (CNN), all active"),
+    "c4": dict(opt="adagrad", rows=256, row_len=4_194_304, frozen=0.0,
+               desc="Adagrad lr=1e-2 lr_decay=1e-4 eps=1e-10 acc0=0.1, 256 replicas x 4,194,304"),
+}
+BYTES_PER_ELEM = {"adam": 28, "adam_amsgrad": 36, "sgd": 20, "adagrad": 20}
+
+
+def _bytes_per_elem(w) -> int:
+    if w["opt"] == "adam":
+        return BYTES_PER_ELEM["adam_amsgrad" if w.get("amsgrad") else "adam"]
+    return BYTES_PER_ELEM[w["opt"]]
+
+
+def _peak_gbs():
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while timing runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.lines: list[str] = []
+        self.proc = None
+        self.thread = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# workload construction
+# ---------------------------------------------------------------------------
+def _hyper(w, n, gen, device):
+    import torch
+
+    def loguniform(lo, hi):
+        return torch.exp(torch.empty(n, device=device).uniform_(math.log(lo), math.log(hi), generator=gen))
+
+    if w["opt"] == "adam":
+        lr = loguniform(1e-5, 1e-3) if w["rows"] >= 1024 else (
+            loguniform(1e-4, 1e-2) if w.get("amsgrad") else torch.full((n,), 1e-3, device=device))
+        return dict(lr=lr, weight_decay=0.0 if w.get("l2_wd") else 0.01, amsgrad=bool(w.get("amsgrad")),
+                    decoupled_weight_decay=not w.get("l2_wd"))
+    if w["opt"] == "sgd":
+        mom = torch.tensor([0.0, 0.5, 0.9], device=device)[torch.randint(0, 3, (n,), device=device, generator=gen)]
+        return dict(lr=1e-2, momentum=mom, dampening=0.0, weight_decay=1e-4)
+    return dict(lr=1e-2, lr_decay=1e-4, eps=1e-10, weight_decay=0.0, initial_accumulator_value=0.1)
+
+
+def build_state(w, n_rows, device, seed):
+    """A `State` over raw (n_rows, row_len) buffers with the workload's optimizer attached."""
+    import torch
+
+    from churten_b200 import optimizer as opts
+    from churten_b200.state import State
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    t = w["row_len"]
+    params = torch.empty(n_rows, t, device=device).normal_(0.0, 0.02, generator=gen)
+    grads = torch.empty(n_rows, t, device=device).normal_(0.0, 1e-3, generator=gen)
+    state = State(params=params, buffers=torch.empty(n_rows, 0, device=device),
+                  param_meta=[("flat", params.shape, 0, t)], buffer_meta=[], grads=grads)
+    cls = {"adam": opts.Adam, "sgd": opts.SGD, "adagrad": opts.Adagrad}[w["opt"]]
+    cls.init(state, **_hyper(w, n_rows, gen, device))
+    if w["frozen"] > 0:
+        frozen = torch.rand(n_rows, device=device, generator=gen) < w["frozen"]
+        state.active_mask.copy_(~frozen)
+    return state, cls
+
+
+# ---------------------------------------------------------------------------
+# CPU legs
+# ---------------------------------------------------------------------------
+def cpu_reference_rate(w, steps, warmup, sample_rows):
+    """param-updates/s of the reference's CPU kernel on `sample_rows` rows of the workload."""
+    import torch
+
+    import oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    kind = "reference" if oracle.load_reference() else "port"
+    cpu = torch.device("cpu")
+    gen = torch.Generator().manual_seed(1234)
+    n, t = sample_rows, w["row_len"]
+    p = torch.empty(n, t).normal_(0.0, 0.02, generator=gen)
+    g = torch.empty(n, t).normal_(0.0, 1e-3, generator=gen)
+    mask = torch.rand(n, generator=gen) >= w["frozen"]
+    stp = torch.zeros(n)
+    full = lambda x: torch.full((n,), float(x))
+    if w["opt"] == "adam":
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        mx = torch.zeros_like(p) if w.get("amsgrad") else None
+        lr = torch.exp(torch.empty(n).uniform_(math.log(1e-5), math.log(1e-3), generator=gen))
+        args = (p, g, m, v, mx, stp, lr, full(0.9), full(0.999), full(1e-8), full(0.01), mask,
+                bool(w.get("amsgrad")), False, True)
+        name = "adam"
+    elif w["opt"] == "sgd":
+        args = (p, g, torch.zeros_like(p), stp, full(1e-2), full(0.9), full(0.0), full(1e-4), mask, False, False)
+        name = "sgd"
+    else:
+        args = (p, g, torch.full_like(p, 0.1), stp, full(1e-2), full(1e-4), full(0.0), full(1e-10), mask, False)
+        name = "adagrad"
+    if kind == "reference":
+        op = getattr(torch.ops.torchstrap, name + "_step_")
+        run = lambda: op(*args)
+    else:
+        oracle.set_threads(cores)
+        fn = getattr(oracle, name + "_step")
+        run = lambda: fn(oracle.CPU_FORM, *args)
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = time.perf_counter() - t0
+    active = int(mask.sum()) * t
+    return dict(value=active * steps / dt, ms_per_step=dt / steps * 1e3, cores=cores, kind=kind,
+                sample=f"{n} of the workload's rows (x T={t}), {int(mask.sum())} active, {steps} steps "
+                       f"after {warmup} warm-ups, all {cores} host threads",
+                active_elements=active)
+
+
+def cpu_baseline_in_child(args) -> dict:
+    """The CPU leg runs in a process of its own: the GPU arm never loads the oracle."""
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--impl", "reference", "--steps", "5",
+           "--warmup", "2", "--workload", args.workload]
+    if args.rows:
+        cmd += ["--rows", str(args.rows)]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        for text in reversed(out.stdout.strip().splitlines()):
+            if text.startswith("{"):
+                return json.loads(text)["cpu_baseline"]
+        return {"value": None, "error": (out.stderr or "no output")[-300:]}
+    except Exception as exc:  # the GPU numbers stand without it
+        return {"value": None, "error": repr(exc)}
+
+
+def _percentile(values, q):
+    ordered = sorted(values)
+    return ordered[min(len(ordered) - 1, max(0, int(round(q * (len(ordered) - 1)))))]
+
+
+def run_reference_arm(args, w, world, rank):
+    if rank != 0:
+        return
+    sample_rows = min(w["rows"], max(1, (1 << 27) // w["row_len"]))  # ~134 M elements per step
+    steps = min(args.steps, 20)
+    res = cpu_reference_rate(w, steps, min(args.warmup, 3), sample_rows)
+    line = {
+        "impl": "reference", "metric": "param_updates_per_s", "value": res["value"],
+        "unit": "param-updates/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
+        "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": w["rows"],
+                   "row_len": w["row_len"]},
+        "cpu_baseline": {"value": res["value"], "unit": "param-updates/s", "cores": res["cores"],
+                         "kind": res["kind"], "sample": res["sample"]},
+        "e2e": {"value": res["value"], "unit": "param-updates/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_ours(args, w, world, rank, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    distributed = world > 1
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if distributed:
+        dist.init_process_group("nccl", device_id=device)
+
+    from churten_b200.kernels import _C
+    from churten_b200.sharded import MetricGather, ShardSpec, verify_shard_map
+
+    n_local, t = w["rows"], w["row_len"]
+    spec = ShardSpec(n_local * world, world, rank)
+    verify_shard_map(spec)
+    state, opt = build_state(w, n_local, device, seed=5 * 1000 + rank)
+    gather = MetricGather(spec, device)
+    loss = state.grads[:, 0].contiguous()  # stands in for the per-replica loss of the step
+    active_rows = int(state.active_mask.sum().item())
+    active_elems = active_rows * t
+    bpe = _bytes_per_elem(w)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def step():
+        gather.start(loss)
+        opt.update(state)
+        gather.wait()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- resident-data timing: K steps, one event pair around each step's op ----
+    stream = torch.cuda.current_stream(device)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = _C.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        t_all0.record(stream)
+        for i in range(args.steps):
+            gather.start(loss)
+            starts[i].record(stream)
+            opt.update(state)
+            stops[i].record(stream)
+            gather.wait()
+        t_all1.record(stream)
+        barrier()
+    launches = _C.launch_count() - launches0
+    total_ms = t_all0.elapsed_time(t_all1)
+    per_op_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+    clock_summary = clocks.summary()
+
+    # ---- end to end: gradients from pinned host memory, step counters read back ----
+    pin_rows = min(n_local, max(1, (1 << 30) // (t * 4)))
+    pinned = torch.empty(pin_rows, t, dtype=torch.float32).pin_memory()
+    pinned.normal_(0.0, 1e-3)
+    steps_host = torch.empty(n_local, dtype=torch.float32).pin_memory()
+    h2d = n_local * t * 4
+    d2h = n_local * 4
+
+    def e2e_step():
+        for r0 in range(0, n_local, pin_rows):
+            r1 = min(n_local, r0 + pin_rows)
+            state.grads[r0:r1].copy_(pinned[: r1 - r0], non_blocking=True)
+        opt.update(state)
+        steps_host.copy_(state.optimizer_state["state_steps"], non_blocking=True)
+
+    e2e_steps = min(args.steps, 10)
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    # ---- max over ranks, sum of work ----
+    stats = torch.tensor([total_ms, e2e_ms, statistics.mean(per_op_ms)], dtype=torch.float64, device=device)
+    work = torch.tensor([active_elems, launches], dtype=torch.float64, device=device)
+    if distributed:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, op_ms = stats.tolist()
+    job_elems, job_launches = work.tolist()
+
+    if rank == 0:
+        peak, peak_kind = _peak_gbs()
+        achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
+        per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else ""))
+        traffic = per_elem * active_elems if per_elem is not None else None
+        line = {
+            "metric": "param_updates_per_s",
+            "value": job_elems * args.steps / (total_ms * 1e-3),
+            "unit": "param-updates/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
+                       "row_len": t, "active_rows_rank0": active_rows,
+                       "l2": "inputs larger than L2 (no flush needed)"
+                             if n_local * t * bpe > 2 * 126e6 else "working set fits in L2: not flushed",
+                       "parallelism": f"replica-block x{world}, no collective on the step; "
+                                      f"loss all-gather ({n_local * world * 4} B) on a side stream"},
+            "e2e": {"value": job_elems * e2e_steps / (e2e_ms * 1e-3), "unit": "param-updates/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(job_launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": peak_kind,
+                         "frac_of_nominal_8tbs": achieved / 8000.0,
+                         "bytes_per_element": bpe, "elements_per_launch": active_elems,
+                         "op_ms_mean": statistics.mean(per_op_ms), "op_ms_median": statistics.median(per_op_ms),
+                         "op_ms_p10": _percentile(per_op_ms, 0.1),
+                         "op_ms_p90": _percentile(per_op_ms, 0.9),
+                         "traffic": traffic},
+            "clocks": clock_summary,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_in_child(args)
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) per active element of the dominant kernel, from an ncu
+# capture of a smaller case of the same kernel (profiles/); traffic grows in
+# proportion to the elements processed.
+TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {}
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5_shard")
+    ap.add_argument("--rows", type=int, default=0, help="override replicas per GPU (profiling small cases)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = dict(WORKLOADS[args.workload])
+    if args.rows:
+        w["rows"] = args.rows
+    if args.impl == "reference":
+        run_reference_arm(args, w, world, rank)
+        return
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        sys.exit("launch with torch.distributed.run for --gpus > 1")
+    run_ours(args, w, world, rank, local_rank)
+
+
+if __name__ == "__main__":
+    main()

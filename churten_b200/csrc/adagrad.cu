@@ -51,7 +51,7 @@ extern "C" int cb200_adagrad_step(float* params, const float* grads, float* stat
   using VecOp = AdagradOp<kAdagradFuseVec>;
   using ElemOp = AdagradOp<kAdagradFuseElem>;
   Bufs<3> bufs;
-  if (int rc = fill_bufs(&bufs, ptrs, strides, row_len, names)) return rc;
+  if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
   return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len,
                                  maximize ? 1 : 0, workspace, workspace_bytes,
                                  static_cast<cudaStream_t>(stream));

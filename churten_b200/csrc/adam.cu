@@ -44,7 +44,7 @@ int adam_dispatch(const AdamHyper& hyper, float* state_steps, const uint8_t* mas
   static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs",
                                        "max_exp_avg_sqs"};
   Bufs<VecOp::kBufs> bufs;
-  if (int rc = fill_bufs(&bufs, ptrs, strides, row_len, names)) return rc;
+  if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
   return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags,
                                  workspace, workspace_bytes, stream);
 }

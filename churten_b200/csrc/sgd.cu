@@ -63,14 +63,14 @@ extern "C" int cb200_sgd_step(float* params, const float* grads, float* momentum
     using VecOp = SgdOp<true, kSgdFuseVecBuf>;
     using ElemOp = SgdOp<true, kSgdFuseElemBuf>;
     Bufs<3> bufs;
-    if (int rc = fill_bufs(&bufs, ptrs, strides, row_len, names)) return rc;
+    if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
     return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len, flags,
                                    workspace, workspace_bytes, s);
   }
   using VecOp = SgdOp<false, kSgdFuseVecPlain>;
   using ElemOp = SgdOp<false, kSgdFuseElemPlain>;
   Bufs<2> bufs;
-  if (int rc = fill_bufs(&bufs, ptrs, strides, row_len, names)) return rc;
+  if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
   return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len, flags,
                                  workspace, workspace_bytes, s);
 }

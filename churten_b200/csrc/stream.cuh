@@ -476,10 +476,12 @@ inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
 
 // Fills a buffer table from the C-ABI arguments.
 template <int NB>
-inline int fill_bufs(Bufs<NB>* out, float* const* ptrs, const int64_t* strides, int64_t row_len,
-                     const char* const* names) {
+inline int fill_bufs(Bufs<NB>* out, float* const* ptrs, const int64_t* strides, int64_t n_rows,
+                     int64_t row_len, const char* const* names) {
+  // Empty matrices have no storage: their pointers may be NULL and are never used.
+  const bool need_data = n_rows > 0 && row_len > 0;
   for (int i = 0; i < NB; ++i) {
-    if (!ptrs[i]) return fail(1, std::string(names[i]) + " must not be NULL");
+    if (need_data && !ptrs[i]) return fail(1, std::string(names[i]) + " must not be NULL");
     out->ptr[i] = ptrs[i];
     out->stride_r[i] = strides ? strides[2 * i] : row_len;
     out->stride_t[i] = strides ? strides[2 * i + 1] : 1;

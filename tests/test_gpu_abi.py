@@ -1,0 +1,146 @@
+"""Direct calls through the C ABI with ctypes (no torch operator in between), its
+error codes on the GPU, and `torch.library.opcheck` of the three operators."""
+
+import ctypes
+
+import pytest
+import torch
+
+from churten_b200 import _lib
+from helpers import assert_bits_equal, full
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _adam_args(R, T, cuda, seed=0):
+    gen = torch.Generator(device=cuda).manual_seed(seed)
+    bufs = [torch.randn(R, T, device=cuda, generator=gen) for _ in range(4)]
+    bufs[3].abs_()
+    side = [full(R, x, cuda) for x in (1e-3, 0.9, 0.999, 1e-8, 1e-2)]
+    return bufs, torch.zeros(R, device=cuda), side, torch.ones(R, dtype=torch.bool, device=cuda)
+
+
+def test_adam_through_ctypes_matches_the_operator(cuda):
+    import churten_b200.kernels  # noqa: F401
+
+    lib = _lib.lib()
+    R, T = 6, 4100
+    bufs, steps, side, mask = _adam_args(R, T, cuda)
+    ref = [b.clone() for b in bufs]
+    ref_steps = steps.clone()
+    ws = torch.empty(lib.cb200_workspace_bytes(R), dtype=torch.uint8, device=cuda)
+    rc = lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+                             _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
+                             0, 0, 1, _ptr(ws), ws.numel(), _stream())
+    assert rc == _lib.OK, _lib.last_error()
+    torch.ops.torchstrap.adam_step_(ref[0], ref[1], ref[2], ref[3], None, ref_steps, *side, mask,
+                                    amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    torch.cuda.synchronize()
+    for a, b in zip(bufs, ref):
+        assert_bits_equal("buffer", a, b)
+    assert torch.equal(steps, ref_steps)
+    assert lib.cb200_launch_count() >= 4
+
+
+def test_error_codes(cuda):
+    lib = _lib.lib()
+    R, T = 4, 64
+    bufs, steps, side, mask = _adam_args(R, T, cuda)
+    before = [b.clone() for b in bufs]
+    ws = torch.empty(lib.cb200_workspace_bytes(R) + 256, dtype=torch.uint8, device=cuda)
+    common = lambda w, wbytes: lib.cb200_adam_step(
+        _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
+        *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, w, wbytes, _stream())
+    assert common(None, 0) == _lib.ERR_WORKSPACE
+    assert common(_ptr(ws), 16) == _lib.ERR_WORKSPACE and "too small" in _lib.last_error()
+    assert common(ctypes.c_void_p(ws.data_ptr() + 8), ws.numel() - 8) == _lib.ERR_WORKSPACE
+    rc = lib.cb200_adam_step(None, _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
+                             *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, _ptr(ws),
+                             ws.numel(), _stream())
+    assert rc == _lib.ERR_INVALID_ARGUMENT and "params" in _lib.last_error()
+    assert lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+                               _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), -1, T, None,
+                               0, 0, 1, _ptr(ws), ws.numel(), _stream()) == _lib.ERR_INVALID_ARGUMENT
+    torch.cuda.synchronize()
+    # a rejected call launches nothing: buffers and clock untouched
+    for a, b in zip(bufs, before):
+        assert_bits_equal("buffer", a, b)
+    assert steps.abs().sum() == 0
+    assert common(_ptr(ws), ws.numel()) == _lib.OK
+
+
+def test_operator_errors_are_runtime_errors(cuda):
+    import churten_b200.kernels  # noqa: F401
+
+    ops = torch.ops.torchstrap
+    R, T = 2, 8
+    bufs, steps, side, mask = _adam_args(R, T, cuda)
+    with pytest.raises(RuntimeError, match="2-D"):
+        ops.adam_step_(bufs[0].view(-1), bufs[1], bufs[2], bufs[3], None, steps, *side, mask,
+                       amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    with pytest.raises(RuntimeError, match="max_exp_avg_sqs"):
+        ops.adam_step_(bufs[0], bufs[1], bufs[2], bufs[3], None, steps, *side, mask,
+                       amsgrad=True, maximize=False, decoupled_weight_decay=True)
+    with pytest.raises(RuntimeError, match="nesterov"):
+        ops.sgd_step_(bufs[0], bufs[1], None, steps, side[0], side[1], side[1], side[1], mask,
+                      nesterov=True, maximize=False)
+    with pytest.raises(RuntimeError, match="float32"):
+        ops.adam_step_(bufs[0].double(), bufs[1].double(), bufs[2].double(), bufs[3].double(), None,
+                       steps, *side, mask, amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    cpu = [b.cpu() for b in bufs]
+    from conftest import HAVE_REFERENCE
+
+    if not HAVE_REFERENCE:  # with the reference loaded, CPU tensors run ITS kernels
+        with pytest.raises(NotImplementedError):
+            ops.adam_step_(cpu[0], cpu[1], cpu[2], cpu[3], None, steps.cpu(),
+                           *[s.cpu() for s in side], mask.cpu(), amsgrad=False, maximize=False,
+                           decoupled_weight_decay=True)
+
+
+def test_returns_fresh_scalar_that_aliases_nothing(cuda):
+    import churten_b200.kernels  # noqa: F401
+
+    bufs, steps, side, mask = _adam_args(3, 16, cuda)
+    out = torch.ops.torchstrap.adam_step_(bufs[0], bufs[1], bufs[2], bufs[3], None, steps, *side,
+                                          mask, amsgrad=False, maximize=False,
+                                          decoupled_weight_decay=True)
+    assert out.shape == () and out.dtype == torch.float32 and out.device == bufs[0].device
+    assert out.data_ptr() not in {b.data_ptr() for b in bufs}
+
+
+@pytest.mark.parametrize("opt", ["adam", "adam_amsgrad", "sgd", "sgd_plain", "adagrad"])
+def test_opcheck(cuda, opt):
+    """Schema, alias annotations, fake kernel (reference test_cpu_cuda_parity.py:34-51)."""
+    import churten_b200.kernels  # noqa: F401
+
+    R, T = 3, 24
+    gen = torch.Generator(device=cuda).manual_seed(0)
+    rnd = lambda: torch.randn(R, T, device=cuda, generator=gen)
+    steps, mask = torch.zeros(R, device=cuda), torch.ones(R, dtype=torch.bool, device=cuda)
+    v = lambda x: full(R, x, cuda)
+    ops = torch.ops.torchstrap
+    tests = ("test_schema", "test_faketensor")
+    if opt.startswith("adam"):
+        ams = opt.endswith("amsgrad")
+        args = (rnd(), rnd(), rnd(), rnd().abs(), rnd().abs() if ams else None, steps, v(1e-3),
+                v(0.9), v(0.999), v(1e-8), v(1e-2), mask)
+        torch.library.opcheck(ops.adam_step_.default, args,
+                              dict(amsgrad=ams, maximize=False, decoupled_weight_decay=True),
+                              test_utils=tests)
+    elif opt.startswith("sgd"):
+        buf = rnd() if opt == "sgd" else None
+        args = (rnd(), rnd(), buf, steps, v(1e-2), v(0.9 if buf is not None else 0.0), v(0.0),
+                v(1e-4), mask)
+        torch.library.opcheck(ops.sgd_step_.default, args, dict(nesterov=False, maximize=False),
+                              test_utils=tests)
+    else:
+        args = (rnd(), rnd(), rnd().abs(), steps, v(1e-2), v(0.0), v(0.0), v(1e-10), mask)
+        torch.library.opcheck(ops.adagrad_step_.default, args, dict(maximize=False), test_utils=tests)

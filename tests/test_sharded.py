@@ -1,0 +1,91 @@
+"""Replica-block sharding (host logic; world_size-2 gloo processes on CPU)."""
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from churten_b200.sharded import MetricGather, ShardSpec, shard_bounds, shard_sizes, verify_shard_map
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("n,world", [(8192, 8), (8192, 4), (8192, 2), (100, 8), (7, 3), (2, 4), (0, 2), (5, 1)])
+def test_blocks_tile_the_ensemble(n, world):
+    bounds = [shard_bounds(n, world, r) for r in range(world)]
+    assert bounds[0][0] == 0 and bounds[-1][1] == n
+    for (a, b), (c, d) in zip(bounds, bounds[1:]):
+        assert b == c and a <= b
+    sizes = shard_sizes(n, world)
+    assert sum(sizes) == n and max(sizes) - min(sizes) <= 1
+
+
+def test_bad_rank_is_rejected():
+    with pytest.raises(ValueError):
+        shard_bounds(10, 2, 2)
+    with pytest.raises(ValueError):
+        shard_bounds(-1, 2, 0)
+
+
+def test_single_process_gather_is_the_identity():
+    spec = ShardSpec(5, 1, 0)
+    verify_shard_map(spec)
+    out = MetricGather(spec, "cpu")(torch.arange(5.0))
+    assert out.tolist() == [0.0, 1.0, 2.0, 3.0, 4.0]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, n_rows, result_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        spec = ShardSpec(n_rows, world, rank)
+        verify_shard_map(spec)
+        a, b = spec.bounds
+        # every rank builds the same full problem and keeps its block
+        gen = torch.Generator().manual_seed(0)
+        full_metric = torch.randn(n_rows, generator=gen)
+        local = spec.local(full_metric).clone()
+        gather = MetricGather(spec, "cpu")
+        out = gather(local)
+        assert torch.equal(out, full_metric), (rank, out, full_metric)
+        # a second round reuses the buffers
+        out2 = gather(local * 2)
+        assert torch.equal(out2, full_metric * 2)
+        # the freeze decision derived from the gathered metric is identical on all ranks
+        # and is applied to the local slice only
+        stop = out > 0.5
+        mask = torch.ones(b - a, dtype=torch.bool)
+        mask[stop[a:b]] = False
+        torch.save({"bounds": (a, b), "mask": mask, "stop": stop}, f"{result_dir}/rank{rank}.pt")
+        # an inconsistent map is caught on every rank
+        bad = ShardSpec(n_rows + (1 if rank == 1 else 0), world, rank)
+        try:
+            verify_shard_map(bad)
+            raise AssertionError("inconsistent shard map was not detected")
+        except RuntimeError as e:
+            assert "shard" in str(e)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_rows", [8, 7])
+def test_two_ranks_gloo(tmp_path, n_rows):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), n_rows, str(tmp_path)), nprocs=world, join=True)
+    parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    assert parts[0]["bounds"][1] == parts[1]["bounds"][0]
+    assert torch.equal(parts[0]["stop"], parts[1]["stop"])
+    joined = torch.cat([p["mask"] for p in parts])
+    assert torch.equal(joined, ~parts[0]["stop"])
