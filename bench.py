@@ -79,61 +79,83 @@ def _peak_gbs():
 # clocks
 # ---------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while timing runs."""
+    """Samples SM clock and clock-event reasons of one GPU (read-only NVML queries)
+    every few milliseconds while the timed region runs; nvidia-smi if NVML is missing."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
+               "sw_thermal_slowdown": 0x20}
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index = index
-        self.lines: list[str] = []
-        self.proc = None
-        self.thread = None
+        self.period = period_s
+        self.sm: list[float] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def _open(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = self.index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if self.index < len(ids) and ids[self.index].isdigit():
+                    physical = int(ids[self.index])
+            handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = (pynvml, handle)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        pynvml, handle = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                bits = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                for name, bit in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def _smi_once(self):
+        try:
+            out = subprocess.run(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm",
+                 "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10)
+            a, b = [float(x) for x in out.stdout.strip().split(",")[:2]]
+            self.sm.append(a)
+            self.max_mhz = b
+        except Exception:
+            pass
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        self._open()
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
     def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        else:
+            self._smi_once()
         return False
 
     def summary(self) -> dict:
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_min_mhz": min(self.sm) if self.sm else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.sm), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 # ---------------------------------------------------------------------------
@@ -306,9 +328,11 @@ def run_ours(args, w, world, rank, local_rank):
         torch.cuda.synchronize(device)
 
     def step():
-        gather.start(loss)
+        if distributed:
+            gather.start(loss)
         opt.update(state)
-        gather.wait()
+        if distributed:
+            gather.wait()
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -324,11 +348,13 @@ def run_ours(args, w, world, rank, local_rank):
         barrier()
         t_all0.record(stream)
         for i in range(args.steps):
-            gather.start(loss)
+            if distributed:
+                gather.start(loss)
             starts[i].record(stream)
             opt.update(state)
             stops[i].record(stream)
-            gather.wait()
+            if distributed:
+                gather.wait()
         t_all1.record(stream)
         barrier()
     launches = _C.launch_count() - launches0

@@ -32,8 +32,8 @@ SIGNATURES = {
         [_P, _P, _P, _P, _P, _P,
          # lr beta1 beta2 eps weight_decay active_mask
          _P, _P, _P, _P, _P, _P,
-         # n_rows row_len strides amsgrad maximize decoupled
-         c_int64, c_int64, _P, c_int, c_int, c_int,
+         # n_rows row_len strides amsgrad maximize decoupled active_rows_hint
+         c_int64, c_int64, _P, c_int, c_int, c_int, c_int64,
          # workspace workspace_bytes stream
          _P, c_size_t, _P],
     ),
@@ -41,15 +41,16 @@ SIGNATURES = {
         c_int,
         # params grads momentum_buffers state_steps lr momentum dampening weight_decay
         [_P, _P, _P, _P, _P, _P, _P, _P,
-         # active_mask nesterov_rows n_rows row_len strides nesterov maximize
-         _P, _P, c_int64, c_int64, _P, c_int, c_int,
+         # active_mask nesterov_rows n_rows row_len strides nesterov maximize active_rows_hint
+         _P, _P, c_int64, c_int64, _P, c_int, c_int, c_int64,
          _P, c_size_t, _P],
     ),
     "cb200_adagrad_step": (
         c_int,
         # params grads state_sums state_steps lr lr_decay weight_decay eps active_mask
         [_P, _P, _P, _P, _P, _P, _P, _P, _P,
-         c_int64, c_int64, _P, c_int, _P, c_size_t, _P],
+         # n_rows row_len strides maximize active_rows_hint workspace workspace_bytes stream
+         c_int64, c_int64, _P, c_int, c_int64, _P, c_size_t, _P],
     ),
     "cb200_set_launch_geometry": (c_int, [c_int, c_int, c_int]),
     "cb200_launch_count": (c_int64, []),

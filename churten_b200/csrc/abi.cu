@@ -15,7 +15,7 @@ namespace {
 
 thread_local std::string g_last_error;
 
-std::atomic<int> g_threads{512};
+std::atomic<int> g_threads{256};
 std::atomic<int> g_unroll{0};
 std::atomic<int> g_ctas_per_sm{0};
 std::atomic<long long> g_launches{0};

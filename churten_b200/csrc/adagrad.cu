@@ -39,7 +39,8 @@ extern "C" int cb200_adagrad_step(float* params, const float* grads, float* stat
                                   float* state_steps, const float* lr, const float* lr_decay,
                                   const float* weight_decay, const float* eps,
                                   const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
-                                  const int64_t* strides, int maximize, void* workspace,
+                                  const int64_t* strides, int maximize,
+                                  int64_t active_rows_hint, void* workspace,
                                   size_t workspace_bytes, void* stream) {
   using namespace cb200;
   if (n_rows > 0 && (!lr || !lr_decay || !weight_decay || !eps)) {
@@ -53,6 +54,6 @@ extern "C" int cb200_adagrad_step(float* params, const float* grads, float* stat
   Bufs<3> bufs;
   if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
   return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len,
-                                 maximize ? 1 : 0, workspace, workspace_bytes,
+                                 maximize ? 1 : 0, active_rows_hint, workspace, workspace_bytes,
                                  static_cast<cudaStream_t>(stream));
 }

@@ -38,14 +38,15 @@ struct AdamOp {
 template <bool AMSGRAD, bool ADAMW>
 int adam_dispatch(const AdamHyper& hyper, float* state_steps, const uint8_t* mask,
                   float* const* ptrs, const int64_t* strides, int64_t n_rows, int64_t row_len,
-                  int flags, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                  int flags, int64_t hint, void* workspace, size_t workspace_bytes,
+                  cudaStream_t stream) {
   using VecOp = AdamOp<AMSGRAD, ADAMW, kAdamFuseVec>;
   using ElemOp = AdamOp<AMSGRAD, ADAMW, kAdamFuseElem>;
   static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs",
                                        "max_exp_avg_sqs"};
   Bufs<VecOp::kBufs> bufs;
   if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
-  return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags,
+  return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags, hint,
                                  workspace, workspace_bytes, stream);
 }
 
@@ -58,10 +59,11 @@ extern "C" int cb200_adam_step(float* params, const float* grads, float* exp_avg
                                const float* eps, const float* weight_decay,
                                const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
                                const int64_t* strides, int amsgrad, int maximize,
-                               int decoupled_weight_decay, void* workspace,
-                               size_t workspace_bytes, void* stream) {
+                               int decoupled_weight_decay, int64_t active_rows_hint,
+                               void* workspace, size_t workspace_bytes, void* stream) {
   using namespace cb200;
-  if (amsgrad && !max_exp_avg_sqs) {
+  // (an empty matrix has no storage, so a NULL there says nothing)
+  if (amsgrad && !max_exp_avg_sqs && n_rows > 0 && row_len > 0) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "amsgrad=True requires max_exp_avg_sqs");
   }
   if (n_rows > 0 && (!lr || !beta1 || !beta2 || !eps || !weight_decay)) {
@@ -74,15 +76,19 @@ extern "C" int cb200_adam_step(float* params, const float* grads, float* exp_avg
   if (amsgrad) {
     if (decoupled_weight_decay) {
       return adam_dispatch<true, true>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                       row_len, flags, workspace, workspace_bytes, s);
+                                       row_len, flags, active_rows_hint, workspace,
+                                       workspace_bytes, s);
     }
     return adam_dispatch<true, false>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                      row_len, flags, workspace, workspace_bytes, s);
+                                      row_len, flags, active_rows_hint, workspace,
+                                       workspace_bytes, s);
   }
   if (decoupled_weight_decay) {
     return adam_dispatch<false, true>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                      row_len, flags, workspace, workspace_bytes, s);
+                                      row_len, flags, active_rows_hint, workspace,
+                                       workspace_bytes, s);
   }
   return adam_dispatch<false, false>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                     row_len, flags, workspace, workspace_bytes, s);
+                                     row_len, flags, active_rows_hint, workspace,
+                                       workspace_bytes, s);
 }

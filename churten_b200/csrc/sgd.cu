@@ -45,10 +45,11 @@ extern "C" int cb200_sgd_step(float* params, const float* grads, float* momentum
                               const float* dampening, const float* weight_decay,
                               const uint8_t* active_mask, const uint8_t* nesterov_rows,
                               int64_t n_rows, int64_t row_len, const int64_t* strides,
-                              int nesterov, int maximize, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+                              int nesterov, int maximize, int64_t active_rows_hint,
+                              void* workspace, size_t workspace_bytes, void* stream) {
   using namespace cb200;
-  if ((nesterov || nesterov_rows) && !momentum_buffers) {
+  // (an empty matrix has no storage, so a NULL there says nothing)
+  if ((nesterov || nesterov_rows) && !momentum_buffers && n_rows > 0 && row_len > 0) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "nesterov=True requires momentum_buffers");
   }
   if (n_rows > 0 && (!lr || !momentum || !dampening || !weight_decay)) {
@@ -65,12 +66,12 @@ extern "C" int cb200_sgd_step(float* params, const float* grads, float* momentum
     Bufs<3> bufs;
     if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
     return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len, flags,
-                                   workspace, workspace_bytes, s);
+                                   active_rows_hint, workspace, workspace_bytes, s);
   }
   using VecOp = SgdOp<false, kSgdFuseVecPlain>;
   using ElemOp = SgdOp<false, kSgdFuseElemPlain>;
   Bufs<2> bufs;
   if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
   return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len, flags,
-                                 workspace, workspace_bytes, s);
+                                 active_rows_hint, workspace, workspace_bytes, s);
 }

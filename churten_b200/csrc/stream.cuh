@@ -45,7 +45,7 @@ namespace cb200 {
 struct LaunchGeometry {
   int threads;      // block size of the streaming kernels
   int unroll;       // 16-byte accesses per thread per buffer per tile; 0 = by size
-  int ctas_per_sm;  // persistent CTAs per SM; 0 = what the occupancy query says
+  int ctas_per_sm;  // 0: one CTA per tile (default); > 0: persistent grid of SMs x this
 };
 LaunchGeometry geometry();
 void set_error(const std::string& msg);
@@ -365,23 +365,13 @@ inline cudaError_t launch_dependent(Kernel kernel, dim3 grid, dim3 block, cudaSt
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <class Kernel>
-inline int resident_ctas(Kernel kernel, int threads) {
-  int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
-    (void)cudaGetLastError();
-    n = 1;
-  }
-  return n;
-}
-
 // Runs the two launches of one step.  VecOp / ElemOp are the same optimizer with
 // the fusion masks of torch's vector and element-wise paths.
 template <class VecOp, class ElemOp>
 inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
                     const uint8_t* active_mask, const Bufs<VecOp::kBufs>& bufs, int64_t n_rows,
-                    int64_t row_len, int flags, void* workspace, size_t workspace_bytes,
-                    cudaStream_t stream) {
+                    int64_t row_len, int flags, int64_t active_rows_hint, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream) {
   static_assert(VecOp::kBufs == ElemOp::kBufs, "same optimizer");
   if (n_rows < 0 || row_len < 0) return fail(1, "n_rows and row_len must be >= 0");
   if (n_rows > 0x7fffffffLL) return fail(1, "n_rows must fit in 31 bits");
@@ -424,25 +414,27 @@ inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
                            VecOp::kBufs;
   const bool stream_hint = footprint > 0.75 * static_cast<double>(l2_bytes);
 
-  // Unroll: as deep as possible while every SM still gets several tiles.
+  // Tile depth.  Measured on B200: with one CTA per tile the shallowest tile (one
+  // 16-byte access per thread per buffer) is fastest, because the many short CTAs
+  // de-phase each other's read and write bursts; the element-wise kernel keeps
+  // four scalar accesses per thread in flight.
   int unroll = geo.unroll;
-  if (unroll == 0) {
-    unroll = 4;
-    while (unroll > 1) {
-      const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
-      const int64_t items = n_rows * ((row_len + tile - 1) / tile);
-      if (items >= static_cast<int64_t>(sm_count) * 8) break;
-      unroll >>= 1;
-    }
-  }
+  if (unroll == 0) unroll = vec ? 1 : 4;
   const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
   const int64_t tiles_per_row = (row_len + tile - 1) / tile;
-  const double max_items = static_cast<double>(n_rows) * static_cast<double>(tiles_per_row);
+  // Grid: one CTA per tile of every row that can be active.
+  const int64_t grid_rows = (active_rows_hint >= 0 && active_rows_hint < n_rows)
+                                ? (active_rows_hint > 0 ? active_rows_hint : 1)
+                                : n_rows;
+  const double max_items = static_cast<double>(grid_rows) * static_cast<double>(tiles_per_row);
 
   auto go = [&](auto kernel) -> int {
-    int per_sm = geo.ctas_per_sm > 0 ? geo.ctas_per_sm : resident_ctas(kernel, threads);
-    double want = static_cast<double>(sm_count) * per_sm;
+    // Default: one CTA per (row, tile) work item, sized for the case that every
+    // row is active; CTAs beyond the active work exit at once.  A persistent grid
+    // (geo.ctas_per_sm > 0) strides over the items instead.
+    double want = geo.ctas_per_sm > 0 ? static_cast<double>(sm_count) * geo.ctas_per_sm : max_items;
     if (want > max_items) want = max_items;
+    if (want > 2147483647.0) want = 2147483647.0;  // the kernels stride, so a capped grid still covers
     if (want < 1) want = 1;
     const unsigned grid = static_cast<unsigned>(want);
     cudaError_t e = launch_dependent(kernel, dim3(grid), dim3(threads), stream, bufs, ws, row_len,

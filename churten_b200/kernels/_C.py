@@ -16,6 +16,7 @@ without its CPU sources.
 from __future__ import annotations
 
 import ctypes
+import weakref
 
 import torch
 
@@ -65,23 +66,51 @@ for _name, _schema in SCHEMAS.items():
 # Host wrappers
 # ---------------------------------------------------------------------------
 
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+class _Slot:
+    """Per (device, stream): the prologue's scratch and what is known about the mask.
 
+    The scratch comes from torch's caching allocator so it lives in the same pool
+    as the state it serves; one per stream because two steps on different streams
+    may overlap on the GPU.
 
-def _workspace(device: torch.device, stream_id: int, n_rows: int) -> torch.Tensor:
-    """Scratch for the prologue, one per (device, stream), grown on demand.
-
-    It comes from torch's caching allocator so it lives in the same pool as the
-    state it serves.  Keyed by stream because two steps on different streams may
-    overlap on the GPU.
+    `count` is the number of active rows of the mask identified by `mask_key`, read
+    back from the device WITHOUT a host sync: on the first step after the mask
+    changed, a 4-byte copy of the prologue's counter into pinned memory is queued
+    behind the step; once its event has completed, later steps with the same
+    (unchanged) mask pass the count to the library, which then launches no CTAs
+    for frozen rows.  Until then, and whenever in doubt, the hint is -1.
     """
-    need = _cb.cb200_workspace_bytes(n_rows)
+
+    __slots__ = ("ws", "pinned", "mask_ref", "mask_key", "count", "event")
+
+    def __init__(self):
+        self.ws = None
+        self.pinned = None
+        self.mask_ref = None   # weak reference to the mask tensor the count belongs to
+        self.mask_key = None   # (its version counter, n_rows) when it was counted
+        self.count = None
+        self.event = None
+
+    def same_mask(self, mask: torch.Tensor, key: tuple) -> bool:
+        return self.mask_ref is not None and self.mask_ref() is mask and self.mask_key == key
+
+
+_slots: dict[tuple[int, int], _Slot] = {}
+
+# Below this many elements the step is launch-bound and the read-back is not worth it.
+_HINT_MIN_ELEMENTS = 1 << 24
+
+
+def _slot(device: torch.device, stream_id: int, n_rows: int) -> _Slot:
     key = (device.index, stream_id)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+    slot = _slots.get(key)
+    if slot is None:
+        slot = _slots[key] = _Slot()
+    need = _cb.cb200_workspace_bytes(n_rows)
+    if slot.ws is None or slot.ws.numel() < need:
+        slot.ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
+        slot.mask_ref = slot.mask_key = None
+    return slot
 
 
 def _check_consolidated(params: torch.Tensor, op: str) -> None:
@@ -132,7 +161,7 @@ def _same_layout_args(op: str, params: torch.Tensor, others: list[tuple[str, tor
 
 
 class _Call:
-    """What every wrapper does around the C call: guard, steps, mask, workspace."""
+    """What every wrapper does around the C call: guard, steps, mask, scratch, hint."""
 
     def __init__(self, op: str, params: torch.Tensor, state_steps: torch.Tensor, active_mask: torch.Tensor):
         self.op = op
@@ -150,16 +179,32 @@ class _Call:
             if self.steps.data_ptr() == state_steps.data_ptr():
                 self.steps = self.steps.clone()
         self.mask = _mask(active_mask)
+        # identity of the caller's tensor + its version counter: any in-place write bumps it
+        self.mask_tensor = active_mask
+        self.mask_key = (active_mask._version, self.n_rows)
         self.guard = None
         if torch.cuda.current_device() != self.device.index:
             self.guard = torch.cuda.device(self.device)
+        self.read_back = False
+        self.hint = -1
 
     def __enter__(self):
         if self.guard is not None:
             self.guard.__enter__()
-        stream = torch.cuda.current_stream(self.device)
-        self.stream = stream.cuda_stream
-        self.ws = _workspace(self.device, self.stream, self.n_rows)
+        self.stream = torch._C._cuda_getCurrentRawStream(self.device.index)
+        slot = self.slot = _slot(self.device, self.stream, self.n_rows)
+        self.ws = slot.ws
+        if self.n_rows * self.row_len >= _HINT_MIN_ELEMENTS and not torch.cuda.is_current_stream_capturing():
+            if slot.same_mask(self.mask_tensor, self.mask_key):
+                if slot.count is None and slot.event is not None and slot.event.query():
+                    slot.count = int(slot.pinned[0])
+                    slot.event = None
+                if slot.count is not None:
+                    self.hint = slot.count
+            else:
+                slot.mask_ref = weakref.ref(self.mask_tensor)
+                slot.mask_key, slot.count, slot.event = self.mask_key, None, None
+                self.read_back = True
         return self
 
     def __exit__(self, *exc):
@@ -171,6 +216,13 @@ class _Call:
         _lib.check(status, self.op)
         if self.steps is not self.steps_out:
             self.steps_out.copy_(self.steps)
+        if self.read_back:
+            slot = self.slot
+            if slot.pinned is None:
+                slot.pinned = torch.empty(1, dtype=torch.int32).pin_memory()
+            slot.pinned.copy_(slot.ws[:4].view(torch.int32), non_blocking=True)
+            slot.event = torch.cuda.Event()
+            slot.event.record()
         # Fresh 0-dim tensor aliasing nothing: vmap rejects a function that returns
         # no Tensor (stubs.cpp:20-24).  Its value is unspecified.
         return params.new_empty(())
@@ -201,7 +253,7 @@ def adam_step_cuda(
             call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
             eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(),
             call.n_rows, call.row_len, strides,
-            int(amsgrad), int(maximize), int(decoupled_weight_decay),
+            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params)
@@ -233,7 +285,7 @@ def sgd_step_cuda(
             call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(),
             wd_c.data_ptr(), call.mask.data_ptr(),
             nrows_c.data_ptr() if nrows_c is not None else None,
-            call.n_rows, call.row_len, strides, int(nesterov), int(maximize),
+            call.n_rows, call.row_len, strides, int(nesterov), int(maximize), call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params)
@@ -254,7 +306,7 @@ def adagrad_step_cuda(
             params.data_ptr(), grads.data_ptr(), state_sums.data_ptr(),
             call.steps.data_ptr(), lr_c.data_ptr(), lrd_c.data_ptr(), wd_c.data_ptr(),
             eps_c.data_ptr(), call.mask.data_ptr(),
-            call.n_rows, call.row_len, strides, int(maximize),
+            call.n_rows, call.row_len, strides, int(maximize), call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params)

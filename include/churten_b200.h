@@ -28,6 +28,11 @@
  *    of active rows and one 32-byte record of per-row scalars per active row.
  *    Two calls that may overlap on the GPU (different streams) need two
  *    workspaces.
+ *  - `active_rows_hint` is the number of non-zero entries of `active_mask` if
+ *    the host happens to know it, else -1.  It only sizes the grid (one CTA per
+ *    tile of an active row; without it, of every row, and the CTAs of frozen rows
+ *    exit at once).  A wrong hint costs time, never correctness: the kernels
+ *    stride over whatever work the device-side row list holds.
  *  - `stream` is a `cudaStream_t` passed as `void*` (NULL = legacy default
  *    stream).  Calls are asynchronous: they enqueue two kernels and return;
  *    nothing synchronises with the host.
@@ -83,7 +88,8 @@ int cb200_adam_step(float* params, const float* grads, float* exp_avgs,
                     const float* weight_decay, const uint8_t* active_mask,
                     int64_t n_rows, int64_t row_len, const int64_t* strides,
                     int amsgrad, int maximize, int decoupled_weight_decay,
-                    void* workspace, size_t workspace_bytes, void* stream);
+                    int64_t active_rows_hint, void* workspace,
+                    size_t workspace_bytes, void* stream);
 
 /*
  * Fused SGD step (momentum / dampening / nesterov / maximize / weight decay).
@@ -102,8 +108,8 @@ int cb200_sgd_step(float* params, const float* grads, float* momentum_buffers,
                    const float* dampening, const float* weight_decay,
                    const uint8_t* active_mask, const uint8_t* nesterov_rows,
                    int64_t n_rows, int64_t row_len, const int64_t* strides,
-                   int nesterov, int maximize, void* workspace,
-                   size_t workspace_bytes, void* stream);
+                   int nesterov, int maximize, int64_t active_rows_hint,
+                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Fused Adagrad step; fp32 storage and accumulator, fp64 parameter update.
@@ -117,17 +123,18 @@ int cb200_adagrad_step(float* params, const float* grads, float* state_sums,
                        const float* lr_decay, const float* weight_decay,
                        const float* eps, const uint8_t* active_mask,
                        int64_t n_rows, int64_t row_len, const int64_t* strides,
-                       int maximize, void* workspace, size_t workspace_bytes,
-                       void* stream);
+                       int maximize, int64_t active_rows_hint, void* workspace,
+                       size_t workspace_bytes, void* stream);
 
 /*
  * Launch geometry of the streaming kernels, for benchmarking sweeps.
- * `threads` in {128, 256, 512, 1024}, `unroll` in {1, 2, 4} 16-byte accesses
- * per thread per buffer, `ctas_per_sm` >= 1 (persistent grid = SMs x this,
- * capped by the work available).  0 keeps a field at its default.  Process-wide
- * and not synchronised: set it before launching, not concurrently with a step.
- * No counterpart in the reference (fixed 512-thread blocks over 65536-element
- * chunks, cuda/consolidated.cuh:63-69).
+ * `threads` in {128, 256, 512} (default 256); `unroll` in {1, 2, 4} 16-byte
+ * accesses per thread per buffer per tile (default 1; -1 restores the default);
+ * `ctas_per_sm` > 0 runs a persistent grid of (SM count x ctas_per_sm) CTAs that
+ * stride over the work, -1 restores the default of one CTA per tile.  0 keeps a
+ * field as it is.  Process-wide and not synchronised: set it before launching,
+ * not concurrently with a step.  No counterpart in the reference (fixed
+ * 512-thread blocks over 65536-element chunks, cuda/consolidated.cuh:63-69).
  */
 int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm);
 

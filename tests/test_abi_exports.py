@@ -60,14 +60,14 @@ def test_argument_errors_need_no_gpu():
     lib = _lib.lib()
     # zero rows: nothing to do, no CUDA call is made
     assert lib.cb200_adam_step(None, None, None, None, None, None, None, None, None, None, None,
-                               None, 0, 16, None, 0, 0, 1, None, 0, None) == _lib.OK
+                               None, 0, 16, None, 0, 0, 1, -1, None, 0, None) == _lib.OK
     # amsgrad without its buffer
     rc = lib.cb200_adam_step(None, None, None, None, None, None, None, None, None, None, None,
-                             None, 4, 16, None, 1, 0, 1, None, 0, None)
+                             None, 4, 16, None, 1, 0, 1, -1, None, 0, None)
     assert rc == _lib.ERR_INVALID_ARGUMENT
     assert "max_exp_avg_sqs" in _lib.last_error()
     rc = lib.cb200_sgd_step(None, None, None, None, None, None, None, None, None, None,
-                            4, 16, None, 1, 0, None, 0, None)
+                            4, 16, None, 1, 0, -1, None, 0, None)
     assert rc == _lib.ERR_INVALID_ARGUMENT and "nesterov" in _lib.last_error()
     with pytest.raises(RuntimeError, match="nesterov"):
         _lib.check(rc, "torchstrap::sgd_step_")

@@ -39,7 +39,7 @@ def test_adam_through_ctypes_matches_the_operator(cuda):
     ws = torch.empty(lib.cb200_workspace_bytes(R), dtype=torch.uint8, device=cuda)
     rc = lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
                              _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
-                             0, 0, 1, _ptr(ws), ws.numel(), _stream())
+                             0, 0, 1, -1, _ptr(ws), ws.numel(), _stream())
     assert rc == _lib.OK, _lib.last_error()
     torch.ops.torchstrap.adam_step_(ref[0], ref[1], ref[2], ref[3], None, ref_steps, *side, mask,
                                     amsgrad=False, maximize=False, decoupled_weight_decay=True)
@@ -58,17 +58,17 @@ def test_error_codes(cuda):
     ws = torch.empty(lib.cb200_workspace_bytes(R) + 256, dtype=torch.uint8, device=cuda)
     common = lambda w, wbytes: lib.cb200_adam_step(
         _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
-        *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, w, wbytes, _stream())
+        *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, -1, w, wbytes, _stream())
     assert common(None, 0) == _lib.ERR_WORKSPACE
     assert common(_ptr(ws), 16) == _lib.ERR_WORKSPACE and "too small" in _lib.last_error()
     assert common(ctypes.c_void_p(ws.data_ptr() + 8), ws.numel() - 8) == _lib.ERR_WORKSPACE
     rc = lib.cb200_adam_step(None, _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
-                             *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, _ptr(ws),
+                             *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, -1, _ptr(ws),
                              ws.numel(), _stream())
     assert rc == _lib.ERR_INVALID_ARGUMENT and "params" in _lib.last_error()
     assert lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
                                _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), -1, T, None,
-                               0, 0, 1, _ptr(ws), ws.numel(), _stream()) == _lib.ERR_INVALID_ARGUMENT
+                               0, 0, 1, -1, _ptr(ws), ws.numel(), _stream()) == _lib.ERR_INVALID_ARGUMENT
     torch.cuda.synchronize()
     # a rejected call launches nothing: buffers and clock untouched
     for a, b in zip(bufs, before):
@@ -144,3 +144,64 @@ def test_opcheck(cuda, opt):
     else:
         args = (rnd(), rnd(), rnd().abs(), steps, v(1e-2), v(0.0), v(0.0), v(1e-10), mask)
         torch.library.opcheck(ops.adagrad_step_.default, args, dict(maximize=False), test_utils=tests)
+
+
+@pytest.mark.parametrize("hint", [-1, 0, 1, 3, 6, 1000])
+def test_active_rows_hint_never_changes_results(cuda, hint):
+    """The hint only sizes the grid: too small, too large or absent, the rows that are
+    active on the device are all updated and the others are not."""
+    import churten_b200.kernels  # noqa: F401
+
+    lib = _lib.lib()
+    R, T = 6, 9000
+    bufs, steps, side, _ = _adam_args(R, T, cuda, seed=3)
+    mask = torch.tensor([True, False, True, True, False, True], device=cuda)
+    ref = [b.clone() for b in bufs]
+    ref_steps = steps.clone()
+    ws = torch.empty(lib.cb200_workspace_bytes(R), dtype=torch.uint8, device=cuda)
+    rc = lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+                             _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
+                             0, 0, 1, hint, _ptr(ws), ws.numel(), _stream())
+    assert rc == _lib.OK, _lib.last_error()
+    torch.ops.torchstrap.adam_step_(ref[0], ref[1], ref[2], ref[3], None, ref_steps, *side, mask,
+                                    amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    torch.cuda.synchronize()
+    for a, b in zip(bufs, ref):
+        assert_bits_equal("buffer", a, b)
+    assert torch.equal(steps, ref_steps)
+
+
+def test_hint_follows_mask_changes_through_the_operator(cuda):
+    """The operator learns the active-row count without a host sync and drops it when
+    the mask is written; freezing and thawing rows between steps stays exact."""
+    import churten_b200.kernels._C as C
+
+    R, T = 64, 262144 + 4  # large enough for the read-back to be used
+    gen = torch.Generator(device=cuda).manual_seed(9)
+    p = torch.randn(R, T, device=cuda, generator=gen)
+    g = torch.randn(R, T, device=cuda, generator=gen)
+    buf = torch.zeros_like(p)
+    p_ref, b_ref = p.clone(), buf.clone()
+    steps, ref_steps = torch.zeros(R, device=cuda), torch.zeros(R, device=cuda)
+    v = lambda x: full(R, x, cuda)
+    mask = torch.ones(R, dtype=torch.bool, device=cuda)
+    schedule = [None, None, ("freeze", slice(0, 48)), None, None, ("thaw", slice(0, 16)), None, ("freeze", slice(0, 64)), None,
+                ("thaw", slice(0, 64)), None]
+    for action in schedule:
+        if action is not None:
+            mask[action[1]] = action[0] == "thaw"
+        torch.ops.torchstrap.sgd_step_(p, g, buf, steps, v(1e-2), v(0.9), v(0.0), v(1e-4), mask,
+                                       nesterov=False, maximize=False)
+        torch.cuda.synchronize()  # lets the queued read-back complete, so later steps use the hint
+        active = mask.nonzero().flatten().tolist()
+        for r in active:
+            ref_steps[r] += 1
+            torch._fused_sgd_([p_ref[r]], [g[r].clone()], [b_ref[r]], weight_decay=1e-4, momentum=0.9,
+                              lr=1e-2, dampening=0.0, nesterov=False, maximize=False,
+                              is_first_step=bool(ref_steps[r] == 1), grad_scale=None, found_inf=None)
+    torch.cuda.synchronize()
+    assert_bits_equal("params", p, p_ref)
+    assert_bits_equal("momentum_buffers", buf, b_ref)
+    assert torch.equal(steps, ref_steps)
+    slot = C._slots[(cuda.index or 0, torch.cuda.current_stream().cuda_stream)]
+    assert slot.count == R  # the last mask (everything thawed) was counted on the device

@@ -239,16 +239,15 @@ def test_sgd_vs_torch_optim_fused(ops, cuda, T, momentum, dampening, nesterov, m
 @pytest.mark.parametrize("T", [1024, 333])
 @pytest.mark.parametrize("lr_decay", [0.0, 1e-4])
 @pytest.mark.parametrize("weight_decay", [0.0, 1e-2])
-def test_adagrad_vs_torch_optim_fused(ops, cuda, T, lr_decay, weight_decay):
-    """torch.optim.Adagrad keeps lr/eps/... as doubles on CUDA, so it is handed
-    fp32-representable values (the vectors of the consolidated op are fp32)."""
+def test_adagrad_multi_replica_vs_aten(ops, cuda, T, lr_decay, weight_decay):
+    """torch 2.11 does not offer `torch.optim.Adagrad(fused=True)` on CUDA (its class
+    lists no CUDA support), so the replicas are replayed with torch._fused_adagrad_,
+    the kernel that class would call.  Hyper-parameters are fp32-representable
+    because that kernel keeps them as doubles."""
     gen = _gen(cuda, 5)
     p = torch.randn(R, T, device=cuda, generator=gen) * 0.02
-    refs = [torch.nn.Parameter(p[r].clone()) for r in range(R)]
-    opts = [torch.optim.Adagrad([refs[r]], lr=f32(LRS[r]), lr_decay=f32(lr_decay),
-                                weight_decay=f32(weight_decay), eps=f32(1e-10),
-                                initial_accumulator_value=f32(0.1), fused=True) for r in range(R)]
     sums = torch.full_like(p, f32(0.1))
+    refs = [[p[r].clone(), sums[r].clone(), torch.zeros((), device=cuda)] for r in range(R)]
     steps = torch.zeros(R, device=cuda)
     lr = torch.tensor(LRS, device=cuda)
     for it in range(STEPS):
@@ -258,9 +257,13 @@ def test_adagrad_vs_torch_optim_fused(ops, cuda, T, lr_decay, weight_decay):
                           full(R, 1e-10, cuda), mask, maximize=False)
         for r in range(R):
             if mask[r]:
-                refs[r].grad = g[r].clone()
-                opts[r].step()
+                refs[r][2] += 1
+                torch._fused_adagrad_([refs[r][0]], [g[r].clone()], [refs[r][1]], [refs[r][2]],
+                                      lr=lr[r].item(), lr_decay=f32(lr_decay),
+                                      weight_decay=f32(weight_decay), eps=f32(1e-10), maximize=False,
+                                      grad_scale=None, found_inf=None)
     torch.cuda.synchronize()
     for r in range(R):
-        assert_bits_equal(f"params[{r}]", p[r], refs[r].data)
-        assert_bits_equal(f"state_sum[{r}]", sums[r], opts[r].state[refs[r]]["sum"])
+        assert_bits_equal(f"params[{r}]", p[r], refs[r][0])
+        assert_bits_equal(f"state_sum[{r}]", sums[r], refs[r][1])
+    assert steps.tolist() == [6.0, 0.0, 6.0, 3.0, 6.0]
