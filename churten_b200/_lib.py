@@ -52,6 +52,12 @@ SIGNATURES = {
          # n_rows row_len strides maximize active_rows_hint workspace workspace_bytes stream
          c_int64, c_int64, _P, c_int, c_int64, _P, c_size_t, _P],
     ),
+    "cb200_adam_step_static_scratch": (
+        c_int,
+        # the arguments of cb200_adam_step without workspace and workspace_bytes
+        [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_int64, c_int64, _P, c_int, c_int, c_int, c_int64, _P],
+    ),
     "cb200_set_launch_geometry": (c_int, [c_int, c_int, c_int]),
     "cb200_launch_count": (c_int64, []),
 }

@@ -26,7 +26,7 @@ BUILD = CSRC / "build"
 LIB = PKG / "libchurten_b200.so"
 PROBE_LIB = PKG / "libchurten_b200_probe.so"
 
-LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu"]
+LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu"]
 PROBE_SOURCES = ["probe.cu"]
 HEADERS = ["rowmath.cuh", "stream.cuh", "contraction.h", "../../include/churten_b200.h"]
 

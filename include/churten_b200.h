@@ -127,6 +127,33 @@ int cb200_adagrad_step(float* params, const float* grads, float* state_sums,
                        size_t workspace_bytes, void* stream);
 
 /*
+ * The Adam step for callers that may not allocate device memory: same arguments
+ * and same results as cb200_adam_step, but no workspace is passed -- the scratch
+ * is a fixed array inside the library (590,080 bytes that every GPU loading the
+ * library holds until the process exits).  Meant for plugins of hosts that gave
+ * all device memory to their own arenas at start-up, or that forbid allocator
+ * calls at step time because cudaMalloc synchronises the whole device, and for
+ * bindings that are handed nothing but the tensors to update.
+ * It has no counterpart in the reference (whose kernels need no scratch and whose
+ * host side allocates through PyTorch).
+ *  - At most CB200_STATIC_SCRATCH_MAX_ROWS rows; more returns CB200_ERR_WORKSPACE.
+ *  - One array per device, shared by all calls: calls that can overlap on the GPU
+ *    (two streams, two threads) race on it.  Serialise them, or use
+ *    cb200_adam_step with a workspace per stream.
+ *  - The first call on a device looks up the array's device address; make that
+ *    first call before any stream capture on that device.
+ *  - It performs no device allocation or free, directly or through a library.
+ */
+#define CB200_STATIC_SCRATCH_MAX_ROWS 16384
+int cb200_adam_step_static_scratch(
+    float* params, const float* grads, float* exp_avgs, float* exp_avg_sqs,
+    float* max_exp_avg_sqs, float* state_steps, const float* lr,
+    const float* beta1, const float* beta2, const float* eps,
+    const float* weight_decay, const uint8_t* active_mask, int64_t n_rows,
+    int64_t row_len, const int64_t* strides, int amsgrad, int maximize,
+    int decoupled_weight_decay, int64_t active_rows_hint, void* stream);
+
+/*
  * Launch geometry of the streaming kernels, for benchmarking sweeps.
  * `threads` in {128, 256, 512} (default 256); `unroll` in {1, 2, 4} 16-byte
  * accesses per thread per buffer per tile (default 1; -1 restores the default);
