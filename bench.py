@@ -252,6 +252,59 @@ def cpu_reference_rate(w, steps, warmup, sample_rows):
                 active_elements=active)
 
 
+def run_reference_cuda_arm(args, w, world, rank, local_rank):
+    """The reference's own CUDA kernels (oracle/_ref/torchstrap_ref_cuda.so, its cuda/*.cu compiled
+    unmodified for sm_100a) on the same workload: the on-GPU comparator.  Runs in a process that
+    never imports this package's kernels."""
+    import torch
+
+    import oracle
+
+    if rank != 0:
+        return
+    if not oracle.REF_CUDA_LIB.exists():
+        print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref/torchstrap_ref_cuda.so not built"}))
+        return
+    torch.ops.load_library(str(oracle.REF_CUDA_LIB))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    gen = torch.Generator(device=device).manual_seed(5000)
+    n, t = w["rows"], w["row_len"]
+    p = torch.empty(n, t, device=device).normal_(0.0, 0.02, generator=gen)
+    g = torch.empty(n, t, device=device).normal_(0.0, 1e-3, generator=gen)
+    mask = torch.rand(n, device=device, generator=gen) >= w["frozen"]
+    stp = torch.zeros(n, device=device)
+    full = lambda x: torch.full((n,), float(x), device=device)
+    ops = torch.ops.torchstrap
+    if w["opt"] == "adam":
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        mx = torch.zeros_like(p) if w.get("amsgrad") else None
+        lr = torch.exp(torch.empty(n, device=device).uniform_(math.log(1e-5), math.log(1e-3), generator=gen))
+        run = lambda: ops.adam_step_(p, g, m, v, mx, stp, lr, full(0.9), full(0.999), full(1e-8), full(0.01),
+                                     mask, bool(w.get("amsgrad")), False, True)
+    elif w["opt"] == "sgd":
+        buf = torch.zeros_like(p)
+        run = lambda: ops.sgd_step_(p, g, buf, stp, full(1e-2), full(0.9), full(0.0), full(1e-4), mask, False, False)
+    else:
+        sums = torch.full_like(p, 0.1)
+        run = lambda: ops.adagrad_step_(p, g, sums, stp, full(1e-2), full(1e-4), full(0.0), full(1e-10), mask, False)
+    for _ in range(max(args.warmup, 3)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    active = int(mask.sum().item()) * t
+    print(json.dumps({"impl": "reference_cuda", "metric": "param_updates_per_s",
+                      "value": active / (ms * 1e-3), "unit": "param-updates/s", "ms_per_step": ms,
+                      "gbs": active * _bytes_per_elem(w) / (ms * 1e-3) / 1e9, "steps": args.steps,
+                      "config": {"workload": args.workload, "rows_per_gpu": n, "row_len": t}}), flush=True)
+
+
 def cpu_baseline_in_child(args) -> dict:
     """The CPU leg runs in a process of its own: the GPU arm never loads the oracle."""
     cmd = [sys.executable, str(Path(__file__).resolve()), "--impl", "reference", "--steps", "5",
@@ -441,7 +494,10 @@ def run_ours(args, w, world, rank, local_rank):
 # DRAM bytes (read + write) per active element of the dominant kernel, from an ncu
 # capture of a smaller case of the same kernel (profiles/); traffic grows in
 # proportion to the elements processed.
-TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {}
+TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {
+    # profiles/adam_stream_kernel_c5shard_rows64_ncu.md: 3.3503 GB over 121,634,816 elements
+    "adam": 27.54,
+}
 
 
 def main():
@@ -449,7 +505,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--impl", choices=("ours", "reference", "reference_cuda"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5_shard")
     ap.add_argument("--rows", type=int, default=0, help="override replicas per GPU (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -463,6 +519,9 @@ def main():
         w["rows"] = args.rows
     if args.impl == "reference":
         run_reference_arm(args, w, world, rank)
+        return
+    if args.impl == "reference_cuda":
+        run_reference_cuda_arm(args, w, world, rank, local_rank)
         return
     if args.gpus != world and world == 1 and args.gpus > 1:
         sys.exit("launch with torch.distributed.run for --gpus > 1")

@@ -25,6 +25,7 @@ BUILD = CSRC / "build"
 
 LIB = PKG / "libchurten_b200.so"
 PROBE_LIB = PKG / "libchurten_b200_probe.so"
+HBM_PROBE = PKG / "hbm_stream_probe"
 
 LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu"]
 PROBE_SOURCES = ["probe.cu"]
@@ -105,11 +106,27 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, bool]:
     }
 
 
+def build_hbm_probe(force: bool = False) -> bool:
+    """The standalone HBM streaming microbenchmark (a measurement tool, not part of the library)."""
+    src = CSRC / "hbm_stream_probe.cu"
+    if not force and not _stale(HBM_PROBE, [src]):
+        return False
+    cmd = [_nvcc(), "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
+           "-o", str(HBM_PROBE), str(src)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {src.name}:\n{res.stdout}\n{res.stderr}")
+    return True
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/spill info")
+    ap.add_argument("--probe", action="store_true", help="also build churten_b200/hbm_stream_probe")
     args = ap.parse_args()
+    if args.probe:
+        print(f"{HBM_PROBE.name}: {'rebuilt' if build_hbm_probe(args.force) else 'up to date'}")
     for name, rebuilt in build(args.force, args.verbose).items():
         print(f"{name}: {'rebuilt' if rebuilt else 'up to date'}")
 

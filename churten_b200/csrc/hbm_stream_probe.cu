@@ -1,0 +1,262 @@
+// hbm_stream_probe: what a B200 gives a kernel shaped like the optimizer step.
+//
+// A standalone measurement tool (no part of the library links it).  It times
+// fp32 streams of NR buffers read and NW of them written back -- 4/3 is Adam,
+// 5/4 Adam+AMSGrad, 3/2 SGD with momentum and Adagrad, 2/1 plain SGD / copy --
+// with trivial arithmetic, so the numbers are the memory system's, for:
+//
+//   * a persistent grid (SM count x k CTAs striding over the tiles) against one
+//     CTA per tile, and capped grids in between;
+//   * 128-bit (ld.global.v4) against 256-bit (ld.global.v8, sm_100) accesses;
+//   * default caching against streaming (.cs / L2::evict_first) hints;
+//   * pure reads and pure writes, as the ceilings.
+//
+// Build:  python -m churten_b200.csrc.build --probe     Run:  churten_b200/hbm_stream_probe
+// Each buffer is 2 GiB (8-10 GiB on the device in total); every line is the
+// median of 5 launches after 2 warm-ups, timed with CUDA events.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#define CK(x)                                                                              \
+  do {                                                                                     \
+    cudaError_t e_ = (x);                                                                  \
+    if (e_ != cudaSuccess) {                                                               \
+      std::printf("CUDA error %s at line %d\n", cudaGetErrorString(e_), __LINE__);        \
+      std::exit(1);                                                                        \
+    }                                                                                      \
+  } while (0)
+
+struct f8 {
+  float4 a, b;
+};
+
+// MODE 0: default caching, MODE 1: streaming hints.
+template <int MODE>
+__device__ __forceinline__ float4 ld4(const float* p) {
+  if (MODE == 1) return __ldcs(reinterpret_cast<const float4*>(p));
+  return *reinterpret_cast<const float4*>(p);
+}
+template <int MODE>
+__device__ __forceinline__ void st4(float* p, float4 v) {
+  if (MODE == 1) {
+    __stcs(reinterpret_cast<float4*>(p), v);
+  } else {
+    *reinterpret_cast<float4*>(p) = v;
+  }
+}
+template <int MODE>
+__device__ __forceinline__ f8 ld8(const float* p) {
+  f8 v;
+  if (MODE == 1) {
+    asm volatile("ld.global.L1::no_allocate.L2::evict_first.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v.a.x), "=f"(v.a.y), "=f"(v.a.z), "=f"(v.a.w), "=f"(v.b.x), "=f"(v.b.y),
+                   "=f"(v.b.z), "=f"(v.b.w)
+                 : "l"(p));
+  } else {
+    asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v.a.x), "=f"(v.a.y), "=f"(v.a.z), "=f"(v.a.w), "=f"(v.b.x), "=f"(v.b.y),
+                   "=f"(v.b.z), "=f"(v.b.w)
+                 : "l"(p));
+  }
+  return v;
+}
+template <int MODE>
+__device__ __forceinline__ void st8(float* p, const f8& v) {
+  if (MODE == 1) {
+    asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p),
+                 "f"(v.a.x), "f"(v.a.y), "f"(v.a.z), "f"(v.a.w), "f"(v.b.x), "f"(v.b.y), "f"(v.b.z),
+                 "f"(v.b.w)
+                 : "memory");
+  } else {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v.a.x),
+                 "f"(v.a.y), "f"(v.a.z), "f"(v.a.w), "f"(v.b.x), "f"(v.b.y), "f"(v.b.z), "f"(v.b.w)
+                 : "memory");
+  }
+}
+
+struct Ptrs {
+  float* p[5];
+};
+
+// NR reads, NW writes (buffer 0 and the last NW-1), tiles of blockDim*4*U floats, grid-stride.
+template <int NR, int NW, int U, int MODE>
+__global__ void __launch_bounds__(512) stream128(Ptrs bufs, int64_t n, float scale) {
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * 4 * U;
+  const int64_t ntiles = (n + tile - 1) / tile;
+  float acc = 0.f;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int64_t e0 = t * tile + threadIdx.x * 4;
+    float4 x[U][NR];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x * 4;
+      if (e < n) {
+#pragma unroll
+        for (int b = 0; b < NR; ++b) x[u][b] = ld4<MODE>(bufs.p[b] + e);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x * 4;
+      if (e < n) {
+        float4 s = x[u][0];
+#pragma unroll
+        for (int b = 1; b < NR; ++b) {
+          s.x += x[u][b].x * scale;
+          s.y += x[u][b].y * scale;
+          s.z += x[u][b].z * scale;
+          s.w += x[u][b].w * scale;
+        }
+        if (NW == 0) acc += s.x + s.y + s.z + s.w;
+#pragma unroll
+        for (int b = 0; b < NW; ++b) st4<MODE>(bufs.p[b == 0 ? 0 : b + (NR - NW)] + e, s);
+      }
+    }
+  }
+  if (NW == 0 && acc == 123.456f) bufs.p[0][0] = acc;
+}
+
+template <int NR, int NW, int U, int MODE>
+__global__ void __launch_bounds__(512) stream256(Ptrs bufs, int64_t n, float scale) {
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * 8 * U;
+  const int64_t ntiles = (n + tile - 1) / tile;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int64_t e0 = t * tile + threadIdx.x * 8;
+    f8 x[U][NR];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x * 8;
+      if (e < n) {
+#pragma unroll
+        for (int b = 0; b < NR; ++b) x[u][b] = ld8<MODE>(bufs.p[b] + e);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x * 8;
+      if (e < n) {
+        f8 s = x[u][0];
+#pragma unroll
+        for (int b = 1; b < NR; ++b) {
+          s.a.x += x[u][b].a.x * scale;
+          s.a.y += x[u][b].a.y * scale;
+          s.a.z += x[u][b].a.z * scale;
+          s.a.w += x[u][b].a.w * scale;
+          s.b.x += x[u][b].b.x * scale;
+          s.b.y += x[u][b].b.y * scale;
+          s.b.z += x[u][b].b.z * scale;
+          s.b.w += x[u][b].b.w * scale;
+        }
+#pragma unroll
+        for (int b = 0; b < NW; ++b) st8<MODE>(bufs.p[b == 0 ? 0 : b + (NR - NW)] + e, s);
+      }
+    }
+  }
+}
+
+template <int NWB, int U, int MODE>
+__global__ void __launch_bounds__(512) write128(Ptrs bufs, int64_t n, float val) {
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * 4 * U;
+  const int64_t ntiles = (n + tile - 1) / tile;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int64_t e0 = t * tile + threadIdx.x * 4;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x * 4;
+      if (e < n) {
+#pragma unroll
+        for (int b = 0; b < NWB; ++b) st4<MODE>(bufs.p[b] + e, make_float4(val, val, val, val));
+      }
+    }
+  }
+}
+
+template <class F>
+float median_ms(F launch) {
+  cudaEvent_t a, b;
+  CK(cudaEventCreate(&a));
+  CK(cudaEventCreate(&b));
+  launch();
+  launch();
+  CK(cudaDeviceSynchronize());
+  std::vector<float> ts;
+  for (int i = 0; i < 5; ++i) {
+    CK(cudaEventRecord(a));
+    launch();
+    CK(cudaEventRecord(b));
+    CK(cudaEventSynchronize(b));
+    float ms = 0.f;
+    CK(cudaEventElapsedTime(&ms, a, b));
+    ts.push_back(ms);
+  }
+  CK(cudaGetLastError());
+  std::sort(ts.begin(), ts.end());
+  return ts[ts.size() / 2];
+}
+
+int main() {
+  const int64_t n = static_cast<int64_t>(1) << 29;  // 2 GiB per buffer
+  Ptrs d;
+  for (int i = 0; i < 5; ++i) {
+    CK(cudaMalloc(&d.p[i], n * 4));
+    CK(cudaMemset(d.p[i], 0, n * 4));
+  }
+  int sms = 0;
+  CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0));
+  std::printf("# SMs %d, %lld floats per buffer\n", sms, static_cast<long long>(n));
+  std::printf("# kind reads writes bits unroll hints threads grid ms GB/s\n");
+
+// GRID: > 0 = that many CTAs; 0 = one CTA per tile; < 0 = SMs * (-GRID)
+#define GRID_OF(G, THREADS, PER)                                                              \
+  ((G) > 0 ? (G)                                                                              \
+           : (G) < 0 ? sms * -(G)                                                             \
+                     : static_cast<int>((n + static_cast<int64_t>(THREADS) * (PER)-1) /       \
+                                        (static_cast<int64_t>(THREADS) * (PER))))
+#define RUN128(NR, NW, U, MODE, THREADS, G)                                                   \
+  do {                                                                                        \
+    const int grid = GRID_OF(G, THREADS, 4 * (U));                                            \
+    const float ms = median_ms([&] { stream128<NR, NW, U, MODE><<<grid, THREADS>>>(d, n, 0.5f); }); \
+    std::printf("stream %d %d 128 %d %s %d %d %.3f %.0f\n", NR, NW, U, MODE ? "cs" : "-", THREADS, \
+                grid, ms, static_cast<double>(NR + NW) * n * 4 / ms / 1e6);                   \
+  } while (0)
+#define RUN256(NR, NW, U, MODE, THREADS, G)                                                   \
+  do {                                                                                        \
+    const int grid = GRID_OF(G, THREADS, 8 * (U));                                            \
+    const float ms = median_ms([&] { stream256<NR, NW, U, MODE><<<grid, THREADS>>>(d, n, 0.5f); }); \
+    std::printf("stream %d %d 256 %d %s %d %d %.3f %.0f\n", NR, NW, U, MODE ? "cs" : "-", THREADS, \
+                grid, ms, static_cast<double>(NR + NW) * n * 4 / ms / 1e6);                   \
+  } while (0)
+#define RUNW(NWB, U, MODE, THREADS, G)                                                        \
+  do {                                                                                        \
+    const int grid = GRID_OF(G, THREADS, 4 * (U));                                            \
+    const float ms = median_ms([&] { write128<NWB, U, MODE><<<grid, THREADS>>>(d, n, 1.0f); }); \
+    std::printf("write 0 %d 128 %d %s %d %d %.3f %.0f\n", NWB, U, MODE ? "cs" : "-", THREADS, grid, \
+                ms, static_cast<double>(NWB) * n * 4 / ms / 1e6);                             \
+  } while (0)
+
+  // ceilings
+  RUN128(4, 0, 4, 0, 512, -1); RUN128(4, 0, 2, 1, 512, -2); RUN128(1, 0, 4, 0, 512, -2);
+  RUNW(3, 4, 0, 512, -2); RUNW(3, 4, 1, 512, -2); RUNW(1, 4, 0, 512, -2);
+  RUN128(2, 1, 4, 0, 512, -2); RUN128(2, 1, 4, 1, 512, -2); RUN128(2, 1, 1, 1, 256, 0);
+  // Adam shape, persistent grids
+  RUN128(4, 3, 4, 1, 512, -1); RUN128(4, 3, 2, 1, 512, -2); RUN128(4, 3, 1, 1, 512, -4);
+  RUN128(4, 3, 2, 1, 256, -4); RUN128(4, 3, 1, 1, 256, -8); RUN128(4, 3, 1, 1, 128, -16);
+  RUN128(4, 3, 1, 0, 512, -4); RUN128(4, 3, 1, 1, 512, -8);
+  RUN256(4, 3, 1, 1, 512, -2); RUN256(4, 3, 2, 1, 512, -1); RUN256(4, 3, 1, 0, 512, -2);
+  // Adam shape, one CTA per tile and capped grids in between
+  RUN128(4, 3, 1, 1, 256, 0); RUN128(4, 3, 1, 0, 256, 0); RUN128(4, 3, 1, 1, 512, 0);
+  RUN128(4, 3, 2, 1, 256, 0); RUN128(4, 3, 4, 1, 128, 0); RUN128(4, 3, 1, 1, 128, 0);
+  RUN256(4, 3, 1, 1, 256, 0);
+  RUN128(4, 3, 1, 1, 256, 262144); RUN128(4, 3, 1, 1, 256, 131072); RUN128(4, 3, 1, 1, 256, 32768);
+  RUN128(4, 3, 1, 1, 256, 8192);
+  // the other optimizers' shapes
+  RUN128(5, 4, 1, 1, 256, 0); RUN128(5, 4, 2, 1, 512, -2);
+  RUN128(3, 2, 1, 1, 256, 0); RUN128(3, 2, 2, 1, 512, -2);
+  RUN128(2, 1, 1, 1, 256, 0);
+  return 0;
+}
