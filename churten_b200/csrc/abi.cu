@@ -15,7 +15,7 @@ namespace {
 
 thread_local std::string g_last_error;
 
-std::atomic<int> g_threads{256};
+std::atomic<int> g_threads{0};
 std::atomic<int> g_unroll{0};
 std::atomic<int> g_ctas_per_sm{0};
 std::atomic<long long> g_launches{0};
@@ -96,8 +96,8 @@ const char* cb200_last_error(void) { return cb200::g_last_error.c_str(); }
 size_t cb200_workspace_bytes(int64_t n_rows) { return cb200::ws_bytes(n_rows); }
 
 int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm) {
-  if (threads != 0 && threads != 128 && threads != 256 && threads != 512) {
-    return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "threads must be 0, 128, 256 or 512");
+  if (threads != 0 && threads != -1 && threads != 128 && threads != 256 && threads != 512) {
+    return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "threads must be 0, 128, 256, 512 (or -1 for the default)");
   }
   if (unroll != 0 && unroll != 1 && unroll != 2 && unroll != 4 && unroll != -1) {
     return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "unroll must be 0, 1, 2, 4 (or -1 for by-size)");
@@ -105,7 +105,7 @@ int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm) {
   if (ctas_per_sm < -1 || ctas_per_sm > 32) {
     return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "ctas_per_sm must be in [-1, 32]");
   }
-  if (threads) cb200::g_threads.store(threads);
+  if (threads) cb200::g_threads.store(threads < 0 ? 0 : threads);
   if (unroll) cb200::g_unroll.store(unroll < 0 ? 0 : unroll);
   if (ctas_per_sm) cb200::g_ctas_per_sm.store(ctas_per_sm < 0 ? 0 : ctas_per_sm);
   return CB200_OK;

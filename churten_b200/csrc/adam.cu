@@ -21,6 +21,8 @@ template <bool AMSGRAD, bool ADAMW, int FUSE>
 struct AdamOp {
   static constexpr int kBufs = AMSGRAD ? 5 : 4;
   static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;  // grads are read-only
+  static constexpr int kThreads = 256;  // measured best on B200: 6.9 TB/s (4 buffers), 6.7 TB/s with AMSGrad
+  static constexpr int kUnroll = 1;
   using Row = AdamRow;
   using Hyper = AdamHyper;
 

@@ -85,6 +85,8 @@ template <bool AMSGRAD, bool ADAMW, int FUSE>
 struct StaticAdamOp {
   static constexpr int kBufs = AMSGRAD ? 5 : 4;
   static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;
+  static constexpr int kThreads = 256;  // measured best on B200: as cb200_adam_step
+  static constexpr int kUnroll = 1;
   using Row = AdamRow;
   using Hyper = StaticAdamHyper;
 

@@ -13,10 +13,13 @@
 // (1 Mi elements per case; Adam 72 cases, SGD 108 + 18, Adagrad 144 per path).
 // The search left exactly one mask for Adam (3), SGD with a buffer (29: the
 // momentum blend is fma(1 - dampening, g, momentum * buf)) and SGD without (17).
-// For Adagrad it fixed the fp32 accumulator site (fused); the two fp64 sites
-// (weight decay, corrected learning rate) change the fp32 result only when a
-// double rounding falls on a tie, which no case hit: they are set to nvcc's
-// default, fused.  powf(beta, step) matched torch.pow for 1.8 M arguments.
+// For Adagrad it fixed the fp32 accumulator site (fused).  The two fp64 sites
+// (weight decay: double(param) * double(wd) + double(grad); corrected learning
+// rate: 1 + double(step - 1) * double(lr_decay)) cannot be told apart and need not
+// be: every operand of those products is an fp32 value widened to fp64, so the
+// product has at most 48 significant bits and is exact in fp64; the fused and the
+// unfused form then round the same exact sum once and are identical.  They are
+// written fused.  powf(beta, step) matched torch.pow for 1.8 M arguments.
 // *_VEC is used by the 128-bit streaming kernels, *_ELEM by the element-wise
 // kernels (ragged row length, misaligned or strided buffers), mirroring which of
 // its two paths torch itself takes for the same layout.

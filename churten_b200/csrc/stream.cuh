@@ -43,8 +43,8 @@ namespace cb200 {
 // Host-side state shared by the entry points (abi.cu owns the definitions).
 // ---------------------------------------------------------------------------
 struct LaunchGeometry {
-  int threads;      // block size of the streaming kernels
-  int unroll;       // 16-byte accesses per thread per buffer per tile; 0 = by size
+  int threads;      // block size of the streaming kernels; 0 = the optimizer's own default
+  int unroll;       // 16-byte accesses per thread per buffer per tile; 0 = the optimizer's default
   int ctas_per_sm;  // 0: one CTA per tile (default); > 0: persistent grid of SMs x this
 };
 LaunchGeometry geometry();
@@ -407,19 +407,19 @@ inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
   if (row_len == 0) return 0;
 
   const LaunchGeometry geo = geometry();
-  const int threads = geo.threads;
+  const int threads = geo.threads > 0 ? geo.threads : VecOp::kThreads;
   const int64_t per_thread = vec ? 4 : 1;
   // Streaming hints once the step's traffic no longer fits in L2.
   const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) * 4.0 *
                            VecOp::kBufs;
   const bool stream_hint = footprint > 0.75 * static_cast<double>(l2_bytes);
 
-  // Tile depth.  Measured on B200: with one CTA per tile the shallowest tile (one
-  // 16-byte access per thread per buffer) is fastest, because the many short CTAs
-  // de-phase each other's read and write bursts; the element-wise kernel keeps
-  // four scalar accesses per thread in flight.
+  // Tile shape.  Measured on B200: with one CTA per tile a shallow tile is fastest,
+  // because the many short CTAs de-phase each other's read and write bursts.  Each
+  // optimizer names its own best (Op::kThreads x Op::kUnroll 16-byte accesses per
+  // buffer); the element-wise kernel keeps four scalar accesses per thread in flight.
   int unroll = geo.unroll;
-  if (unroll == 0) unroll = vec ? 1 : 4;
+  if (unroll == 0) unroll = vec ? VecOp::kUnroll : 4;
   const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
   const int64_t tiles_per_row = (row_len + tile - 1) / tile;
   // Grid: one CTA per tile of every row that can be active.

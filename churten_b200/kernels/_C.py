@@ -97,6 +97,16 @@ class _Slot:
 
 _slots: dict[tuple[int, int], _Slot] = {}
 
+# Grid-size hint used while a CUDA graph is being captured (no read-back is possible
+# there); None = size the grid for every row.
+_capture_hint: int | None = None
+
+
+def set_capture_hint(active_rows: int | None) -> None:
+    global _capture_hint
+    _capture_hint = None if active_rows is None else int(active_rows)
+
+
 # Below this many elements the step is launch-bound and the read-back is not worth it.
 _HINT_MIN_ELEMENTS = 1 << 24
 
@@ -194,7 +204,9 @@ class _Call:
         self.stream = torch._C._cuda_getCurrentRawStream(self.device.index)
         slot = self.slot = _slot(self.device, self.stream, self.n_rows)
         self.ws = slot.ws
-        if self.n_rows * self.row_len >= _HINT_MIN_ELEMENTS and not torch.cuda.is_current_stream_capturing():
+        if _capture_hint is not None:
+            self.hint = _capture_hint
+        elif self.n_rows * self.row_len >= _HINT_MIN_ELEMENTS and not torch.cuda.is_current_stream_capturing():
             if slot.same_mask(self.mask_tensor, self.mask_key):
                 if slot.count is None and slot.event is not None and slot.event.query():
                     slot.count = int(slot.pinned[0])
