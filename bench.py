@@ -380,10 +380,16 @@ def run_ours(args, w, world, rank, local_rank):
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    update = (lambda: opt.update(state))
+    if args.graph:
+        from churten_b200.graphs import GraphedUpdate
+
+        update = GraphedUpdate(opt, state, active_rows=active_rows)
+
     def step():
         if distributed:
             gather.start(loss)
-        opt.update(state)
+        update()
         if distributed:
             gather.wait()
 
@@ -404,7 +410,7 @@ def run_ours(args, w, world, rank, local_rank):
             if distributed:
                 gather.start(loss)
             starts[i].record(stream)
-            opt.update(state)
+            update()
             stops[i].record(stream)
             if distributed:
                 gather.wait()
@@ -464,7 +470,7 @@ def run_ours(args, w, world, rank, local_rank):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
-                       "row_len": t, "active_rows_rank0": active_rows,
+                       "row_len": t, "active_rows_rank0": active_rows, "cuda_graph": bool(args.graph),
                        "l2": "inputs larger than L2 (no flush needed)"
                              if n_local * t * bpe > 2 * 126e6 else "working set fits in L2: not flushed",
                        "parallelism": f"replica-block x{world}, no collective on the step; "
@@ -509,6 +515,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5_shard")
     ap.add_argument("--rows", type=int, default=0, help="override replicas per GPU (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the step from a CUDA graph (churten_b200.graphs.GraphedUpdate)")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
