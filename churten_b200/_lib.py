@@ -52,6 +52,11 @@ SIGNATURES = {
          # n_rows row_len strides maximize active_rows_hint workspace workspace_bytes stream
          c_int64, c_int64, _P, c_int, c_int64, _P, c_size_t, _P],
     ),
+    "cb200_scatter_rows": (
+        c_int,
+        # dst dst_row_stride dst_row_len n_rows n_parts parts offsets numels row_strides stream
+        [_P, c_int64, c_int64, c_int64, c_int, _P, _P, _P, _P, _P],
+    ),
     "cb200_adam_step_static_scratch": (
         c_int,
         # the arguments of cb200_adam_step without workspace and workspace_bytes

@@ -136,6 +136,8 @@ def _check_consolidated(params: torch.Tensor, op: str) -> None:
 
 def _hyper(t: torch.Tensor, device: torch.device) -> torch.Tensor:
     # cuda/consolidated.cuh:87-89 `to_hyper`: compute dtype + contiguous; no-ops normally.
+    if t.dtype is torch.float32 and t.is_cuda and t.is_contiguous() and t.get_device() == device.index:
+        return t
     if t.dtype is not torch.float32:
         t = t.to(torch.float32)
     if t.device != device:
@@ -154,6 +156,14 @@ def _same_layout_args(op: str, params: torch.Tensor, others: list[tuple[str, tor
     """Pointers and the strides table for the (R, T) buffers."""
     shape = params.shape
     tensors = [("params", params), *others]
+    index = params.get_device()
+    # the usual case: every buffer dense fp32 on the same device with the same shape
+    for _, t in tensors:
+        if not (t.is_contiguous() and t.dtype is torch.float32 and t.shape == shape
+                and t.is_cuda and t.get_device() == index):
+            break
+    else:
+        return None
     dense = True
     for name, t in tensors:
         if t.shape != shape:
@@ -327,6 +337,30 @@ def adagrad_step_cuda(
 _library.impl("adam_step_", adam_step_cuda, "CUDA")
 _library.impl("sgd_step_", lambda *a: sgd_step_cuda(*a), "CUDA")
 _library.impl("adagrad_step_", adagrad_step_cuda, "CUDA")
+
+
+def scatter_rows(dst: torch.Tensor, parts: list[tuple[torch.Tensor, int, int]]) -> None:
+    """Write dense fp32 `(N, ...)` tensors into column windows of the `(N, T)` buffer `dst`.
+
+    `parts` holds `(tensor, first_column, columns)`; one launch per 24 parts
+    (`cb200_scatter_rows`).  The caller has checked dtype, device and density.
+    """
+    k = len(parts)
+    ptrs = (ctypes.c_void_p * k)(*[p[0].data_ptr() for p in parts])
+    offsets = (ctypes.c_int64 * k)(*[p[1] for p in parts])
+    numels = (ctypes.c_int64 * k)(*[p[2] for p in parts])
+    device = dst.device
+    guard = torch.cuda.device(device) if torch.cuda.current_device() != device.index else None
+    if guard is not None:
+        guard.__enter__()
+    try:
+        status = _cb.cb200_scatter_rows(
+            dst.data_ptr(), dst.stride(0), dst.shape[1], dst.shape[0], k, ptrs, offsets, numels,
+            None, torch._C._cuda_getCurrentRawStream(device.index))
+    finally:
+        if guard is not None:
+            guard.__exit__(None, None, None)
+    _lib.check(status, "cb200_scatter_rows")
 
 
 def launch_count() -> int:

@@ -6,7 +6,7 @@ import torch
 
 from churten_b200.kernels.adagrad import adagrad_step_
 from churten_b200.optimizer.grad_transform import GradientTransformation
-from churten_b200.state import State
+from churten_b200.state import State, _as_1d, _as_2d
 
 __all__ = ["Adagrad", "adagrad_step_"]
 
@@ -43,15 +43,15 @@ class Adagrad(metaclass=GradientTransformation):
         opt = state.optimizer_state
         maximize = bool(opt.get("maximize", maximize))
         adagrad_step_(
-            torch.atleast_2d(state.flat_params),
-            torch.atleast_2d(state.flat_grads),
-            torch.atleast_2d(opt["state_sums"]),
-            torch.atleast_1d(opt["state_steps"]),
-            torch.atleast_1d(opt["lr"]),
-            torch.atleast_1d(opt["lr_decay"]),
-            torch.atleast_1d(opt["weight_decay"]),
-            torch.atleast_1d(opt["eps"]),
-            torch.atleast_1d(state.active_mask),
+            _as_2d(state.flat_params),
+            _as_2d(state.flat_grads),
+            _as_2d(opt["state_sums"]),
+            _as_1d(opt["state_steps"]),
+            _as_1d(opt["lr"]),
+            _as_1d(opt["lr_decay"]),
+            _as_1d(opt["weight_decay"]),
+            _as_1d(opt["eps"]),
+            _as_1d(state.active_mask),
             maximize=maximize,
         )
         return state

@@ -6,7 +6,7 @@ import torch
 
 from churten_b200.kernels.adam import adam_step_
 from churten_b200.optimizer.grad_transform import GradientTransformation
-from churten_b200.state import State
+from churten_b200.state import State, _as_1d, _as_2d
 
 __all__ = ["Adam", "adam_step_"]
 
@@ -55,18 +55,18 @@ class Adam(metaclass=GradientTransformation):
         decoupled_weight_decay = bool(opt.get("decoupled_weight_decay", decoupled_weight_decay))
         max_exp_avg_sqs = opt.get("max_exp_avg_sqs")
         adam_step_(
-            torch.atleast_2d(state.flat_params),
-            torch.atleast_2d(state.flat_grads),
-            torch.atleast_2d(opt["exp_avgs"]),
-            torch.atleast_2d(opt["exp_avg_sqs"]),
-            torch.atleast_2d(max_exp_avg_sqs) if max_exp_avg_sqs is not None else None,
-            torch.atleast_1d(opt["state_steps"]),
-            torch.atleast_1d(opt["lr"]),
-            torch.atleast_1d(opt["beta1"]),
-            torch.atleast_1d(opt["beta2"]),
-            torch.atleast_1d(opt["eps"]),
-            torch.atleast_1d(opt["weight_decay"]),
-            torch.atleast_1d(state.active_mask),
+            _as_2d(state.flat_params),
+            _as_2d(state.flat_grads),
+            _as_2d(opt["exp_avgs"]),
+            _as_2d(opt["exp_avg_sqs"]),
+            _as_2d(max_exp_avg_sqs) if max_exp_avg_sqs is not None else None,
+            _as_1d(opt["state_steps"]),
+            _as_1d(opt["lr"]),
+            _as_1d(opt["beta1"]),
+            _as_1d(opt["beta2"]),
+            _as_1d(opt["eps"]),
+            _as_1d(opt["weight_decay"]),
+            _as_1d(state.active_mask),
             amsgrad=amsgrad,
             maximize=maximize,
             decoupled_weight_decay=decoupled_weight_decay,

@@ -6,7 +6,7 @@ import torch
 
 from churten_b200.kernels.sgd import sgd_step_
 from churten_b200.optimizer.grad_transform import GradientTransformation
-from churten_b200.state import State
+from churten_b200.state import State, _as_1d, _as_2d
 
 __all__ = ["SGD", "sgd_step_"]
 
@@ -51,15 +51,15 @@ class SGD(metaclass=GradientTransformation):
         maximize = bool(opt.get("maximize", maximize))
         buffers = opt.get("momentum_buffers")
         sgd_step_(
-            torch.atleast_2d(state.flat_params),
-            torch.atleast_2d(state.flat_grads),
-            torch.atleast_2d(buffers) if buffers is not None else None,
-            torch.atleast_1d(opt["state_steps"]),
-            torch.atleast_1d(opt["lr"]),
-            torch.atleast_1d(opt["momentum"]),
-            torch.atleast_1d(opt["dampening"]),
-            torch.atleast_1d(opt["weight_decay"]),
-            torch.atleast_1d(state.active_mask),
+            _as_2d(state.flat_params),
+            _as_2d(state.flat_grads),
+            _as_2d(buffers) if buffers is not None else None,
+            _as_1d(opt["state_steps"]),
+            _as_1d(opt["lr"]),
+            _as_1d(opt["momentum"]),
+            _as_1d(opt["dampening"]),
+            _as_1d(opt["weight_decay"]),
+            _as_1d(state.active_mask),
             nesterov=nesterov,
             maximize=maximize,
         )

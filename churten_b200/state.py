@@ -36,6 +36,15 @@ from torch.nn import Module, ModuleList
 _CONSOLIDATION_ALIGNMENT = 4
 
 
+def _as_2d(t: torch.Tensor) -> torch.Tensor:
+    """`torch.atleast_2d` without the call when the tensor already has two dims (the usual case)."""
+    return t if t.dim() == 2 else torch.atleast_2d(t)
+
+
+def _as_1d(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dim() == 1 else torch.atleast_1d(t)
+
+
 def _padded_width(raw: int, element_size: int = 4) -> int:
     """Smallest multiple of the alignment that holds `raw` elements (0 stays 0)."""
     align = max(_CONSOLIDATION_ALIGNMENT, 16 // element_size)
@@ -159,12 +168,36 @@ class OptimizerState(Mapping):
 
 
 class _GradViews:
-    """What `State._consolidated_grads` returns: per-name views into `grads`."""
+    """What `State._consolidated_grads` returns: per-name views into `grads`.
 
-    def __init__(self, views: dict[str, torch.Tensor]):
+    `update_` is the gradient scatter of `apply_gradient`.  On a CUDA device, dense
+    fp32 gradients are written by one fused launch of the library
+    (`cb200_scatter_rows`) instead of one `copy_` per parameter tensor; anything
+    else (other dtypes, strided gradients, CPU) takes the per-tensor `copy_`.
+    """
+
+    def __init__(self, views: dict[str, torch.Tensor], grads: torch.Tensor | None = None,
+                 meta: list[tuple] | None = None):
         self._views = views
+        self._grads = grads
+        self._meta = {name: (offset, numel) for name, _, offset, numel in (meta or [])}
 
     def update_(self, grads: Mapping[str, torch.Tensor]) -> "_GradViews":
+        dst = self._grads
+        if dst is not None and dst.is_cuda and dst.dtype is torch.float32 and len(grads) > 1:
+            n = dst.shape[0]
+            fused = {}
+            for name, value in grads.items():
+                off_numel = self._meta.get(name)
+                if (off_numel is not None and value.is_cuda and value.dtype is torch.float32
+                        and value.is_contiguous() and value.shape[0] == n
+                        and value.numel() == n * off_numel[1] and value.device == dst.device):
+                    fused[name] = value
+            if len(fused) > 1:
+                from churten_b200.kernels._C import scatter_rows
+
+                scatter_rows(dst, [(v, *self._meta[k]) for k, v in fused.items()])
+                grads = {k: v for k, v in grads.items() if k not in fused}
         for name, value in grads.items():
             self._views[name].copy_(value)
         return self
@@ -259,7 +292,8 @@ class State:
 
     @property
     def _consolidated_grads(self) -> _GradViews:
-        return _GradViews(consolidated_dict_view(self.grads, self.param_meta))
+        return _GradViews(consolidated_dict_view(self.grads, self.param_meta), self.grads,
+                          self.param_meta)
 
     # -- optimizer state ------------------------------------------------------------
     def like_tensor(self, value: Any = None, per_param: bool = False) -> torch.Tensor:

@@ -127,6 +127,23 @@ int cb200_adagrad_step(float* params, const float* grads, float* state_sums,
                        size_t workspace_bytes, void* stream);
 
 /*
+ * Scatter K per-parameter gradient tensors into the consolidated (n_rows,
+ * dst_row_len) gradient buffer with one launch (per 24 parts).  Part k is an fp32
+ * device matrix of n_rows rows x part_numels[k] columns (row stride
+ * part_row_strides[k], or part_numels[k] if that table is NULL) and lands in
+ * columns [part_offsets[k], part_offsets[k] + part_numels[k]) of every row.  The
+ * four tables are HOST arrays of n_parts entries.  Columns covered by no part
+ * (the alignment pad) are not written.
+ * Replaces the per-parameter `copy_` loop of `state._consolidated_grads.update_`
+ * called by `GradientTransformation.apply_gradient`
+ * (src/torchstrap/state.py:217-226, src/torchstrap/optimizer/grad_transform.py:28-31).
+ */
+int cb200_scatter_rows(float* dst, int64_t dst_row_stride, int64_t dst_row_len,
+                       int64_t n_rows, int n_parts, const float* const* parts,
+                       const int64_t* part_offsets, const int64_t* part_numels,
+                       const int64_t* part_row_strides, void* stream);
+
+/*
  * The Adam step for callers that may not allocate device memory: same arguments
  * and same results as cb200_adam_step, but no workspace is passed -- the scratch
  * is a fixed array inside the library (590,080 bytes that every GPU loading the
