@@ -19,6 +19,7 @@ bench.py may import this package; the shipped package never does.
 from __future__ import annotations
 
 import ctypes
+import os
 import subprocess
 from ctypes import POINTER, Structure, c_float, c_int, c_int64, c_uint, c_void_p
 from pathlib import Path
@@ -39,8 +40,18 @@ class _Mat(Structure):
     _fields_ = [("ptr", c_void_p), ("stride_r", c_int64), ("stride_t", c_int64)]
 
 
-def build(reference_root: str | None = "/root/reference") -> dict[str, bool]:
-    """Compile liboracle.so, and the reference's CPU kernels when its checkout is there."""
+def default_reference_root() -> str:
+    """$REFERENCE_ROOT, else a checkout named `reference` beside this repository."""
+    return os.environ.get("REFERENCE_ROOT", str(HERE.parent.parent / "reference"))
+
+
+def build(reference_root: str | None = "") -> dict[str, bool]:
+    """Compile liboracle.so, and the reference's CPU kernels when its checkout is there.
+
+    `reference_root`: "" = the default location, None = do not build the reference.
+    """
+    if reference_root == "":
+        reference_root = default_reference_root()
     out = {}
     subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
     out["liboracle.so"] = ORACLE_LIB.exists()
