@@ -59,6 +59,12 @@ WORKLOADS = {
                desc="Adagrad lr=1e-2 lr_decay=1e-4 eps=1e-10 acc0=0.1, 256 replicas x 4,194,304"),
 }
 BYTES_PER_ELEM = {"adam": 28, "adam_amsgrad": 36, "sgd": 20, "adagrad": 20}
+# per-replica tensor lists of the two model configs (row length = their sum, padded to 4)
+MLP_SHAPES = [(512, 128), (512,), (384, 512), (384,), (4, 384), (4,)]
+CNN_SHAPES = [(32, 3, 3, 3), (32,), (64, 32, 3, 3), (64,), (128, 64, 3, 3), (128,), (512, 2048), (512,),
+              (10, 512), (10,)]
+for _name, _shapes in (("c1", MLP_SHAPES), ("c2", MLP_SHAPES), ("c3", CNN_SHAPES)):
+    WORKLOADS[_name]["shapes"] = _shapes
 
 
 def _bytes_per_elem(w) -> int:
@@ -189,8 +195,16 @@ def build_state(w, n_rows, device, seed):
     t = w["row_len"]
     params = torch.empty(n_rows, t, device=device).normal_(0.0, 0.02, generator=gen)
     grads = torch.empty(n_rows, t, device=device).normal_(0.0, 1e-3, generator=gen)
+    meta, offset = [], 0
+    for i, shape in enumerate(w.get("shapes", [(t,)])):
+        numel = math.prod(shape)
+        meta.append((f"p{i}", torch.Size((n_rows, *shape)), offset, numel))
+        offset += numel
+    assert offset <= t < offset + 4, (offset, t)
+    params[:, offset:] = 0  # alignment pad
+    grads[:, offset:] = 0
     state = State(params=params, buffers=torch.empty(n_rows, 0, device=device),
-                  param_meta=[("flat", params.shape, 0, t)], buffer_meta=[], grads=grads)
+                  param_meta=meta, buffer_meta=[], grads=grads)
     cls = {"adam": opts.Adam, "sgd": opts.SGD, "adagrad": opts.Adagrad}[w["opt"]]
     cls.init(state, **_hyper(w, n_rows, gen, device))
     if w["frozen"] > 0:
@@ -381,6 +395,13 @@ def run_ours(args, w, world, rank, local_rank):
         torch.cuda.synchronize(device)
 
     update = (lambda: opt.update(state))
+    if args.apply_gradient:
+        # the whole `apply_gradient`: per-parameter gradient tensors (what vmap(grad) returns)
+        # are scattered into the consolidated buffer, then the fused step runs
+        part_grads = {name: state.grads[:, off:off + numel].reshape(shape).contiguous()
+                      for name, shape, off, numel in state.param_meta}
+        update = (lambda: opt.apply_gradient(state, part_grads))
+        bpe += 8
     if args.graph:
         from churten_b200.graphs import GraphedUpdate
 
@@ -471,6 +492,7 @@ def run_ours(args, w, world, rank, local_rank):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
                        "row_len": t, "active_rows_rank0": active_rows, "cuda_graph": bool(args.graph),
+                       "apply_gradient": bool(args.apply_gradient),
                        "l2": "inputs larger than L2 (no flush needed)"
                              if n_local * t * bpe > 2 * 126e6 else "working set fits in L2: not flushed",
                        "parallelism": f"replica-block x{world}, no collective on the step; "
@@ -515,6 +537,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5_shard")
     ap.add_argument("--rows", type=int, default=0, help="override replicas per GPU (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--apply-gradient", action="store_true",
+                    help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
     ap.add_argument("--graph", action="store_true",
                     help="replay the step from a CUDA graph (churten_b200.graphs.GraphedUpdate)")
     args = ap.parse_args()

@@ -1,0 +1,118 @@
+"""Device-resident early stopping: freeze replicas whose score stops improving.
+
+The reference's `EarlyStopping` (src/torchstrap/callbacks/training.py:221-347)
+pulls the `(N,)` score and the mask to the host every epoch, decides there, and
+writes `state.active_mask[idx] = False` back.  This one keeps every counter on
+the score's device and updates `state.active_mask` in place with a handful of
+`(N,)` tensor ops, so an epoch boundary costs no host synchronisation unless the
+caller asks for the Python `bool` — and, on several GPUs, each rank runs it over
+its own block of replicas with its slice of the all-gathered score
+(`churten_b200.sharded.MetricGather`), agreeing on "everyone has stopped" with one
+1-element all-reduce.
+
+Decision rule, replica by replica, identical to the reference's:
+
+    improved   = active and (score < threshold)            ( > if higher is better)
+    misses     = 0 if improved else misses + 1             (active replicas only)
+    threshold  = score - (t * score  if improved else 0)   (mode "rel";  t if "abs")
+                 [+ instead of - if higher is better]      (active replicas only)
+    freeze       active replicas whose misses reached `patience`
+    done       = no replica is active any more
+
+Frozen replicas keep their counters and thresholds.  `best_epoch_` records the
+last epoch a replica improved.  Snapshots of best weights (the reference's
+`track_best`) are not part of this class.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class StopFlag:
+    """Result of one early-stopping call: a 0-dim bool tensor on the device.
+
+    `bool(flag)` synchronises (like the reference's return value); `flag.tensor`
+    does not, for callers that poll it later or combine it on the device.
+    """
+
+    def __init__(self, tensor: torch.Tensor):
+        self.tensor = tensor
+
+    def __bool__(self) -> bool:
+        return bool(self.tensor.item())
+
+    def __repr__(self) -> str:
+        return f"StopFlag({self.tensor!r})"
+
+
+class EarlyStopping:
+    def __init__(
+        self,
+        patience: int = 5,
+        threshold: float = 1e-4,
+        threshold_mode: str = "rel",
+        lower_is_better: bool = True,
+        group=None,
+    ):
+        if threshold_mode not in ("rel", "abs"):
+            raise ValueError(f"Invalid threshold mode: '{threshold_mode}'")
+        self.patience = int(patience)
+        self.threshold = float(threshold)
+        self.threshold_mode = threshold_mode
+        self.lower_is_better = bool(lower_is_better)
+        self.group = group
+        self.misses_: torch.Tensor | None = None
+        self.dynamic_threshold_: torch.Tensor | None = None
+        self.best_epoch_: torch.Tensor | None = None
+        self._epoch = 0
+
+    def _init(self, n: int, device: torch.device) -> None:
+        worst = float("inf") if self.lower_is_better else float("-inf")
+        self.misses_ = torch.zeros(n, dtype=torch.int32, device=device)
+        self.dynamic_threshold_ = torch.full((n,), worst, dtype=torch.float32, device=device)
+        self.best_epoch_ = torch.zeros(n, dtype=torch.int32, device=device)
+
+    @torch.no_grad()
+    def __call__(self, state, score: torch.Tensor) -> StopFlag:
+        """Update the counters from this epoch's `(N_local,)` score and freeze in place."""
+        mask = state.active_mask
+        score = torch.as_tensor(score).detach().to(device=mask.device, dtype=torch.float32).reshape(-1)
+        if score.shape[0] != mask.shape[0]:
+            raise ValueError(f"score has {score.shape[0]} entries, the state {mask.shape[0]} replicas")
+        if self.misses_ is None:
+            self._init(score.shape[0], mask.device)
+        active = mask.reshape(-1)
+        threshold = self.dynamic_threshold_
+        beats = score < threshold if self.lower_is_better else score > threshold
+        improved = beats & active
+
+        bumped = torch.where(improved, torch.zeros_like(self.misses_), self.misses_ + 1)
+        self.misses_ = torch.where(active, bumped, self.misses_)
+
+        margin = self.threshold * score if self.threshold_mode == "rel" else torch.full_like(score, self.threshold)
+        margin = torch.where(improved, margin, torch.zeros_like(score))
+        moved = score - margin if self.lower_is_better else score + margin
+        self.dynamic_threshold_ = torch.where(active, moved, threshold)
+        self.best_epoch_ = torch.where(improved, torch.full_like(self.best_epoch_, self._epoch), self.best_epoch_)
+
+        newly_stopped = (self.misses_ >= self.patience) & active
+        remaining = active & ~newly_stopped
+        mask.copy_(remaining.reshape(mask.shape))  # in place: the optimizer step reads this tensor
+        self._epoch += 1
+
+        done = ~remaining.any()
+        if self.group is not None or (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+            # every rank must have run out of active replicas
+            flag = done.to(torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            done = flag.to(torch.bool)
+        return StopFlag(done)
+
+    def rearm(self, state) -> None:
+        """Thaw every replica and forget the counters (the reference re-arms with
+        `active_mask.fill_(True)`)."""
+        state.active_mask.fill_(True)
+        self.misses_ = self.dynamic_threshold_ = self.best_epoch_ = None
+        self._epoch = 0

@@ -69,6 +69,19 @@ def _worker(rank, world, port, n_rows, result_dir):
         mask = torch.ones(b - a, dtype=torch.bool)
         mask[stop[a:b]] = False
         torch.save({"bounds": (a, b), "mask": mask, "stop": stop}, f"{result_dir}/rank{rank}.pt")
+        # early stopping over the local block; "done" only when every rank is done
+        from churten_b200.freeze import EarlyStopping
+
+        class _S:
+            active_mask = torch.ones(b - a, dtype=torch.bool)
+
+        early = EarlyStopping(patience=1, threshold=0.0, threshold_mode="abs")
+        first = early(_S, torch.ones(b - a))
+        # rank 0's replicas stall at once, rank 1's keep improving for one more epoch
+        second = early(_S, torch.full((b - a,), 2.0 if rank == 0 else 0.5))
+        third = early(_S, torch.full((b - a,), 2.0))
+        assert (bool(first), bool(second), bool(third)) == (False, False, True), rank
+        assert not _S.active_mask.any()
         # an inconsistent map is caught on every rank
         bad = ShardSpec(n_rows + (1 if rank == 1 else 0), world, rank)
         try:
