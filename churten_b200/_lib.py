@@ -7,12 +7,14 @@ been built, importing this module raises with the command that builds it.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_double, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libchurten_b200.so"
 PROBE_LIB_PATH = _PKG / "libchurten_b200_probe.so"
+
+F32, F64, F16, BF16 = 0, 1, 2, 3  # enum cb200_dtype
 
 OK = 0
 ERR_INVALID_ARGUMENT = 1
@@ -28,29 +30,32 @@ SIGNATURES = {
     "cb200_workspace_bytes": (c_size_t, [c_int64]),
     "cb200_adam_step": (
         c_int,
-        # params grads exp_avgs exp_avg_sqs max_exp_avg_sqs state_steps
-        [_P, _P, _P, _P, _P, _P,
+        # dtype params grads exp_avgs exp_avg_sqs max_exp_avg_sqs state_steps
+        [c_int, _P, _P, _P, _P, _P, _P,
          # lr beta1 beta2 eps weight_decay active_mask
          _P, _P, _P, _P, _P, _P,
-         # n_rows row_len strides amsgrad maximize decoupled active_rows_hint
-         c_int64, c_int64, _P, c_int, c_int, c_int, c_int64,
+         # n_rows row_len strides amsgrad maximize decoupled steps_already_bumped active_rows_hint
+         c_int64, c_int64, _P, c_int, c_int, c_int, c_int, c_int64,
          # workspace workspace_bytes stream
          _P, c_size_t, _P],
     ),
     "cb200_sgd_step": (
         c_int,
-        # params grads momentum_buffers state_steps lr momentum dampening weight_decay
-        [_P, _P, _P, _P, _P, _P, _P, _P,
-         # active_mask nesterov_rows n_rows row_len strides nesterov maximize active_rows_hint
-         _P, _P, c_int64, c_int64, _P, c_int, c_int, c_int64,
-         _P, c_size_t, _P],
+        # dtype params grads momentum_buffers state_steps lr momentum dampening weight_decay
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+         # active_mask nesterov_rows n_rows row_len strides nesterov maximize
+         _P, _P, c_int64, c_int64, _P, c_int, c_int,
+         # steps_already_bumped active_rows_hint workspace workspace_bytes stream
+         c_int, c_int64, _P, c_size_t, _P],
     ),
     "cb200_adagrad_step": (
         c_int,
-        # params grads state_sums state_steps lr lr_decay weight_decay eps active_mask
-        [_P, _P, _P, _P, _P, _P, _P, _P, _P,
-         # n_rows row_len strides maximize active_rows_hint workspace workspace_bytes stream
-         c_int64, c_int64, _P, c_int, c_int64, _P, c_size_t, _P],
+        # dtype params grads state_sums state_steps lr lr_decay weight_decay eps active_mask
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+         # n_rows row_len strides maximize steps_already_bumped active_rows_hint
+         c_int64, c_int64, _P, c_int, c_int, c_int64,
+         # workspace workspace_bytes stream
+         _P, c_size_t, _P],
     ),
     "cb200_scatter_rows": (
         c_int,
@@ -70,17 +75,20 @@ SIGNATURES = {
 PROBE_SIGNATURES = {
     "cb200_probe_adam": (
         c_int,
-        [c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int64,
-         c_float, c_float, c_float, c_float, c_float, c_float, _P],
+        # dtype fuse amsgrad adamw maximize p g m v mx n lr beta1 beta2 eps wd step stream
+        [c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int64,
+         c_double, c_double, c_double, c_double, c_double, c_double, _P],
     ),
     "cb200_probe_sgd": (
         c_int,
-        [c_int, c_int, c_int, c_int, _P, _P, _P, c_int64,
-         c_float, c_float, c_float, c_float, c_float, _P],
+        # dtype fuse has_buf maximize nesterov p g buf n lr momentum dampening wd step stream
+        [c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int64,
+         c_double, c_double, c_double, c_double, c_double, _P],
     ),
     "cb200_probe_adagrad": (
         c_int,
-        [c_int, c_int, _P, _P, _P, c_int64, c_float, c_float, c_float, c_float, c_float, _P],
+        # dtype fuse maximize p g sum n lr lr_decay wd eps step stream
+        [c_int, c_int, c_int, _P, _P, _P, c_int64, c_double, c_double, c_double, c_double, c_double, _P],
     ),
     "cb200_probe_powf": (c_int, [_P, _P, _P, c_int64, _P]),
 }

@@ -93,7 +93,8 @@ int cb200_version(void) { return 100; }
 
 const char* cb200_last_error(void) { return cb200::g_last_error.c_str(); }
 
-size_t cb200_workspace_bytes(int64_t n_rows) { return cb200::ws_bytes(n_rows); }
+// Sized for the 64-byte row records of fp64 storage; the other storage types use half of it.
+size_t cb200_workspace_bytes(int64_t n_rows) { return cb200::ws_bytes(n_rows, cb200::kMaxRecordBytes); }
 
 int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm) {
   if (threads != 0 && threads != -1 && threads != 128 && threads != 256 && threads != 512) {

@@ -1,5 +1,5 @@
-// cb200_adagrad_step: fused Adagrad over consolidated (N, T) buffers; fp32
-// storage and accumulator, fp64 parameter update.
+// cb200_adagrad_step: fused Adagrad over consolidated (N, T) buffers; the
+// accumulator lives in the math type, the parameter update is done in fp64.
 // Behaviour follows adagrad_step_cuda / adagrad_step_kernel of the reference
 // (src/torchstrap/kernels/csrc/cuda/adagrad.cu:238-283, :69-198).
 #include "../../include/churten_b200.h"
@@ -9,53 +9,106 @@
 namespace cb200 {
 namespace {
 
+template <class M>
 struct AdagradHyper {
-  const float* lr;
-  const float* lr_decay;
-  const float* weight_decay;
-  const float* eps;
+  const M* lr;
+  const M* lr_decay;
+  const M* weight_decay;
+  const M* eps;
 };
 
 // Buffer order: params, grads, state_sums.
-template <int FUSE>
+template <class T, int FUSE>
 struct AdagradOp {
+  using Storage = T;
+  using Math = typename Pack<T>::Math;
   static constexpr int kBufs = 3;
   static constexpr unsigned kWriteMask = 0x5u;
   static constexpr int kThreads = 128;  // measured best on B200: the fp64 divide makes this one latency-sensitive: 6.2 TB/s against 5.2 for 256 x 1
   static constexpr int kUnroll = 2;
   using Row = AdagradRow;
-  using Hyper = AdagradHyper;
+  using Hyper = AdagradHyper<Math>;
 
-  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, float step) {
-    return adagrad_row<FUSE>(h.lr[r], h.lr_decay[r], h.weight_decay[r], h.eps[r], step);
+  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, Math step) {
+    return adagrad_row<FUSE>(static_cast<double>(h.lr[r]), static_cast<double>(h.lr_decay[r]),
+                             static_cast<double>(h.weight_decay[r]), static_cast<double>(h.eps[r]),
+                             static_cast<float>(step));
   }
-  __device__ static __forceinline__ void apply(float (&x)[kBufs], const Row& c, int flags) {
-    adagrad_elem<FUSE>(x[0], x[1], x[2], c, (flags & 1) != 0);
+  __device__ static __forceinline__ void apply(Math (&x)[kBufs], const Row& c, int flags) {
+    adagrad_elem<FUSE, Math>(x[0], x[1], x[2], c, (flags & 1) != 0);
   }
 };
+
+struct AdagradArgs {
+  void* ptrs[3];
+  void* state_steps;
+  const void* lr;
+  const void* lr_decay;
+  const void* weight_decay;
+  const void* eps;
+  const uint8_t* mask;
+  int64_t n_rows, row_len;
+  const int64_t* strides;
+  int flags, bump;
+  int64_t hint;
+  void* workspace;
+  size_t workspace_bytes;
+  cudaStream_t stream;
+};
+
+template <class T>
+int adagrad_run(const AdagradArgs& a) {
+  using VecOp = AdagradOp<T, Fuse<T>::kAdagradVec>;
+  using ElemOp = AdagradOp<T, Fuse<T>::kAdagradElem>;
+  using M = typename VecOp::Math;
+  static const char* const names[3] = {"params", "grads", "state_sums"};
+  Bufs<3> bufs;
+  if (int rc = fill_bufs(&bufs, a.ptrs, a.strides, a.n_rows, a.row_len, names)) return rc;
+  const AdagradHyper<M> hyper{static_cast<const M*>(a.lr), static_cast<const M*>(a.lr_decay),
+                              static_cast<const M*>(a.weight_decay), static_cast<const M*>(a.eps)};
+  return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
+                                 a.row_len, a.flags, a.bump, a.hint, a.workspace,
+                                 a.workspace_bytes, a.stream);
+}
 
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_adagrad_step(float* params, const float* grads, float* state_sums,
-                                  float* state_steps, const float* lr, const float* lr_decay,
-                                  const float* weight_decay, const float* eps,
+extern "C" int cb200_adagrad_step(int dtype, void* params, const void* grads, void* state_sums,
+                                  void* state_steps, const void* lr, const void* lr_decay,
+                                  const void* weight_decay, const void* eps,
                                   const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
-                                  const int64_t* strides, int maximize,
+                                  const int64_t* strides, int maximize, int steps_already_bumped,
                                   int64_t active_rows_hint, void* workspace,
                                   size_t workspace_bytes, void* stream) {
   using namespace cb200;
   if (n_rows > 0 && (!lr || !lr_decay || !weight_decay || !eps)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }
-  const AdagradHyper hyper{lr, lr_decay, weight_decay, eps};
-  static const char* const names[3] = {"params", "grads", "state_sums"};
-  float* ptrs[3] = {params, const_cast<float*>(grads), state_sums};
-  using VecOp = AdagradOp<kAdagradFuseVec>;
-  using ElemOp = AdagradOp<kAdagradFuseElem>;
-  Bufs<3> bufs;
-  if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
-  return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len,
-                                 maximize ? 1 : 0, active_rows_hint, workspace, workspace_bytes,
-                                 static_cast<cudaStream_t>(stream));
+  AdagradArgs a;
+  a.ptrs[0] = params;
+  a.ptrs[1] = const_cast<void*>(grads);
+  a.ptrs[2] = state_sums;
+  a.state_steps = state_steps;
+  a.lr = lr;
+  a.lr_decay = lr_decay;
+  a.weight_decay = weight_decay;
+  a.eps = eps;
+  a.mask = active_mask;
+  a.n_rows = n_rows;
+  a.row_len = row_len;
+  a.strides = strides;
+  a.flags = maximize ? 1 : 0;
+  a.bump = steps_already_bumped ? 0 : 1;
+  a.hint = active_rows_hint;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case kF32: return adagrad_run<float>(a);
+    case kF64: return adagrad_run<double>(a);
+    case kF16: return adagrad_run<__half>(a);
+    case kBF16: return adagrad_run<__nv_bfloat16>(a);
+    default: return fail(CB200_ERR_INVALID_ARGUMENT, "dtype must be CB200_F32, _F64, _F16 or _BF16");
+  }
 }

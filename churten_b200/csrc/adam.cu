@@ -1,6 +1,7 @@
 // cb200_adam_step: fused Adam / AdamW (+AMSGrad) over consolidated (N, T) buffers.
 // Behaviour follows adam_step_cuda / adam_step_kernel of the reference
-// (src/torchstrap/kernels/csrc/cuda/adam.cu:250-331, :70-205).
+// (src/torchstrap/kernels/csrc/cuda/adam.cu:250-331, :70-205), for the four
+// storage types it dispatches (:302-303).
 #include "../../include/churten_b200.h"
 #include "contraction.h"
 #include "stream.cuh"
@@ -8,61 +9,91 @@
 namespace cb200 {
 namespace {
 
+template <class M>
 struct AdamHyper {
-  const float* lr;
-  const float* beta1;
-  const float* beta2;
-  const float* eps;
-  const float* weight_decay;
+  const M* lr;
+  const M* beta1;
+  const M* beta2;
+  const M* eps;
+  const M* weight_decay;
 };
 
 // Buffer order: params, grads, exp_avgs, exp_avg_sqs, [max_exp_avg_sqs].
-template <bool AMSGRAD, bool ADAMW, int FUSE>
+template <class T, bool AMSGRAD, bool ADAMW, int FUSE>
 struct AdamOp {
+  using Storage = T;
+  using Math = typename Pack<T>::Math;
   static constexpr int kBufs = AMSGRAD ? 5 : 4;
   static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;  // grads are read-only
   static constexpr int kThreads = 256;  // measured best on B200: 6.9 TB/s (4 buffers), 6.7 TB/s with AMSGrad
   static constexpr int kUnroll = 1;
-  using Row = AdamRow;
-  using Hyper = AdamHyper;
+  using Row = AdamRowT<Math>;
+  using Hyper = AdamHyper<Math>;
 
-  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, float step) {
-    return adam_row(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
+  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, Math step) {
+    return adam_row<Math>(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
   }
-  __device__ static __forceinline__ void apply(float (&x)[kBufs], const Row& c, int flags) {
-    float mx = 0.0f;
+  __device__ static __forceinline__ void apply(Math (&x)[kBufs], const Row& c, int flags) {
+    Math mx = Math(0);
     if constexpr (AMSGRAD) mx = x[4];
-    adam_elem<AMSGRAD, ADAMW, FUSE>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
+    adam_elem<AMSGRAD, ADAMW, FUSE, Math>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
     if constexpr (AMSGRAD) x[4] = mx;
   }
 };
 
-template <bool AMSGRAD, bool ADAMW>
-int adam_dispatch(const AdamHyper& hyper, float* state_steps, const uint8_t* mask,
-                  float* const* ptrs, const int64_t* strides, int64_t n_rows, int64_t row_len,
-                  int flags, int64_t hint, void* workspace, size_t workspace_bytes,
-                  cudaStream_t stream) {
-  using VecOp = AdamOp<AMSGRAD, ADAMW, kAdamFuseVec>;
-  using ElemOp = AdamOp<AMSGRAD, ADAMW, kAdamFuseElem>;
+struct AdamArgs {
+  void* ptrs[5];
+  void* state_steps;
+  const void* lr;
+  const void* beta1;
+  const void* beta2;
+  const void* eps;
+  const void* weight_decay;
+  const uint8_t* mask;
+  int64_t n_rows, row_len;
+  const int64_t* strides;
+  int flags, bump, amsgrad, adamw;
+  int64_t hint;
+  void* workspace;
+  size_t workspace_bytes;
+  cudaStream_t stream;
+};
+
+template <class T, bool AMSGRAD, bool ADAMW>
+int adam_run(const AdamArgs& a) {
+  using VecOp = AdamOp<T, AMSGRAD, ADAMW, Fuse<T>::kAdamVec>;
+  using ElemOp = AdamOp<T, AMSGRAD, ADAMW, Fuse<T>::kAdamElem>;
+  using M = typename VecOp::Math;
   static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs",
                                        "max_exp_avg_sqs"};
   Bufs<VecOp::kBufs> bufs;
-  if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
-  return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags, hint,
-                                 workspace, workspace_bytes, stream);
+  if (int rc = fill_bufs(&bufs, a.ptrs, a.strides, a.n_rows, a.row_len, names)) return rc;
+  const AdamHyper<M> hyper{static_cast<const M*>(a.lr), static_cast<const M*>(a.beta1),
+                           static_cast<const M*>(a.beta2), static_cast<const M*>(a.eps),
+                           static_cast<const M*>(a.weight_decay)};
+  return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
+                                 a.row_len, a.flags, a.bump, a.hint, a.workspace,
+                                 a.workspace_bytes, a.stream);
+}
+
+template <class T>
+int adam_variant(const AdamArgs& a) {
+  if (a.amsgrad) return a.adamw ? adam_run<T, true, true>(a) : adam_run<T, true, false>(a);
+  return a.adamw ? adam_run<T, false, true>(a) : adam_run<T, false, false>(a);
 }
 
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_adam_step(float* params, const float* grads, float* exp_avgs,
-                               float* exp_avg_sqs, float* max_exp_avg_sqs, float* state_steps,
-                               const float* lr, const float* beta1, const float* beta2,
-                               const float* eps, const float* weight_decay,
+extern "C" int cb200_adam_step(int dtype, void* params, const void* grads, void* exp_avgs,
+                               void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps,
+                               const void* lr, const void* beta1, const void* beta2,
+                               const void* eps, const void* weight_decay,
                                const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
                                const int64_t* strides, int amsgrad, int maximize,
-                               int decoupled_weight_decay, int64_t active_rows_hint,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+                               int decoupled_weight_decay, int steps_already_bumped,
+                               int64_t active_rows_hint, void* workspace,
+                               size_t workspace_bytes, void* stream) {
   using namespace cb200;
   // (an empty matrix has no storage, so a NULL there says nothing)
   if (amsgrad && !max_exp_avg_sqs && n_rows > 0 && row_len > 0) {
@@ -71,26 +102,35 @@ extern "C" int cb200_adam_step(float* params, const float* grads, float* exp_avg
   if (n_rows > 0 && (!lr || !beta1 || !beta2 || !eps || !weight_decay)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }
-  const AdamHyper hyper{lr, beta1, beta2, eps, weight_decay};
-  float* ptrs[5] = {params, const_cast<float*>(grads), exp_avgs, exp_avg_sqs, max_exp_avg_sqs};
-  const int flags = maximize ? 1 : 0;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (amsgrad) {
-    if (decoupled_weight_decay) {
-      return adam_dispatch<true, true>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                       row_len, flags, active_rows_hint, workspace,
-                                       workspace_bytes, s);
-    }
-    return adam_dispatch<true, false>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                      row_len, flags, active_rows_hint, workspace,
-                                       workspace_bytes, s);
+  AdamArgs a;
+  a.ptrs[0] = params;
+  a.ptrs[1] = const_cast<void*>(grads);
+  a.ptrs[2] = exp_avgs;
+  a.ptrs[3] = exp_avg_sqs;
+  a.ptrs[4] = max_exp_avg_sqs;
+  a.state_steps = state_steps;
+  a.lr = lr;
+  a.beta1 = beta1;
+  a.beta2 = beta2;
+  a.eps = eps;
+  a.weight_decay = weight_decay;
+  a.mask = active_mask;
+  a.n_rows = n_rows;
+  a.row_len = row_len;
+  a.strides = strides;
+  a.flags = maximize ? 1 : 0;
+  a.bump = steps_already_bumped ? 0 : 1;
+  a.amsgrad = amsgrad;
+  a.adamw = decoupled_weight_decay;
+  a.hint = active_rows_hint;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case kF32: return adam_variant<float>(a);
+    case kF64: return adam_variant<double>(a);
+    case kF16: return adam_variant<__half>(a);
+    case kBF16: return adam_variant<__nv_bfloat16>(a);
+    default: return fail(CB200_ERR_INVALID_ARGUMENT, "dtype must be CB200_F32, _F64, _F16 or _BF16");
   }
-  if (decoupled_weight_decay) {
-    return adam_dispatch<false, true>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                      row_len, flags, active_rows_hint, workspace,
-                                       workspace_bytes, s);
-  }
-  return adam_dispatch<false, false>(hyper, state_steps, active_mask, ptrs, strides, n_rows,
-                                     row_len, flags, active_rows_hint, workspace,
-                                       workspace_bytes, s);
 }

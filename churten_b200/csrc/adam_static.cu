@@ -83,6 +83,8 @@ struct StaticAdamHyper {
 // params, grads, exp_avgs, exp_avg_sqs, [max_exp_avg_sqs]; grads are read-only).
 template <bool AMSGRAD, bool ADAMW, int FUSE>
 struct StaticAdamOp {
+  using Storage = float;
+  using Math = float;
   static constexpr int kBufs = AMSGRAD ? 5 : 4;
   static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;
   static constexpr int kThreads = 256;  // measured best on B200: as cb200_adam_step
@@ -91,28 +93,28 @@ struct StaticAdamOp {
   using Hyper = StaticAdamHyper;
 
   __device__ static __forceinline__ Row make_row(const Hyper& h, int r, float step) {
-    return adam_row(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
+    return adam_row<float>(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
   }
   __device__ static __forceinline__ void apply(float (&x)[kBufs], const Row& c, int flags) {
     float mx = 0.0f;
     if constexpr (AMSGRAD) mx = x[4];
-    adam_elem<AMSGRAD, ADAMW, FUSE>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
+    adam_elem<AMSGRAD, ADAMW, FUSE, float>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
     if constexpr (AMSGRAD) x[4] = mx;
   }
 };
 
 template <bool AMSGRAD, bool ADAMW>
 int static_adam(const StaticAdamHyper& hyper, float* state_steps, const uint8_t* mask,
-                float* const* ptrs, const int64_t* strides, int64_t n_rows, int64_t row_len,
+                void* const* ptrs, const int64_t* strides, int64_t n_rows, int64_t row_len,
                 int flags, int64_t hint, void* scratch, cudaStream_t stream) {
-  using VecOp = StaticAdamOp<AMSGRAD, ADAMW, kAdamFuseVec>;
-  using ElemOp = StaticAdamOp<AMSGRAD, ADAMW, kAdamFuseElem>;
+  using VecOp = StaticAdamOp<AMSGRAD, ADAMW, Fuse<float>::kAdamVec>;
+  using ElemOp = StaticAdamOp<AMSGRAD, ADAMW, Fuse<float>::kAdamElem>;
   static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs",
                                        "max_exp_avg_sqs"};
   Bufs<VecOp::kBufs> bufs;
   if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
-  return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags, hint,
-                                 scratch, kStaticScratchBytes, stream);
+  return run_step<VecOp, ElemOp>(hyper, state_steps, mask, bufs, n_rows, row_len, flags,
+                                 /*bump_steps=*/1, hint, scratch, kStaticScratchBytes, stream);
 }
 
 }  // namespace
@@ -143,7 +145,7 @@ extern "C" int cb200_adam_step_static_scratch(
     if (int rc = static_scratch(&scratch)) return rc;
   }
   const StaticAdamHyper hyper{lr, beta1, beta2, eps, weight_decay};
-  float* ptrs[5] = {params, const_cast<float*>(grads), exp_avgs, exp_avg_sqs, max_exp_avg_sqs};
+  void* ptrs[5] = {params, const_cast<float*>(grads), exp_avgs, exp_avg_sqs, max_exp_avg_sqs};
   const int flags = maximize ? 1 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (amsgrad) {

@@ -33,13 +33,24 @@ def f32(x: float) -> float:
     return torch.tensor(x, dtype=torch.float32).item()
 
 
+DTYPES = {"f32": (torch.float32, _lib.F32), "f16": (torch.float16, _lib.F16),
+          "bf16": (torch.bfloat16, _lib.BF16), "f64": (torch.float64, _lib.F64)}
+_dtype = torch.float32  # storage type of the current sweep
+_code = _lib.F32
+
+
 def _inputs(n: int, seed: int, dev, positive: bool = False) -> torch.Tensor:
     gen = torch.Generator(device=dev).manual_seed(seed)
     x = torch.randn(n, device=dev, generator=gen)
-    # a quarter of the lanes get a wild scale: 2^-60 .. 2^40
-    e = torch.randint(-60, 40, (n,), device=dev, generator=gen).float()
+    # a quarter of the lanes get a wild scale: 2^-60 .. 2^40 (2^-6 .. 2^6 for fp16's range)
+    lo, hi = (-6, 6) if _dtype is torch.float16 else (-60, 40)
+    e = torch.randint(lo, hi, (n,), device=dev, generator=gen).float()
     wild = torch.rand(n, device=dev, generator=gen) < 0.25
     x = torch.where(wild, x * torch.exp2(e), x)
+    if _dtype is torch.float64:
+        # fill the low mantissa bits too, or every product would be exact in fp64
+        x = x.double() * (1.0 + torch.rand(n, device=dev, generator=gen, dtype=torch.float64) * 2.0 ** -20)
+    x = x.to(_dtype)
     return x.abs() if positive else x
 
 
@@ -49,7 +60,14 @@ def _stream() -> int:
 
 def _eq(a: torch.Tensor, b: torch.Tensor) -> bool:
     # bit equality, NaNs included
-    return bool(torch.equal(a.view(torch.int32), b.view(torch.int32)))
+    bits = {2: torch.int16, 4: torch.int32, 8: torch.int64}[a.element_size()]
+    return bool(torch.equal(a.view(bits), b.view(bits)))
+
+
+def _hp(x: float) -> float:
+    """Hyper-parameters reach torch as Python doubles; fp32-representable ones mean the
+    same number to float math and to double math."""
+    return f32(x)
 
 
 def search_adam(n: int, dev) -> dict:
@@ -78,7 +96,7 @@ def search_adam(n: int, dev) -> dict:
             for fuse in range(4):
                 q = [t.clone() if t is not None else None for t in start]
                 rc = probe.cb200_probe_adam(
-                    fuse, int(amsgrad), int(adamw), int(maximize), q[0].data_ptr(), g.data_ptr(),
+                    _code, fuse, int(amsgrad), int(adamw), int(maximize), q[0].data_ptr(), g.data_ptr(),
                     q[1].data_ptr(), q[2].data_ptr(), q[3].data_ptr() if amsgrad else None, n,
                     lr, b1, b2, eps, wd, float(it + 1), _stream())
                 assert rc == 0
@@ -119,7 +137,7 @@ def search_sgd(n: int, dev, has_buf: bool) -> dict:
             for fuse in all_masks:
                 q = [start[0].clone(), start[1].clone() if has_buf else None]
                 rc = probe.cb200_probe_sgd(
-                    fuse, int(has_buf), int(maximize), int(nesterov), q[0].data_ptr(), g.data_ptr(),
+                    _code, fuse, int(has_buf), int(maximize), int(nesterov), q[0].data_ptr(), g.data_ptr(),
                     q[1].data_ptr() if has_buf else None, n, lr, mom, damp, wd, float(it + 1),
                     _stream())
                 assert rc == 0
@@ -159,7 +177,7 @@ def search_adagrad(n: int, dev) -> dict:
             passing = []
             for fuse in range(8):
                 q = [start[0].clone(), start[1].clone()]
-                rc = probe.cb200_probe_adagrad(fuse, int(maximize), q[0].data_ptr(), g.data_ptr(),
+                rc = probe.cb200_probe_adagrad(_code, fuse, int(maximize), q[0].data_ptr(), g.data_ptr(),
                                                q[1].data_ptr(), n, lr, lr_decay, wd, eps,
                                                float(it + 1), _stream())
                 assert rc == 0
@@ -193,17 +211,22 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--n", type=int, default=1 << 20, help="elements per case (vector path)")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--dtypes", default="f32,f16,bf16,f64", help="storage types to sweep")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         sys.exit("contraction_search needs a CUDA device")
     dev = torch.device("cuda")
     report = {"torch": torch.__version__, "cuda": torch.version.cuda,
               "device": torch.cuda.get_device_name(0)}
-    for label, n in (("vec", args.n), ("elem", args.n + 1)):
-        report[f"adam_{label}"] = search_adam(n, dev)
-        report[f"sgd_buf_{label}"] = search_sgd(n, dev, True)
-        report[f"sgd_plain_{label}"] = search_sgd(n, dev, False)
-        report[f"adagrad_{label}"] = search_adagrad(n, dev)
+    global _dtype, _code
+    for name in args.dtypes.split(","):
+        _dtype, _code = DTYPES[name]
+        prefix = "" if name == "f32" else name + "_"
+        for label, n in (("vec", args.n), ("elem", args.n + 1)):
+            report[f"{prefix}adam_{label}"] = search_adam(n, dev)
+            report[f"{prefix}sgd_buf_{label}"] = search_sgd(n, dev, True)
+            report[f"{prefix}sgd_plain_{label}"] = search_sgd(n, dev, False)
+            report[f"{prefix}adagrad_{label}"] = search_adagrad(n, dev)
     report["powf"] = check_powf(dev)
     torch.cuda.synchronize()
     summary = {k: ({"masks": v["masks"], "cases": v["cases"]} if "masks" in v else v)

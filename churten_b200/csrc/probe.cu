@@ -1,57 +1,64 @@
 // libchurten_b200_probe.so: the element math of rowmath.cuh with the fusion mask
-// chosen at RUN time, over one flat row.  contraction_search.py uses it to find,
-// against torch's own fused CUDA kernels, which mask reproduces torch bit for
-// bit; the masks it finds are the constants in contraction.h.  Not used by the
-// step entry points.
+// chosen at RUN time and the storage type chosen by `dtype`, over one flat row.
+// contraction_search.py uses it to find, against torch's own fused CUDA kernels,
+// which mask reproduces torch bit for bit for each storage type; the masks it
+// finds are the constants in contraction.h.  Not used by the step entry points.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "rowmath.cuh"
+#include "stream.cuh"
 
 namespace cb200 {
 namespace {
 
-template <bool AMSGRAD, bool ADAMW, int FUSE>
-__global__ void probe_adam_kernel(float* p, const float* g, float* m, float* v, float* mx,
-                                  int64_t n, float lr, float beta1, float beta2, float eps,
-                                  float wd, float step, bool maximize) {
-  const AdamRow c = adam_row(lr, beta1, beta2, eps, wd, step);
+template <class T, bool AMSGRAD, bool ADAMW, int FUSE>
+__global__ void probe_adam_kernel(T* p, const T* g, T* m, T* v, T* mx, int64_t n, double lr,
+                                  double beta1, double beta2, double eps, double wd, double step,
+                                  bool maximize) {
+  using M = typename Pack<T>::Math;
+  using P = Pack<T>;
+  const AdamRowT<M> c = adam_row<M>(M(lr), M(beta1), M(beta2), M(eps), M(wd), M(step));
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float pp = p[i], mm = m[i], vv = v[i], xx = AMSGRAD ? mx[i] : 0.0f;
-    adam_elem<AMSGRAD, ADAMW, FUSE>(pp, g[i], mm, vv, xx, c, maximize);
-    p[i] = pp;
-    m[i] = mm;
-    v[i] = vv;
-    if (AMSGRAD) mx[i] = xx;
+    M pp = P::to_math(p[i]), mm = P::to_math(m[i]), vv = P::to_math(v[i]);
+    M xx = AMSGRAD ? P::to_math(mx[i]) : M(0);
+    adam_elem<AMSGRAD, ADAMW, FUSE, M>(pp, P::to_math(g[i]), mm, vv, xx, c, maximize);
+    p[i] = P::from_math(pp);
+    m[i] = P::from_math(mm);
+    v[i] = P::from_math(vv);
+    if (AMSGRAD) mx[i] = P::from_math(xx);
   }
 }
 
-template <bool HAS_BUF, int FUSE>
-__global__ void probe_sgd_kernel(float* p, const float* g, float* buf, int64_t n, float lr,
-                                 float momentum, float dampening, float wd, float step,
-                                 bool nesterov, bool maximize) {
-  const SgdRow c = sgd_row(lr, momentum, dampening, wd, step, nesterov);
+template <class T, bool HAS_BUF, int FUSE>
+__global__ void probe_sgd_kernel(T* p, const T* g, T* buf, int64_t n, double lr, double momentum,
+                                 double dampening, double wd, double step, bool nesterov,
+                                 bool maximize) {
+  using M = typename Pack<T>::Math;
+  using P = Pack<T>;
+  const SgdRowT<M> c = sgd_row<M>(M(lr), M(momentum), M(dampening), M(wd), M(step), nesterov);
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float pp = p[i], bb = HAS_BUF ? buf[i] : 0.0f;
-    sgd_elem<HAS_BUF, FUSE>(pp, g[i], bb, c, maximize);
-    p[i] = pp;
-    if (HAS_BUF) buf[i] = bb;
+    M pp = P::to_math(p[i]), bb = HAS_BUF ? P::to_math(buf[i]) : M(0);
+    sgd_elem<HAS_BUF, FUSE, M>(pp, P::to_math(g[i]), bb, c, maximize);
+    p[i] = P::from_math(pp);
+    if (HAS_BUF) buf[i] = P::from_math(bb);
   }
 }
 
-template <int FUSE>
-__global__ void probe_adagrad_kernel(float* p, const float* g, float* sum, int64_t n, float lr,
-                                     float lr_decay, float wd, float eps, float step,
+template <class T, int FUSE>
+__global__ void probe_adagrad_kernel(T* p, const T* g, T* sum, int64_t n, double lr,
+                                     double lr_decay, double wd, double eps, double step,
                                      bool maximize) {
-  const AdagradRow c = adagrad_row<FUSE>(lr, lr_decay, wd, eps, step);
+  using M = typename Pack<T>::Math;
+  using P = Pack<T>;
+  const AdagradRow c = adagrad_row<FUSE>(lr, lr_decay, wd, eps, static_cast<float>(step));
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float pp = p[i], ss = sum[i];
-    adagrad_elem<FUSE>(pp, g[i], ss, c, maximize);
-    p[i] = pp;
-    sum[i] = ss;
+    M pp = P::to_math(p[i]), ss = P::to_math(sum[i]);
+    adagrad_elem<FUSE, M>(pp, P::to_math(g[i]), ss, c, maximize);
+    p[i] = P::from_math(pp);
+    sum[i] = P::from_math(ss);
   }
 }
 
@@ -69,66 +76,78 @@ inline unsigned grid_for(int64_t n) {
   return static_cast<unsigned>(b);
 }
 
-template <int FUSE>
-int adam_fuse(int amsgrad, int adamw, float* p, const float* g, float* m, float* v, float* mx,
-              int64_t n, float lr, float b1, float b2, float eps, float wd, float step,
-              bool maximize, cudaStream_t s) {
-  const unsigned grid = grid_for(n);
-  if (amsgrad && adamw) {
-    probe_adam_kernel<true, true, FUSE><<<grid, 256, 0, s>>>(p, g, m, v, mx, n, lr, b1, b2, eps, wd, step, maximize);
-  } else if (amsgrad) {
-    probe_adam_kernel<true, false, FUSE><<<grid, 256, 0, s>>>(p, g, m, v, mx, n, lr, b1, b2, eps, wd, step, maximize);
-  } else if (adamw) {
-    probe_adam_kernel<false, true, FUSE><<<grid, 256, 0, s>>>(p, g, m, v, mx, n, lr, b1, b2, eps, wd, step, maximize);
+struct AdamProbe {
+  int amsgrad, adamw;
+  void *p, *m, *v, *mx;
+  const void* g;
+  int64_t n;
+  double lr, b1, b2, eps, wd, step;
+  bool maximize;
+  cudaStream_t s;
+};
+
+template <class T, int FUSE>
+int adam_fuse(const AdamProbe& a) {
+  const unsigned grid = grid_for(a.n);
+  T *p = static_cast<T*>(a.p), *m = static_cast<T*>(a.m), *v = static_cast<T*>(a.v),
+    *mx = static_cast<T*>(a.mx);
+  const T* g = static_cast<const T*>(a.g);
+#define CB200_GO(A, W)                                                                          \
+  probe_adam_kernel<T, A, W, FUSE><<<grid, 256, 0, a.s>>>(p, g, m, v, mx, a.n, a.lr, a.b1, a.b2, \
+                                                          a.eps, a.wd, a.step, a.maximize)
+  if (a.amsgrad && a.adamw) {
+    CB200_GO(true, true);
+  } else if (a.amsgrad) {
+    CB200_GO(true, false);
+  } else if (a.adamw) {
+    CB200_GO(false, true);
   } else {
-    probe_adam_kernel<false, false, FUSE><<<grid, 256, 0, s>>>(p, g, m, v, mx, n, lr, b1, b2, eps, wd, step, maximize);
+    CB200_GO(false, false);
   }
+#undef CB200_GO
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
-template <int FUSE>
-int sgd_fuse(int has_buf, float* p, const float* g, float* buf, int64_t n, float lr, float mom,
-             float damp, float wd, float step, bool nesterov, bool maximize, cudaStream_t s) {
-  const unsigned grid = grid_for(n);
-  if (has_buf) {
-    probe_sgd_kernel<true, FUSE><<<grid, 256, 0, s>>>(p, g, buf, n, lr, mom, damp, wd, step, nesterov, maximize);
-  } else {
-    probe_sgd_kernel<false, FUSE><<<grid, 256, 0, s>>>(p, g, buf, n, lr, mom, damp, wd, step, nesterov, maximize);
-  }
-  return cudaGetLastError() == cudaSuccess ? 0 : 3;
-}
-
-
-}  // namespace
-}  // namespace cb200
-
-extern "C" {
-
-// fuse: AdamFuse mask, 0..3.
-int cb200_probe_adam(int fuse, int amsgrad, int adamw, int maximize, float* p, const float* g,
-                     float* m, float* v, float* mx, int64_t n, float lr, float beta1, float beta2,
-                     float eps, float wd, float step, void* stream) {
-  using namespace cb200;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool mz = maximize != 0;
+template <class T>
+int adam_dtype(int fuse, const AdamProbe& a) {
   switch (fuse) {
-    case 0: return adam_fuse<0>(amsgrad, adamw, p, g, m, v, mx, n, lr, beta1, beta2, eps, wd, step, mz, s);
-    case 1: return adam_fuse<1>(amsgrad, adamw, p, g, m, v, mx, n, lr, beta1, beta2, eps, wd, step, mz, s);
-    case 2: return adam_fuse<2>(amsgrad, adamw, p, g, m, v, mx, n, lr, beta1, beta2, eps, wd, step, mz, s);
-    case 3: return adam_fuse<3>(amsgrad, adamw, p, g, m, v, mx, n, lr, beta1, beta2, eps, wd, step, mz, s);
+    case 0: return adam_fuse<T, 0>(a);
+    case 1: return adam_fuse<T, 1>(a);
+    case 2: return adam_fuse<T, 2>(a);
+    case 3: return adam_fuse<T, 3>(a);
     default: return 1;
   }
 }
 
-// fuse: SgdFuse mask, 0..31 with blend field (bits 1-2) in 0..2.
-int cb200_probe_sgd(int fuse, int has_buf, int maximize, int nesterov, float* p, const float* g,
-                    float* buf, int64_t n, float lr, float momentum, float dampening, float wd,
-                    float step, void* stream) {
-  using namespace cb200;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool mz = maximize != 0, nv = nesterov != 0;
+struct SgdProbe {
+  int has_buf;
+  void *p, *buf;
+  const void* g;
+  int64_t n;
+  double lr, mom, damp, wd, step;
+  bool nesterov, maximize;
+  cudaStream_t s;
+};
+
+template <class T, int FUSE>
+int sgd_fuse(const SgdProbe& a) {
+  const unsigned grid = grid_for(a.n);
+  T *p = static_cast<T*>(a.p), *buf = static_cast<T*>(a.buf);
+  const T* g = static_cast<const T*>(a.g);
+  if (a.has_buf) {
+    probe_sgd_kernel<T, true, FUSE><<<grid, 256, 0, a.s>>>(p, g, buf, a.n, a.lr, a.mom, a.damp, a.wd,
+                                                           a.step, a.nesterov, a.maximize);
+  } else {
+    probe_sgd_kernel<T, false, FUSE><<<grid, 256, 0, a.s>>>(p, g, buf, a.n, a.lr, a.mom, a.damp, a.wd,
+                                                            a.step, a.nesterov, a.maximize);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+template <class T>
+int sgd_dtype(int fuse, const SgdProbe& a) {
 #define CB200_CASE(F) \
-  case F: return sgd_fuse<F>(has_buf, p, g, buf, n, lr, momentum, dampening, wd, step, nv, mz, s);
+  case F: return sgd_fuse<T, F>(a);
   switch (fuse) {
     CB200_CASE(0) CB200_CASE(1) CB200_CASE(2) CB200_CASE(3) CB200_CASE(4) CB200_CASE(5)
     CB200_CASE(8) CB200_CASE(9) CB200_CASE(10) CB200_CASE(11) CB200_CASE(12) CB200_CASE(13)
@@ -139,16 +158,24 @@ int cb200_probe_sgd(int fuse, int has_buf, int maximize, int nesterov, float* p,
 #undef CB200_CASE
 }
 
-// fuse: AdagradFuse mask, 0..7.
-int cb200_probe_adagrad(int fuse, int maximize, float* p, const float* g, float* sum, int64_t n,
-                        float lr, float lr_decay, float wd, float eps, float step, void* stream) {
-  using namespace cb200;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool mz = maximize != 0;
-  const unsigned grid = grid_for(n);
-#define CB200_CASE(F)                                                                              \
-  case F:                                                                                          \
-    probe_adagrad_kernel<F><<<grid, 256, 0, s>>>(p, g, sum, n, lr, lr_decay, wd, eps, step, mz); \
+struct AdagradProbe {
+  void *p, *sum;
+  const void* g;
+  int64_t n;
+  double lr, lr_decay, wd, eps, step;
+  bool maximize;
+  cudaStream_t s;
+};
+
+template <class T>
+int adagrad_dtype(int fuse, const AdagradProbe& a) {
+  const unsigned grid = grid_for(a.n);
+  T *p = static_cast<T*>(a.p), *sum = static_cast<T*>(a.sum);
+  const T* g = static_cast<const T*>(a.g);
+#define CB200_CASE(F)                                                                         \
+  case F:                                                                                     \
+    probe_adagrad_kernel<T, F><<<grid, 256, 0, a.s>>>(p, g, sum, a.n, a.lr, a.lr_decay, a.wd, \
+                                                      a.eps, a.step, a.maximize);             \
     break;
   switch (fuse) {
     CB200_CASE(0) CB200_CASE(1) CB200_CASE(2) CB200_CASE(3)
@@ -157,6 +184,50 @@ int cb200_probe_adagrad(int fuse, int maximize, float* p, const float* g, float*
   }
 #undef CB200_CASE
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+#define CB200_BY_DTYPE(FN, ...)                          \
+  switch (dtype) {                                       \
+    case kF32: return FN<float>(__VA_ARGS__);            \
+    case kF64: return FN<double>(__VA_ARGS__);           \
+    case kF16: return FN<__half>(__VA_ARGS__);           \
+    case kBF16: return FN<__nv_bfloat16>(__VA_ARGS__);   \
+    default: return 1;                                   \
+  }
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" {
+
+// dtype: storage type of p, g, m, v, mx (enum cb200_dtype); fuse: AdamFuse mask, 0..3.
+int cb200_probe_adam(int dtype, int fuse, int amsgrad, int adamw, int maximize, void* p,
+                     const void* g, void* m, void* v, void* mx, int64_t n, double lr, double beta1,
+                     double beta2, double eps, double wd, double step, void* stream) {
+  using namespace cb200;
+  const AdamProbe a{amsgrad, adamw, p, m, v, mx, g, n, lr, beta1, beta2, eps, wd, step,
+                    maximize != 0, static_cast<cudaStream_t>(stream)};
+  CB200_BY_DTYPE(adam_dtype, fuse, a)
+}
+
+// fuse: SgdFuse mask, 0..31 with blend field (bits 1-2) in 0..2.
+int cb200_probe_sgd(int dtype, int fuse, int has_buf, int maximize, int nesterov, void* p,
+                    const void* g, void* buf, int64_t n, double lr, double momentum,
+                    double dampening, double wd, double step, void* stream) {
+  using namespace cb200;
+  const SgdProbe a{has_buf, p, buf, g, n, lr, momentum, dampening, wd, step, nesterov != 0,
+                   maximize != 0, static_cast<cudaStream_t>(stream)};
+  CB200_BY_DTYPE(sgd_dtype, fuse, a)
+}
+
+// fuse: AdagradFuse mask, 0..7.
+int cb200_probe_adagrad(int dtype, int fuse, int maximize, void* p, const void* g, void* sum,
+                        int64_t n, double lr, double lr_decay, double wd, double eps, double step,
+                        void* stream) {
+  using namespace cb200;
+  const AdagradProbe a{p, sum, g, n, lr, lr_decay, wd, eps, step, maximize != 0,
+                       static_cast<cudaStream_t>(stream)};
+  CB200_BY_DTYPE(adagrad_dtype, fuse, a)
 }
 
 // out[i] = powf(base[i], expo[i]) as the prologue computes it.

@@ -13,12 +13,34 @@
 // them into one fma; each such site is a bit of the `Fuse` mask below, so the
 // choice that reproduces the installed torch build bit for bit is a compile-time
 // constant (contraction.h) found by running every combination against torch.
+//
+// `M` is the math type ("opmath" in ATen): float for fp32 / fp16 / bf16 storage,
+// double for fp64 storage.
 #pragma once
 
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace cb200 {
+
+// ---------------------------------------------------------------------------
+// Round-to-nearest primitives for both math types.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+__device__ __forceinline__ float fma_rn(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+__device__ __forceinline__ double fma_rn(double a, double b, double c) { return __fma_rn(a, b, c); }
+__device__ __forceinline__ float div_rn(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ double div_rn(double a, double b) { return __ddiv_rn(a, b); }
+__device__ __forceinline__ float sqrt_rn(float a) { return __fsqrt_rn(a); }
+__device__ __forceinline__ double sqrt_rn(double a) { return __dsqrt_rn(a); }
+// ATen's pow_(base, exp) is ::pow on the math type (ATen/native/cuda/Pow.cuh:41-44).
+__device__ __forceinline__ float pow_m(float a, float b) { return powf(a, b); }
+__device__ __forceinline__ double pow_m(double a, double b) { return pow(a, b); }
 
 // ---------------------------------------------------------------------------
 // Fusion sites.  A set bit means "this a*b+c is ONE fma".
@@ -43,32 +65,34 @@ enum SgdFuse : int {
 
 enum AdagradFuse : int {
   kAdagradFuseWd = 1,    // grad += param * weight_decay   (fp64 product and sum)
-  kAdagradFuseSum = 2,   // state_sum += grad * grad       (fp32)
+  kAdagradFuseSum = 2,   // state_sum += grad * grad       (in the math type)
   kAdagradFuseClr = 4,   // 1 + (step - 1) * lr_decay      (fp64, once per row)
   kAdagradFuseAll = 7,
 };
 
 // ---------------------------------------------------------------------------
-// Per-row scalar records: 32 bytes each, written once per step by the prologue
-// kernel and read by every block that works on the row.
+// Per-row scalar records, written once per step by the prologue kernel and read
+// by every block that works on the row: 32 bytes for float math, 64 for double.
 // ---------------------------------------------------------------------------
-struct alignas(32) AdamRow {
-  float lr;
-  float beta1;
-  float beta2;
-  float weight_decay;
-  float eps;
-  float step_size;   // lr / (1 - beta1^step)
-  float bc2_sqrt;    // sqrt(1 - beta2^step)
-  float lr_wd;       // lr * weight_decay (the left product of AdamW's decay)
+template <class M>
+struct alignas(8 * sizeof(M)) AdamRowT {
+  M lr;
+  M beta1;
+  M beta2;
+  M weight_decay;
+  M eps;
+  M step_size;   // lr / (1 - beta1^step)
+  M bc2_sqrt;    // sqrt(1 - beta2^step)
+  M lr_wd;       // lr * weight_decay (the left product of AdamW's decay)
 };
 
-struct alignas(32) SgdRow {
-  float lr;
-  float momentum;
-  float one_minus_dampening;  // 1.0f - dampening, in fp32
-  float weight_decay;
-  uint32_t first_step;        // state_steps[r] == 1 after the bump
+template <class M>
+struct alignas(8 * sizeof(M)) SgdRowT {
+  M lr;
+  M momentum;
+  M one_minus_dampening;  // 1 - dampening, in the math type
+  M weight_decay;
+  uint32_t first_step;    // state_steps[r] == 1 after the bump
   uint32_t nesterov;
   uint32_t pad0, pad1;
 };
@@ -80,58 +104,64 @@ struct alignas(32) AdagradRow {
   double pad;
 };
 
-static_assert(sizeof(AdamRow) == 32 && sizeof(SgdRow) == 32 && sizeof(AdagradRow) == 32,
-              "row records are one 32-byte sector");
+using AdamRow = AdamRowT<float>;
+using SgdRow = SgdRowT<float>;
+static_assert(sizeof(AdamRowT<float>) == 32 && sizeof(SgdRowT<float>) == 32 && sizeof(AdagradRow) == 32,
+              "float-math row records are one 32-byte sector");
+static_assert(sizeof(AdamRowT<double>) == 64 && sizeof(SgdRowT<double>) == 64,
+              "double-math row records are two sectors");
 
 // ---------------------------------------------------------------------------
 // Row scalars.
 // ---------------------------------------------------------------------------
 
-// Bias corrections in fp32 from the fp32 step, as the CUDA reference does
-// (cuda/adam.cu:105-122; ATen fused_adam_utils.cuh:140-153): 1 - powf(beta, step).
-__device__ __forceinline__ AdamRow adam_row(float lr, float beta1, float beta2, float eps,
-                                            float weight_decay, float step) {
-  AdamRow c;
+// Bias corrections in the math type from the step in the math type, as the CUDA
+// reference does (cuda/adam.cu:105-122; ATen fused_adam_utils.cuh:140-153):
+// 1 - pow(beta, step).
+template <class M>
+__device__ __forceinline__ AdamRowT<M> adam_row(M lr, M beta1, M beta2, M eps, M weight_decay,
+                                                M step) {
+  AdamRowT<M> c;
   c.lr = lr;
   c.beta1 = beta1;
   c.beta2 = beta2;
   c.weight_decay = weight_decay;
   c.eps = eps;
-  const float bc1 = __fsub_rn(1.0f, powf(beta1, step));
-  const float bc2 = __fsub_rn(1.0f, powf(beta2, step));
-  c.step_size = __fdiv_rn(lr, bc1);
-  c.bc2_sqrt = __fsqrt_rn(bc2);
-  c.lr_wd = __fmul_rn(lr, weight_decay);
+  const M bc1 = sub_rn(M(1), pow_m(beta1, step));
+  const M bc2 = sub_rn(M(1), pow_m(beta2, step));
+  c.step_size = div_rn(lr, bc1);
+  c.bc2_sqrt = sqrt_rn(bc2);
+  c.lr_wd = mul_rn(lr, weight_decay);
   return c;
 }
 
-__device__ __forceinline__ SgdRow sgd_row(float lr, float momentum, float dampening,
-                                          float weight_decay, float step, bool nesterov) {
-  SgdRow c;
+template <class M>
+__device__ __forceinline__ SgdRowT<M> sgd_row(M lr, M momentum, M dampening, M weight_decay, M step,
+                                              bool nesterov) {
+  SgdRowT<M> c;
   c.lr = lr;
   c.momentum = momentum;
-  c.one_minus_dampening = __fsub_rn(1.0f, dampening);
+  c.one_minus_dampening = sub_rn(M(1), dampening);
   c.weight_decay = weight_decay;
-  c.first_step = (step == 1.0f) ? 1u : 0u;  // cuda/sgd.cu:171
+  c.first_step = (step == M(1)) ? 1u : 0u;  // cuda/sgd.cu:171
   c.nesterov = nesterov ? 1u : 0u;
   c.pad0 = c.pad1 = 0u;
   return c;
 }
 
-// cuda/adagrad.cu:112-117: the step is fp32, `step - 1` is an fp32 subtraction,
+// cuda/adagrad.cu:103-117: hyper-parameters widen to fp64; the step is read as
+// fp32 (`static_cast<float>(state_steps[r])`), `step - 1` is an fp32 subtraction,
 // everything after it is fp64.
 template <int FUSE>
-__device__ __forceinline__ AdagradRow adagrad_row(float lr, float lr_decay, float weight_decay,
-                                                  float eps, float step) {
+__device__ __forceinline__ AdagradRow adagrad_row(double lr, double lr_decay, double weight_decay,
+                                                  double eps, float step) {
   AdagradRow c;
-  const double lr_d = static_cast<double>(lr);
-  const double decay_d = static_cast<double>(lr_decay);
   const double s = static_cast<double>(__fsub_rn(step, 1.0f));
-  const double denom = (FUSE & kAdagradFuseClr) ? __fma_rn(s, decay_d, 1.0)
-                                                : __dadd_rn(1.0, __dmul_rn(s, decay_d));
-  c.clr = __ddiv_rn(lr_d, denom);
-  c.weight_decay = static_cast<double>(weight_decay);
-  c.eps = static_cast<double>(eps);
+  const double denom = (FUSE & kAdagradFuseClr) ? __fma_rn(s, lr_decay, 1.0)
+                                                : __dadd_rn(1.0, __dmul_rn(s, lr_decay));
+  c.clr = __ddiv_rn(lr, denom);
+  c.weight_decay = weight_decay;
+  c.eps = eps;
   c.pad = 0.0;
   return c;
 }
@@ -143,85 +173,80 @@ __device__ __forceinline__ AdagradRow adagrad_row(float lr, float lr_decay, floa
 
 // adam_math, fused_adam_utils.cuh:55-84.  `std::max(a, b)` is `(a < b) ? b : a`,
 // which keeps a NaN already stored in max_exp_avg_sq.
-template <bool AMSGRAD, bool ADAMW, int FUSE>
-__device__ __forceinline__ void adam_elem(float& p, float g, float& m, float& v, float& mx,
-                                          const AdamRow& c, bool maximize) {
+template <bool AMSGRAD, bool ADAMW, int FUSE, class M>
+__device__ __forceinline__ void adam_elem(M& p, M g, M& m, M& v, M& mx, const AdamRowT<M>& c,
+                                          bool maximize) {
   if (maximize) g = -g;
-  if (c.weight_decay != 0.0f) {
+  if (c.weight_decay != M(0)) {
     if (!ADAMW) {
-      g = (FUSE & kAdamFuseL2) ? __fmaf_rn(p, c.weight_decay, g)
-                               : __fadd_rn(g, __fmul_rn(p, c.weight_decay));
+      g = (FUSE & kAdamFuseL2) ? fma_rn(p, c.weight_decay, g) : add_rn(g, mul_rn(p, c.weight_decay));
     } else {
-      p = (FUSE & kAdamFuseAdamW) ? __fmaf_rn(-c.lr_wd, p, p)
-                                  : __fsub_rn(p, __fmul_rn(c.lr_wd, p));
+      p = (FUSE & kAdamFuseAdamW) ? fma_rn(-c.lr_wd, p, p) : sub_rn(p, mul_rn(c.lr_wd, p));
     }
   }
-  m = __fmaf_rn(c.beta1, m, __fmaf_rn(-c.beta1, g, g));
-  const float gg = __fmul_rn(g, g);
-  v = __fmaf_rn(c.beta2, v, __fmaf_rn(-c.beta2, gg, gg));
-  float root;
+  m = fma_rn(c.beta1, m, fma_rn(-c.beta1, g, g));
+  const M gg = mul_rn(g, g);
+  v = fma_rn(c.beta2, v, fma_rn(-c.beta2, gg, gg));
+  M root;
   if (AMSGRAD) {
     mx = (mx < v) ? v : mx;
-    root = __fsqrt_rn(mx);
+    root = sqrt_rn(mx);
   } else {
-    root = __fsqrt_rn(v);
+    root = sqrt_rn(v);
   }
-  const float denom = __fadd_rn(__fdiv_rn(root, c.bc2_sqrt), c.eps);
-  p = __fsub_rn(p, __fdiv_rn(__fmul_rn(c.step_size, m), denom));
+  const M denom = add_rn(div_rn(root, c.bc2_sqrt), c.eps);
+  p = sub_rn(p, div_rn(mul_rn(c.step_size, m), denom));
 }
 
 // sgd_math, cuda/sgd.cu:103-131.  With HAS_BUF the buffer is always rewritten,
 // also for a row whose momentum is 0 (cuda/sgd.cu:40-50).
-template <bool HAS_BUF, int FUSE>
-__device__ __forceinline__ void sgd_elem(float& p, float g, float& buf, const SgdRow& c,
-                                         bool maximize) {
+template <bool HAS_BUF, int FUSE, class M>
+__device__ __forceinline__ void sgd_elem(M& p, M g, M& buf, const SgdRowT<M>& c, bool maximize) {
   if (maximize) g = -g;
-  if (c.weight_decay != 0.0f) {
-    g = (FUSE & kSgdFuseWd) ? __fmaf_rn(c.weight_decay, p, g)
-                            : __fadd_rn(g, __fmul_rn(c.weight_decay, p));
+  if (c.weight_decay != M(0)) {
+    g = (FUSE & kSgdFuseWd) ? fma_rn(c.weight_decay, p, g) : add_rn(g, mul_rn(c.weight_decay, p));
   }
   if (HAS_BUF) {
-    float b;
+    M b;
     if (c.first_step) {
       b = g;
     } else {
       constexpr int blend = (FUSE & kSgdBlendMask) >> kSgdBlendShift;
       if (blend == 1) {
-        b = __fmaf_rn(c.momentum, buf, __fmul_rn(c.one_minus_dampening, g));
+        b = fma_rn(c.momentum, buf, mul_rn(c.one_minus_dampening, g));
       } else if (blend == 2) {
-        b = __fmaf_rn(c.one_minus_dampening, g, __fmul_rn(c.momentum, buf));
+        b = fma_rn(c.one_minus_dampening, g, mul_rn(c.momentum, buf));
       } else {
-        b = __fadd_rn(__fmul_rn(c.momentum, buf), __fmul_rn(c.one_minus_dampening, g));
+        b = add_rn(mul_rn(c.momentum, buf), mul_rn(c.one_minus_dampening, g));
       }
     }
     buf = b;
     if (c.nesterov) {
-      g = (FUSE & kSgdFuseNesterov) ? __fmaf_rn(c.momentum, b, g)
-                                    : __fadd_rn(g, __fmul_rn(c.momentum, b));
+      g = (FUSE & kSgdFuseNesterov) ? fma_rn(c.momentum, b, g) : add_rn(g, mul_rn(c.momentum, b));
     } else {
       g = b;
     }
   }
-  p = (FUSE & kSgdFuseUpdate) ? __fmaf_rn(-c.lr, g, p) : __fsub_rn(p, __fmul_rn(c.lr, g));
+  p = (FUSE & kSgdFuseUpdate) ? fma_rn(-c.lr, g, p) : sub_rn(p, mul_rn(c.lr, g));
 }
 
-// adagrad_math, fused_adagrad_utils.cuh:25-48.  The accumulator is fp32; the
-// parameter update widens to fp64 because the hyper-parameters are doubles.
-template <int FUSE>
-__device__ __forceinline__ void adagrad_elem(float& p, float g, float& sum, const AdagradRow& c,
-                                             bool maximize) {
+// adagrad_math, fused_adagrad_utils.cuh:25-48.  The accumulator lives in the math
+// type; the hyper-parameters are doubles, so with float math the weight decay and
+// the parameter update widen to fp64 and narrow back.
+template <int FUSE, class M>
+__device__ __forceinline__ void adagrad_elem(M& p, M g, M& sum, const AdagradRow& c, bool maximize) {
   if (maximize) g = -g;
   if (c.weight_decay != 0.0) {
     const double pd = static_cast<double>(p);
     const double gd = static_cast<double>(g);
     const double t = (FUSE & kAdagradFuseWd) ? __fma_rn(pd, c.weight_decay, gd)
                                              : __dadd_rn(gd, __dmul_rn(pd, c.weight_decay));
-    g = __double2float_rn(t);
+    g = static_cast<M>(t);  // round to nearest for float, identity for double
   }
-  sum = (FUSE & kAdagradFuseSum) ? __fmaf_rn(g, g, sum) : __fadd_rn(sum, __fmul_rn(g, g));
-  const double denom = __dadd_rn(static_cast<double>(__fsqrt_rn(sum)), c.eps);
+  sum = (FUSE & kAdagradFuseSum) ? fma_rn(g, g, sum) : add_rn(sum, mul_rn(g, g));
+  const double denom = __dadd_rn(static_cast<double>(sqrt_rn(sum)), c.eps);
   const double delta = __ddiv_rn(__dmul_rn(c.clr, static_cast<double>(g)), denom);
-  p = __double2float_rn(__dsub_rn(static_cast<double>(p), delta));
+  p = static_cast<M>(__dsub_rn(static_cast<double>(p), delta));
 }
 
 }  // namespace cb200

@@ -8,47 +8,90 @@
 namespace cb200 {
 namespace {
 
+template <class M>
 struct SgdHyper {
-  const float* lr;
-  const float* momentum;
-  const float* dampening;
-  const float* weight_decay;
+  const M* lr;
+  const M* momentum;
+  const M* dampening;
+  const M* weight_decay;
   const uint8_t* nesterov_rows;  // NULL: every row uses `nesterov`
   int nesterov;
 };
 
 // Buffer order: params, grads, [momentum_buffers].
-template <bool HAS_BUF, int FUSE>
+template <class T, bool HAS_BUF, int FUSE>
 struct SgdOp {
+  using Storage = T;
+  using Math = typename Pack<T>::Math;
   static constexpr int kBufs = HAS_BUF ? 3 : 2;
   static constexpr unsigned kWriteMask = HAS_BUF ? 0x5u : 0x1u;
   static constexpr int kThreads = 256;  // measured best on B200: 6.5-6.9 TB/s with a momentum buffer
   static constexpr int kUnroll = 1;
-  using Row = SgdRow;
-  using Hyper = SgdHyper;
+  using Row = SgdRowT<Math>;
+  using Hyper = SgdHyper<Math>;
 
-  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, float step) {
+  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, Math step) {
     const bool nesterov = h.nesterov_rows ? (h.nesterov_rows[r] != 0) : (h.nesterov != 0);
-    return sgd_row(h.lr[r], h.momentum[r], h.dampening[r], h.weight_decay[r], step, nesterov);
+    return sgd_row<Math>(h.lr[r], h.momentum[r], h.dampening[r], h.weight_decay[r], step, nesterov);
   }
-  __device__ static __forceinline__ void apply(float (&x)[kBufs], const Row& c, int flags) {
-    float buf = 0.0f;
+  __device__ static __forceinline__ void apply(Math (&x)[kBufs], const Row& c, int flags) {
+    Math buf = Math(0);
     if constexpr (HAS_BUF) buf = x[2];
-    sgd_elem<HAS_BUF, FUSE>(x[0], x[1], buf, c, (flags & 1) != 0);
+    sgd_elem<HAS_BUF, FUSE, Math>(x[0], x[1], buf, c, (flags & 1) != 0);
     if constexpr (HAS_BUF) x[2] = buf;
   }
 };
 
+struct SgdArgs {
+  void* ptrs[3];
+  void* state_steps;
+  const void* lr;
+  const void* momentum;
+  const void* dampening;
+  const void* weight_decay;
+  const uint8_t* mask;
+  const uint8_t* nesterov_rows;
+  int64_t n_rows, row_len;
+  const int64_t* strides;
+  int nesterov, flags, bump;
+  int64_t hint;
+  void* workspace;
+  size_t workspace_bytes;
+  cudaStream_t stream;
+};
+
+template <class T, bool HAS_BUF>
+int sgd_run(const SgdArgs& a) {
+  using VecOp = SgdOp<T, HAS_BUF, HAS_BUF ? Fuse<T>::kSgdBufVec : Fuse<T>::kSgdPlainVec>;
+  using ElemOp = SgdOp<T, HAS_BUF, HAS_BUF ? Fuse<T>::kSgdBufElem : Fuse<T>::kSgdPlainElem>;
+  using M = typename VecOp::Math;
+  static const char* const names[3] = {"params", "grads", "momentum_buffers"};
+  Bufs<VecOp::kBufs> bufs;
+  if (int rc = fill_bufs(&bufs, a.ptrs, a.strides, a.n_rows, a.row_len, names)) return rc;
+  const SgdHyper<M> hyper{static_cast<const M*>(a.lr), static_cast<const M*>(a.momentum),
+                          static_cast<const M*>(a.dampening), static_cast<const M*>(a.weight_decay),
+                          a.nesterov_rows, a.nesterov};
+  return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
+                                 a.row_len, a.flags, a.bump, a.hint, a.workspace,
+                                 a.workspace_bytes, a.stream);
+}
+
+template <class T>
+int sgd_variant(const SgdArgs& a) {
+  return a.ptrs[2] ? sgd_run<T, true>(a) : sgd_run<T, false>(a);
+}
+
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_sgd_step(float* params, const float* grads, float* momentum_buffers,
-                              float* state_steps, const float* lr, const float* momentum,
-                              const float* dampening, const float* weight_decay,
+extern "C" int cb200_sgd_step(int dtype, void* params, const void* grads, void* momentum_buffers,
+                              void* state_steps, const void* lr, const void* momentum,
+                              const void* dampening, const void* weight_decay,
                               const uint8_t* active_mask, const uint8_t* nesterov_rows,
                               int64_t n_rows, int64_t row_len, const int64_t* strides,
-                              int nesterov, int maximize, int64_t active_rows_hint,
-                              void* workspace, size_t workspace_bytes, void* stream) {
+                              int nesterov, int maximize, int steps_already_bumped,
+                              int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
+                              void* stream) {
   using namespace cb200;
   // (an empty matrix has no storage, so a NULL there says nothing)
   if ((nesterov || nesterov_rows) && !momentum_buffers && n_rows > 0 && row_len > 0) {
@@ -57,23 +100,32 @@ extern "C" int cb200_sgd_step(float* params, const float* grads, float* momentum
   if (n_rows > 0 && (!lr || !momentum || !dampening || !weight_decay)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }
-  const SgdHyper hyper{lr, momentum, dampening, weight_decay, nesterov_rows, nesterov};
-  static const char* const names[3] = {"params", "grads", "momentum_buffers"};
-  float* ptrs[3] = {params, const_cast<float*>(grads), momentum_buffers};
-  const int flags = maximize ? 1 : 0;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (momentum_buffers) {
-    using VecOp = SgdOp<true, kSgdFuseVecBuf>;
-    using ElemOp = SgdOp<true, kSgdFuseElemBuf>;
-    Bufs<3> bufs;
-    if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
-    return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len, flags,
-                                   active_rows_hint, workspace, workspace_bytes, s);
+  SgdArgs a;
+  a.ptrs[0] = params;
+  a.ptrs[1] = const_cast<void*>(grads);
+  a.ptrs[2] = momentum_buffers;
+  a.state_steps = state_steps;
+  a.lr = lr;
+  a.momentum = momentum;
+  a.dampening = dampening;
+  a.weight_decay = weight_decay;
+  a.mask = active_mask;
+  a.nesterov_rows = nesterov_rows;
+  a.n_rows = n_rows;
+  a.row_len = row_len;
+  a.strides = strides;
+  a.nesterov = nesterov;
+  a.flags = maximize ? 1 : 0;
+  a.bump = steps_already_bumped ? 0 : 1;
+  a.hint = active_rows_hint;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case kF32: return sgd_variant<float>(a);
+    case kF64: return sgd_variant<double>(a);
+    case kF16: return sgd_variant<__half>(a);
+    case kBF16: return sgd_variant<__nv_bfloat16>(a);
+    default: return fail(CB200_ERR_INVALID_ARGUMENT, "dtype must be CB200_F32, _F64, _F16 or _BF16");
   }
-  using VecOp = SgdOp<false, kSgdFuseVecPlain>;
-  using ElemOp = SgdOp<false, kSgdFuseElemPlain>;
-  Bufs<2> bufs;
-  if (int rc = fill_bufs(&bufs, ptrs, strides, n_rows, row_len, names)) return rc;
-  return run_step<VecOp, ElemOp>(hyper, state_steps, active_mask, bufs, n_rows, row_len, flags,
-                                 active_rows_hint, workspace, workspace_bytes, s);
 }

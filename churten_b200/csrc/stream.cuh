@@ -29,6 +29,8 @@
 // contraction; it is bound by HBM bandwidth (12-36 bytes per element).
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -61,7 +63,8 @@ constexpr int kMaxBufs = 5;
 
 // ---------------------------------------------------------------------------
 // Workspace: [header 256 B][row ids: n_rows x int32, padded to 256 B][records:
-// n_rows x 32 B].  Only the first n_active ids / records are meaningful.
+// n_rows x 32 B (64 B for fp64 storage)].  Only the first n_active ids / records
+// are meaningful.
 // ---------------------------------------------------------------------------
 struct WsHeader {
   int32_t n_active;
@@ -72,9 +75,11 @@ inline size_t ws_ids_bytes(int64_t n_rows) {
   const size_t raw = static_cast<size_t>(n_rows) * sizeof(int32_t);
   return (raw + kWsAlign - 1) / kWsAlign * kWsAlign;
 }
-inline size_t ws_bytes(int64_t n_rows) {
+// `record_bytes`: 32 for float math, 64 for double math (the size cb200_workspace_bytes reports).
+constexpr size_t kMaxRecordBytes = 64;
+inline size_t ws_bytes(int64_t n_rows, size_t record_bytes = kMaxRecordBytes) {
   if (n_rows < 0) n_rows = 0;
-  return kWsAlign + ws_ids_bytes(n_rows) + static_cast<size_t>(n_rows) * 32;
+  return kWsAlign + ws_ids_bytes(n_rows) + static_cast<size_t>(n_rows) * record_bytes;
 }
 
 struct WsView {
@@ -96,7 +101,7 @@ inline WsView ws_view(void* workspace, int64_t n_rows) {
 // ---------------------------------------------------------------------------
 template <int NB>
 struct Bufs {
-  float* ptr[NB];
+  void* ptr[NB];   // storage type of the optimizer (float, double, __half, __nv_bfloat16)
   int64_t stride_r[NB];
   int64_t stride_t[NB];
 };
@@ -110,25 +115,25 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 
 template <bool STREAM>
-__device__ __forceinline__ float4 load4(const float* p) {
-  if (STREAM) return __ldcs(reinterpret_cast<const float4*>(p));
-  return *reinterpret_cast<const float4*>(p);
+__device__ __forceinline__ uint4 load16(const void* p) {
+  if (STREAM) return __ldcs(reinterpret_cast<const uint4*>(p));
+  return *reinterpret_cast<const uint4*>(p);
 }
 template <bool STREAM>
-__device__ __forceinline__ void store4(float* p, const float4& v) {
+__device__ __forceinline__ void store16(void* p, const uint4& v) {
   if (STREAM) {
-    __stcs(reinterpret_cast<float4*>(p), v);
+    __stcs(reinterpret_cast<uint4*>(p), v);
   } else {
-    *reinterpret_cast<float4*>(p) = v;
+    *reinterpret_cast<uint4*>(p) = v;
   }
 }
-template <bool STREAM>
-__device__ __forceinline__ float load1(const float* p) {
+template <bool STREAM, class T>
+__device__ __forceinline__ T load1(const T* p) {
   if (STREAM) return __ldcs(p);
   return *p;
 }
-template <bool STREAM>
-__device__ __forceinline__ void store1(float* p, float v) {
+template <bool STREAM, class T>
+__device__ __forceinline__ void store1(T* p, T v) {
   if (STREAM) {
     __stcs(p, v);
   } else {
@@ -136,26 +141,119 @@ __device__ __forceinline__ void store1(float* p, float v) {
   }
 }
 
-__device__ __forceinline__ float& lane(float4& v, int i) {
-  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
-}
+// Storage <-> math conversions.  `Pack<T>` views one 16-byte access as kVec
+// elements of storage type T and converts them to the math type and back
+// (round to nearest even, as ATen's c10::Half / c10::BFloat16 constructors do).
+template <class T>
+struct Pack;
+
+template <>
+struct Pack<float> {
+  using Math = float;
+  static constexpr int kVec = 4;
+  __device__ static __forceinline__ float to_math(float x) { return x; }
+  __device__ static __forceinline__ float from_math(float x) { return x; }
+  __device__ static __forceinline__ void unpack(const uint4& v, float (&out)[4]) {
+    out[0] = __uint_as_float(v.x);
+    out[1] = __uint_as_float(v.y);
+    out[2] = __uint_as_float(v.z);
+    out[3] = __uint_as_float(v.w);
+  }
+  __device__ static __forceinline__ uint4 pack(const float (&in)[4]) {
+    return make_uint4(__float_as_uint(in[0]), __float_as_uint(in[1]), __float_as_uint(in[2]),
+                      __float_as_uint(in[3]));
+  }
+};
+
+template <>
+struct Pack<double> {
+  using Math = double;
+  static constexpr int kVec = 2;
+  __device__ static __forceinline__ double to_math(double x) { return x; }
+  __device__ static __forceinline__ double from_math(double x) { return x; }
+  __device__ static __forceinline__ void unpack(const uint4& v, double (&out)[2]) {
+    out[0] = __hiloint2double(static_cast<int>(v.y), static_cast<int>(v.x));
+    out[1] = __hiloint2double(static_cast<int>(v.w), static_cast<int>(v.z));
+  }
+  __device__ static __forceinline__ uint4 pack(const double (&in)[2]) {
+    return make_uint4(static_cast<unsigned>(__double2loint(in[0])),
+                      static_cast<unsigned>(__double2hiint(in[0])),
+                      static_cast<unsigned>(__double2loint(in[1])),
+                      static_cast<unsigned>(__double2hiint(in[1])));
+  }
+};
+
+template <>
+struct Pack<__half> {
+  using Math = float;
+  static constexpr int kVec = 8;
+  __device__ static __forceinline__ float to_math(__half x) { return __half2float(x); }
+  __device__ static __forceinline__ __half from_math(float x) { return __float2half_rn(x); }
+  __device__ static __forceinline__ void unpack(const uint4& v, float (&out)[8]) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      out[2 * i] = __low2float(h);
+      out[2 * i + 1] = __high2float(h);
+    }
+  }
+  __device__ static __forceinline__ uint4 pack(const float (&in)[8]) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+      w[i] = *reinterpret_cast<const unsigned*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <>
+struct Pack<__nv_bfloat16> {
+  using Math = float;
+  static constexpr int kVec = 8;
+  __device__ static __forceinline__ float to_math(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ static __forceinline__ __nv_bfloat16 from_math(float x) { return __float2bfloat16_rn(x); }
+  __device__ static __forceinline__ void unpack(const uint4& v, float (&out)[8]) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // a bf16 is the upper half of an fp32
+      out[2 * i] = __uint_as_float(w[i] << 16);
+      out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static __forceinline__ uint4 pack(const float (&in)[8]) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+      w[i] = *reinterpret_cast<const unsigned*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
 
 // ---------------------------------------------------------------------------
 // Launch 1: the prologue.
 //
 // Op supplies:  struct Hyper (device pointers to the (n_rows,) vectors + flags),
-//               using Row, and
-//               __device__ static Row make_row(const Hyper&, int r, float step).
+//               using Row, using Math (float or double: the type of the step counter
+//               and of the hyper-parameter vectors), and
+//               __device__ static Row make_row(const Hyper&, int r, Math step).
+// `bump` = 0: the caller has already advanced the counters of the active rows.
 // ---------------------------------------------------------------------------
 template <class Op>
 __global__ void __launch_bounds__(kPrologueThreads)
-prologue_kernel(typename Op::Hyper hyper, float* __restrict__ state_steps,
-                const uint8_t* __restrict__ active_mask, int n_rows, WsView ws) {
+prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_steps,
+                const uint8_t* __restrict__ active_mask, int n_rows, int bump, WsView ws) {
   // Let the streaming grid become resident now; it blocks in pdl_wait() until
   // this grid has finished and its writes are visible.
   pdl_launch_dependents();
 
   using Row = typename Op::Row;
+  using M = typename Op::Math;
   Row* rows = static_cast<Row*>(ws.rows);
 
   __shared__ int warp_count[kPrologueThreads / 32];
@@ -187,10 +285,13 @@ prologue_kernel(typename Op::Hyper hyper, float* __restrict__ state_steps,
     __syncthreads();
     if (active) {
       const int slot = running + warp_offset[warp_id] + __popc(ballot & ((1u << lane_id) - 1u));
-      // The reference bumps with `state_steps.add_(mask.to(float))`
-      // (cuda/adam.cu:277): an fp32 add of 1.0f.
-      const float step = __fadd_rn(state_steps[r], 1.0f);
-      state_steps[r] = step;
+      // The reference bumps with `state_steps.add_(mask.to(dtype))`
+      // (cuda/adam.cu:277): an add of 1 in the counter's own type.
+      M step = state_steps[r];
+      if (bump) {
+        step = add_rn(step, M(1));
+        state_steps[r] = step;
+      }
       ws.ids[slot] = r;
       rows[slot] = Op::make_row(hyper, r, step);
     }
@@ -204,12 +305,14 @@ prologue_kernel(typename Op::Hyper hyper, float* __restrict__ state_steps,
 }
 
 // ---------------------------------------------------------------------------
-// Launch 2a: persistent 128-bit streaming kernel.
+// Launch 2a: 128-bit streaming kernel.
 //
-// Op supplies:  kBufs, kWriteMask (bit b set: buffer b is written back), Row,
-//               __device__ static void apply(float (&x)[kBufs], const Row&, int flags)
-//               for ONE element (x[b] = that element of buffer b).
-// Requires element stride 1, 16-byte aligned rows, row_len % 4 == 0.
+// Op supplies:  Storage (element type in memory), Math, kBufs, kWriteMask (bit b
+//               set: buffer b is written back), Row, and
+//               __device__ static void apply(Math (&x)[kBufs], const Row&, int flags)
+//               for ONE element (x[b] = that element of buffer b, in the math type).
+// Requires element stride 1, 16-byte aligned rows, row_len % (16 / sizeof(Storage)) == 0.
+// A 16-byte access holds kVec = 4 fp32, 8 fp16/bf16 or 2 fp64 elements.
 // ---------------------------------------------------------------------------
 template <class Op, int UNROLL, bool STREAM>
 __global__ void __launch_bounds__(512)
@@ -217,13 +320,17 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
               int flags) {
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
+  using T = typename Op::Storage;
+  using M = typename Op::Math;
+  using P = Pack<T>;
+  constexpr int VEC = P::kVec;
 
   pdl_wait();
 
   const int n_active = ws.header->n_active;
   const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
-  const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * 4 * UNROLL;
-  const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * 4;
+  const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * VEC * UNROLL;
+  const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * VEC;
   const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
@@ -239,37 +346,40 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
     }
     const int64_t r = ws.ids[a];
     const Row c = rows[a];
-    const int64_t e0 = tile * tile_elems + static_cast<int64_t>(threadIdx.x) * 4;
+    const int64_t e0 = tile * tile_elems + static_cast<int64_t>(threadIdx.x) * VEC;
 
-    float* base[NB];
+    T* base[NB];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) base[b] = bufs.ptr[b] + r * bufs.stride_r[b] + e0;
+    for (int b = 0; b < NB; ++b) base[b] = static_cast<T*>(bufs.ptr[b]) + r * bufs.stride_r[b] + e0;
 
-    float4 x[UNROLL][NB];
+    uint4 raw[UNROLL][NB];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       if (e0 + u * lane_elems < row_len) {
 #pragma unroll
-        for (int b = 0; b < NB; ++b) x[u][b] = load4<STREAM>(base[b] + u * lane_elems);
+        for (int b = 0; b < NB; ++b) raw[u][b] = load16<STREAM>(base[b] + u * lane_elems);
       }
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       if (e0 + u * lane_elems < row_len) {
+        M x[NB][VEC];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float e[NB];
+        for (int b = 0; b < NB; ++b) P::unpack(raw[u][b], x[b]);
 #pragma unroll
-          for (int b = 0; b < NB; ++b) e[b] = lane(x[u][b], k);
+        for (int k = 0; k < VEC; ++k) {
+          M e[NB];
+#pragma unroll
+          for (int b = 0; b < NB; ++b) e[b] = x[b][k];
           Op::apply(e, c, flags);
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
-            if ((Op::kWriteMask >> b) & 1) lane(x[u][b], k) = e[b];
+            if ((Op::kWriteMask >> b) & 1) x[b][k] = e[b];
           }
         }
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          if ((Op::kWriteMask >> b) & 1) store4<STREAM>(base[b] + u * lane_elems, x[u][b]);
+          if ((Op::kWriteMask >> b) & 1) store16<STREAM>(base[b] + u * lane_elems, P::pack(x[b]));
         }
       }
     }
@@ -286,6 +396,9 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
                int flags) {
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
+  using T = typename Op::Storage;
+  using M = typename Op::Math;
+  using P = Pack<T>;
 
   pdl_wait();
 
@@ -301,14 +414,15 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
     const Row c = rows[a];
     const int64_t e0 = tile * tile_elems + threadIdx.x;
 
-    float x[UNROLL][NB];
+    M x[UNROLL][NB];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int64_t e = e0 + static_cast<int64_t>(u) * blockDim.x;
       if (e < row_len) {
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          x[u][b] = load1<STREAM>(bufs.ptr[b] + r * bufs.stride_r[b] + e * bufs.stride_t[b]);
+          const T* src = static_cast<const T*>(bufs.ptr[b]) + r * bufs.stride_r[b] + e * bufs.stride_t[b];
+          x[u][b] = P::to_math(load1<STREAM>(src));
         }
       }
     }
@@ -320,7 +434,8 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
           if ((Op::kWriteMask >> b) & 1) {
-            store1<STREAM>(bufs.ptr[b] + r * bufs.stride_r[b] + e * bufs.stride_t[b], x[u][b]);
+            T* dst = static_cast<T*>(bufs.ptr[b]) + r * bufs.stride_r[b] + e * bufs.stride_t[b];
+            store1<STREAM>(dst, P::from_math(x[u][b]));
           }
         }
       }
@@ -331,19 +446,12 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
 // ---------------------------------------------------------------------------
 // Host launcher.
 // ---------------------------------------------------------------------------
-struct StepShape {
-  int64_t n_rows;
-  int64_t row_len;
-  bool vector_ok;       // every buffer dense-in-row, 16-byte aligned, row_len % 4 == 0
-  size_t bytes_per_elem;  // algorithmic traffic per element (for the cache-policy choice)
-};
-
 template <int NB>
-inline bool vector_layout_ok(const Bufs<NB>& b, int64_t row_len) {
-  if (row_len % 4 != 0) return false;
+inline bool vector_layout_ok(const Bufs<NB>& b, int64_t row_len, int vec) {
+  if (row_len % vec != 0) return false;
   for (int i = 0; i < NB; ++i) {
     if (b.stride_t[i] != 1) return false;
-    if (b.stride_r[i] % 4 != 0) return false;
+    if (b.stride_r[i] % vec != 0) return false;
     if (reinterpret_cast<uintptr_t>(b.ptr[i]) % 16 != 0) return false;
   }
   return true;
@@ -366,13 +474,17 @@ inline cudaError_t launch_dependent(Kernel kernel, dim3 grid, dim3 block, cudaSt
 }
 
 // Runs the two launches of one step.  VecOp / ElemOp are the same optimizer with
-// the fusion masks of torch's vector and element-wise paths.
+// the fusion masks of torch's vector and element-wise paths.  `bump_steps` = 0
+// when the caller has already advanced the counters of the active rows.
 template <class VecOp, class ElemOp>
-inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
+inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* state_steps,
                     const uint8_t* active_mask, const Bufs<VecOp::kBufs>& bufs, int64_t n_rows,
-                    int64_t row_len, int flags, int64_t active_rows_hint, void* workspace,
-                    size_t workspace_bytes, cudaStream_t stream) {
+                    int64_t row_len, int flags, int bump_steps, int64_t active_rows_hint,
+                    void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   static_assert(VecOp::kBufs == ElemOp::kBufs, "same optimizer");
+  using T = typename VecOp::Storage;
+  constexpr int kVec = Pack<T>::kVec;
+  constexpr size_t kRecord = sizeof(typename VecOp::Row);
   if (n_rows < 0 || row_len < 0) return fail(1, "n_rows and row_len must be >= 0");
   if (n_rows > 0x7fffffffLL) return fail(1, "n_rows must fit in 31 bits");
   if (n_rows == 0) return 0;
@@ -380,24 +492,24 @@ inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
   if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kWsAlign != 0) {
     return fail(2, "workspace must be a 256-byte aligned device pointer");
   }
-  if (workspace_bytes < ws_bytes(n_rows)) {
-    return fail(2, "workspace too small: need " + std::to_string(ws_bytes(n_rows)) + " bytes, got " +
-                       std::to_string(workspace_bytes));
+  if (workspace_bytes < ws_bytes(n_rows, kRecord)) {
+    return fail(2, "workspace too small: need " + std::to_string(ws_bytes(n_rows, kRecord)) +
+                       " bytes, got " + std::to_string(workspace_bytes));
   }
   int sm_count = 0;
   size_t l2_bytes = 0;
   if (int rc = device_info(&sm_count, &l2_bytes)) return rc;
 
   const WsView ws = ws_view(workspace, n_rows);
-  const bool vec = vector_layout_ok(bufs, row_len);
+  const bool vec = vector_layout_ok(bufs, row_len, kVec);
 
   // The row records are built with the fusion mask of the path that reads them.
   if (vec) {
-    prologue_kernel<VecOp><<<1, kPrologueThreads, 0, stream>>>(hyper, state_steps, active_mask,
-                                                                static_cast<int>(n_rows), ws);
+    prologue_kernel<VecOp><<<1, kPrologueThreads, 0, stream>>>(
+        hyper, state_steps, active_mask, static_cast<int>(n_rows), bump_steps, ws);
   } else {
-    prologue_kernel<ElemOp><<<1, kPrologueThreads, 0, stream>>>(hyper, state_steps, active_mask,
-                                                                 static_cast<int>(n_rows), ws);
+    prologue_kernel<ElemOp><<<1, kPrologueThreads, 0, stream>>>(
+        hyper, state_steps, active_mask, static_cast<int>(n_rows), bump_steps, ws);
   }
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return cuda_fail(err, "prologue launch");
@@ -408,10 +520,10 @@ inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
 
   const LaunchGeometry geo = geometry();
   const int threads = geo.threads > 0 ? geo.threads : VecOp::kThreads;
-  const int64_t per_thread = vec ? 4 : 1;
+  const int64_t per_thread = vec ? kVec : 1;
   // Streaming hints once the step's traffic no longer fits in L2.
-  const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) * 4.0 *
-                           VecOp::kBufs;
+  const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) *
+                           static_cast<double>(sizeof(T)) * VecOp::kBufs;
   const bool stream_hint = footprint > 0.75 * static_cast<double>(l2_bytes);
 
   // Tile shape.  Measured on B200: with one CTA per tile a shallow tile is fastest,
@@ -468,7 +580,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, float* state_steps,
 
 // Fills a buffer table from the C-ABI arguments.
 template <int NB>
-inline int fill_bufs(Bufs<NB>* out, float* const* ptrs, const int64_t* strides, int64_t n_rows,
+inline int fill_bufs(Bufs<NB>* out, void* const* ptrs, const int64_t* strides, int64_t n_rows,
                      int64_t row_len, const char* const* names) {
   // Empty matrices have no storage: their pointers may be NULL and are never used.
   const bool need_data = n_rows > 0 && row_len > 0;
@@ -480,5 +592,8 @@ inline int fill_bufs(Bufs<NB>* out, float* const* ptrs, const int64_t* strides, 
   }
   return 0;
 }
+
+// Storage types of the C ABI's `dtype` argument.
+enum Dtype : int { kF32 = 0, kF64 = 1, kF16 = 2, kBF16 = 3 };
 
 }  // namespace cb200

@@ -123,25 +123,42 @@ def _slot(device: torch.device, stream_id: int, n_rows: int) -> _Slot:
     return slot
 
 
+# storage dtype -> (cb200_dtype, math dtype): the four types the reference dispatches
+# (cuda/adam.cu:302-303); fp16 / bf16 compute in fp32 like ATen's opmath_type.
+_DTYPES = {
+    torch.float32: (_lib.F32, torch.float32),
+    torch.float64: (_lib.F64, torch.float64),
+    torch.float16: (_lib.F16, torch.float32),
+    torch.bfloat16: (_lib.BF16, torch.float32),
+}
+
+
 def _check_consolidated(params: torch.Tensor, op: str) -> None:
     # The reference also rejects R > 65535 (cuda/consolidated.cuh:72-81) because
     # it maps rows onto blockIdx.y; the flat work list here has no such limit.
     if params.dim() != 2:
         raise RuntimeError(f"{op}: params must be a 2-D (R, T) buffer")
-    if params.dtype != torch.float32:
+    if params.dtype not in _DTYPES:
         raise RuntimeError(
-            f"{op}: only float32 storage is implemented on sm_100a, got {params.dtype}"
+            f"{op}: storage must be float32, float64, float16 or bfloat16, got {params.dtype}"
         )
 
 
-def _hyper(t: torch.Tensor, device: torch.device) -> torch.Tensor:
-    # cuda/consolidated.cuh:87-89 `to_hyper`: compute dtype + contiguous; no-ops normally.
-    if t.dtype is torch.float32 and t.is_cuda and t.is_contiguous() and t.get_device() == device.index:
+def _hyper(t: torch.Tensor, params: torch.Tensor) -> torch.Tensor:
+    """cuda/consolidated.cuh:87-89 `to_hyper`: the `(R,)` side input in the storage dtype,
+    contiguous (so a bf16 model sees its learning rate rounded to bf16, as in the
+    reference), then widened to the math type the library reads.  No-ops normally."""
+    storage = params.dtype
+    math = _DTYPES[storage][1]
+    if t.dtype is storage and storage is math and t.is_cuda and t.is_contiguous() \
+            and t.get_device() == params.get_device():
         return t
-    if t.dtype is not torch.float32:
-        t = t.to(torch.float32)
-    if t.device != device:
-        raise RuntimeError(f"hyper-parameter on {t.device}, params on {device}")
+    if t.device != params.device:
+        raise RuntimeError(f"hyper-parameter on {t.device}, params on {params.device}")
+    if t.dtype is not storage:
+        t = t.to(storage)
+    if storage is not math:
+        t = t.to(math)
     return t if t.is_contiguous() else t.contiguous()
 
 
@@ -159,7 +176,7 @@ def _same_layout_args(op: str, params: torch.Tensor, others: list[tuple[str, tor
     index = params.get_device()
     # the usual case: every buffer dense fp32 on the same device with the same shape
     for _, t in tensors:
-        if not (t.is_contiguous() and t.dtype is torch.float32 and t.shape == shape
+        if not (t.is_contiguous() and t.dtype is params.dtype and t.shape == shape
                 and t.is_cuda and t.get_device() == index):
             break
     else:
@@ -168,8 +185,8 @@ def _same_layout_args(op: str, params: torch.Tensor, others: list[tuple[str, tor
     for name, t in tensors:
         if t.shape != shape:
             raise RuntimeError(f"{op}: {name} has shape {tuple(t.shape)}, params {tuple(shape)}")
-        if t.dtype != torch.float32 or t.device != params.device:
-            raise RuntimeError(f"{op}: {name} must be float32 on {params.device}")
+        if t.dtype != params.dtype or t.device != params.device:
+            raise RuntimeError(f"{op}: {name} must be {params.dtype} on {params.device}")
         if shape[0] > 0 and shape[1] > 0 and (t.stride(1) != 1 or (shape[0] > 1 and t.stride(0) != shape[1])):
             dense = False
     if dense:
@@ -189,15 +206,18 @@ class _Call:
         self.n_rows, self.row_len = params.shape
         if state_steps.numel() != self.n_rows or active_mask.numel() != self.n_rows:
             raise RuntimeError(f"{op}: state_steps and active_mask must have one entry per row")
-        # The bump lands in the caller's storage (a declared mutation).  A counter
-        # that is not dense fp32 is bumped through a dense copy and written back.
-        self.steps_out = state_steps
-        if state_steps.dtype is torch.float32 and state_steps.is_contiguous():
+        self.dtype, math = _DTYPES[params.dtype]
+        # The bump lands in the caller's storage (a declared mutation).  A dense
+        # counter of the math type is bumped by the prologue kernel; any other is
+        # bumped here the way the reference does it (`state_steps.add_(mask.to(dtype))`,
+        # cuda/adam.cu:277) and handed over as `to_hyper` would (consolidated.cuh:87-89).
+        if state_steps.dtype is math and state_steps.is_contiguous():
             self.steps = state_steps
+            self.bumped = 0
         else:
-            self.steps = state_steps.to(torch.float32).contiguous()
-            if self.steps.data_ptr() == state_steps.data_ptr():
-                self.steps = self.steps.clone()
+            state_steps.add_(active_mask.to(state_steps.dtype))
+            self.steps = state_steps.to(params.dtype).to(math).contiguous()
+            self.bumped = 1
         self.mask = _mask(active_mask)
         # identity of the caller's tensor + its version counter: any in-place write bumps it
         self.mask_tensor = active_mask
@@ -236,8 +256,6 @@ class _Call:
 
     def finish(self, status: int, params: torch.Tensor) -> torch.Tensor:
         _lib.check(status, self.op)
-        if self.steps is not self.steps_out:
-            self.steps_out.copy_(self.steps)
         if self.read_back:
             slot = self.slot
             if slot.pinned is None:
@@ -265,17 +283,16 @@ def adam_step_cuda(
     strides = _same_layout_args(op, params, others)
     if strides is not None and not amsgrad:
         strides = (ctypes.c_int64 * 10)(*strides, 0, 0)
-    dev = params.device
     with _Call(op, params, state_steps, active_mask) as call:
-        lr_c, b1_c, b2_c = _hyper(lr, dev), _hyper(beta1, dev), _hyper(beta2, dev)
-        eps_c, wd_c = _hyper(eps, dev), _hyper(weight_decay, dev)
+        lr_c, b1_c, b2_c = _hyper(lr, params), _hyper(beta1, params), _hyper(beta2, params)
+        eps_c, wd_c = _hyper(eps, params), _hyper(weight_decay, params)
         status = _cb.cb200_adam_step(
-            params.data_ptr(), grads.data_ptr(), exp_avgs.data_ptr(), exp_avg_sqs.data_ptr(),
+            call.dtype, params.data_ptr(), grads.data_ptr(), exp_avgs.data_ptr(), exp_avg_sqs.data_ptr(),
             max_exp_avg_sqs.data_ptr() if amsgrad else None,
             call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
             eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(),
             call.n_rows, call.row_len, strides,
-            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.hint,
+            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.bumped, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params)
@@ -296,18 +313,17 @@ def sgd_step_cuda(
     strides = _same_layout_args(op, params, others)
     if strides is not None and momentum_buffers is None:
         strides = (ctypes.c_int64 * 6)(*strides, 0, 0)
-    dev = params.device
     with _Call(op, params, state_steps, active_mask) as call:
-        lr_c, mom_c = _hyper(lr, dev), _hyper(momentum, dev)
-        damp_c, wd_c = _hyper(dampening, dev), _hyper(weight_decay, dev)
+        lr_c, mom_c = _hyper(lr, params), _hyper(momentum, params)
+        damp_c, wd_c = _hyper(dampening, params), _hyper(weight_decay, params)
         nrows_c = _mask(nesterov_rows) if nesterov_rows is not None else None
         status = _cb.cb200_sgd_step(
-            params.data_ptr(), grads.data_ptr(),
+            call.dtype, params.data_ptr(), grads.data_ptr(),
             momentum_buffers.data_ptr() if momentum_buffers is not None else None,
             call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(),
             wd_c.data_ptr(), call.mask.data_ptr(),
             nrows_c.data_ptr() if nrows_c is not None else None,
-            call.n_rows, call.row_len, strides, int(nesterov), int(maximize), call.hint,
+            call.n_rows, call.row_len, strides, int(nesterov), int(maximize), call.bumped, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params)
@@ -320,15 +336,14 @@ def adagrad_step_cuda(
     op = "torchstrap::adagrad_step_"
     _check_consolidated(params, op)
     strides = _same_layout_args(op, params, [("grads", grads), ("state_sums", state_sums)])
-    dev = params.device
     with _Call(op, params, state_steps, active_mask) as call:
-        lr_c, lrd_c = _hyper(lr, dev), _hyper(lr_decay, dev)
-        wd_c, eps_c = _hyper(weight_decay, dev), _hyper(eps, dev)
+        lr_c, lrd_c = _hyper(lr, params), _hyper(lr_decay, params)
+        wd_c, eps_c = _hyper(weight_decay, params), _hyper(eps, params)
         status = _cb.cb200_adagrad_step(
-            params.data_ptr(), grads.data_ptr(), state_sums.data_ptr(),
+            call.dtype, params.data_ptr(), grads.data_ptr(), state_sums.data_ptr(),
             call.steps.data_ptr(), lr_c.data_ptr(), lrd_c.data_ptr(), wd_c.data_ptr(),
             eps_c.data_ptr(), call.mask.data_ptr(),
-            call.n_rows, call.row_len, strides, int(maximize), call.hint,
+            call.n_rows, call.row_len, strides, int(maximize), call.bumped, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params)

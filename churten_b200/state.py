@@ -168,45 +168,55 @@ class OptimizerState(Mapping):
 
 
 class _GradViews:
-    """What `State._consolidated_grads` returns: per-name views into `grads`.
+    """What `State._consolidated_grads` returns: the per-name windows of `grads`.
 
     `update_` is the gradient scatter of `apply_gradient`.  On a CUDA device, dense
     fp32 gradients are written by one fused launch of the library
     (`cb200_scatter_rows`) instead of one `copy_` per parameter tensor; anything
-    else (other dtypes, strided gradients, CPU) takes the per-tensor `copy_`.
+    else (other dtypes, strided gradients, CPU) takes the per-tensor `copy_` into
+    an aliased view, which is built only when it is needed.
     """
 
-    def __init__(self, views: dict[str, torch.Tensor], grads: torch.Tensor | None = None,
-                 meta: list[tuple] | None = None):
-        self._views = views
+    def __init__(self, grads: torch.Tensor, meta: list[tuple], windows: dict[str, tuple[int, int]]):
         self._grads = grads
-        self._meta = {name: (offset, numel) for name, _, offset, numel in (meta or [])}
+        self._meta = meta
+        self._windows = windows
+        self._views: dict[str, torch.Tensor] | None = None
+
+    def _view(self, name: str) -> torch.Tensor:
+        if self._views is None:
+            self._views = consolidated_dict_view(self._grads, self._meta)
+        return self._views[name]
 
     def update_(self, grads: Mapping[str, torch.Tensor]) -> "_GradViews":
         dst = self._grads
-        if dst is not None and dst.is_cuda and dst.dtype is torch.float32 and len(grads) > 1:
-            n = dst.shape[0]
-            fused = {}
+        rest = grads
+        if dst.is_cuda and dst.dtype is torch.float32 and len(grads) > 1:
+            n, index = dst.shape[0], dst.get_device()
+            fused, rest = [], {}
             for name, value in grads.items():
-                off_numel = self._meta.get(name)
-                if (off_numel is not None and value.is_cuda and value.dtype is torch.float32
-                        and value.is_contiguous() and value.shape[0] == n
-                        and value.numel() == n * off_numel[1] and value.device == dst.device):
-                    fused[name] = value
+                window = self._windows.get(name)
+                if (window is not None and value.is_cuda and value.dtype is torch.float32
+                        and value.is_contiguous() and value.numel() == n * window[1]
+                        and value.get_device() == index):
+                    fused.append((value, window[0], window[1]))
+                else:
+                    rest[name] = value
             if len(fused) > 1:
                 from churten_b200.kernels._C import scatter_rows
 
-                scatter_rows(dst, [(v, *self._meta[k]) for k, v in fused.items()])
-                grads = {k: v for k, v in grads.items() if k not in fused}
-        for name, value in grads.items():
-            self._views[name].copy_(value)
+                scatter_rows(dst, fused)
+            else:
+                rest = grads
+        for name, value in rest.items():
+            self._view(name).copy_(value)
         return self
 
     def keys(self):
-        return self._views.keys()
+        return self._windows.keys()
 
     def __getitem__(self, key: str) -> torch.Tensor:
-        return self._views[key]
+        return self._view(key)
 
 
 class State:
@@ -242,6 +252,8 @@ class State:
         )
         for name, value in values.items():
             object.__setattr__(self, name, value)
+        # name -> (first column, columns) of every parameter, for the gradient scatter
+        object.__setattr__(self, "_windows", {k: (off, cnt) for k, _, off, cnt in values["param_meta"]})
         object.__setattr__(self, "_frozen", True)
 
     # -- frozen: fields are bound once; their tensors are mutated in place --------
@@ -292,8 +304,7 @@ class State:
 
     @property
     def _consolidated_grads(self) -> _GradViews:
-        return _GradViews(consolidated_dict_view(self.grads, self.param_meta), self.grads,
-                          self.param_meta)
+        return _GradViews(self.grads, self.param_meta, self._windows)
 
     # -- optimizer state ------------------------------------------------------------
     def like_tensor(self, value: Any = None, per_param: bool = False) -> torch.Tensor:

@@ -10,22 +10,29 @@
  * Conventions shared by every entry point
  * ---------------------------------------
  *  - All buffer pointers are DEVICE pointers on the CURRENT CUDA device.
- *    `params`, `grads` and the state buffers are fp32 `(n_rows, row_len)`
- *    matrices: row r is replica r, consolidated over all of its tensors.
+ *    `params`, `grads` and the state buffers are `(n_rows, row_len)` matrices of
+ *    the storage type named by `dtype` (CB200_F32, _F64, _F16, _BF16 -- the four
+ *    the reference dispatches, cuda/adam.cu:302-303): row r is replica r,
+ *    consolidated over all of its tensors.  Arithmetic is done in the MATH type:
+ *    fp32 for F32 / F16 / BF16 storage, fp64 for F64 storage; results are rounded
+ *    to nearest-even on the way back to storage.
  *  - `strides` is NULL for dense row-major buffers (row stride = row_len,
  *    element stride = 1); otherwise it points at HOST memory holding, for each
  *    buffer in argument order, the pair {row stride, element stride} counted in
- *    elements.  Dense, 16-byte aligned rows with `row_len % 4 == 0` take the
- *    128-bit streaming kernel; anything else takes the element-wise kernel.
+ *    elements.  Dense, 16-byte aligned rows whose length is a multiple of one
+ *    16-byte access (4 fp32, 8 fp16/bf16, 2 fp64 elements) take the 128-bit
+ *    streaming kernel; anything else takes the element-wise kernel.
  *  - `state_steps`, the hyper-parameter vectors and `active_mask` are dense
- *    `(n_rows,)` device vectors: fp32, and one byte per row (0 = frozen) for
- *    the mask.
- *  - `state_steps[r]` is incremented by 1.0f iff `active_mask[r]`, BEFORE the
- *    update math reads it, so a replica's first update sees step 1.  Frozen
- *    rows are never read or written: they stay byte-identical.
+ *    `(n_rows,)` device vectors: of the MATH type (float, or double for F64
+ *    storage), and one byte per row (0 = frozen) for the mask.
+ *  - `state_steps[r]` is incremented by 1 iff `active_mask[r]`, BEFORE the
+ *    update math reads it, so a replica's first update sees step 1 -- unless
+ *    `steps_already_bumped` is non-zero (a caller whose counter lives in another
+ *    type does the increment itself and passes a converted copy).  Frozen rows
+ *    are never read or written: they stay byte-identical.
  *  - `workspace` is device scratch of at least `cb200_workspace_bytes(n_rows)`
  *    bytes, 256-byte aligned, owned by the caller.  It holds the compacted list
- *    of active rows and one 32-byte record of per-row scalars per active row.
+ *    of active rows and one record of per-row scalars per active row.
  *    Two calls that may overlap on the GPU (different streams) need two
  *    workspaces.
  *  - `active_rows_hint` is the number of non-zero entries of `active_mask` if
@@ -49,6 +56,8 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+enum cb200_dtype { CB200_F32 = 0, CB200_F64 = 1, CB200_F16 = 2, CB200_BF16 = 3 };
 
 enum cb200_status {
   CB200_OK = 0,
@@ -81,13 +90,13 @@ size_t cb200_workspace_bytes(int64_t n_rows);
  * grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs (5 pairs; the last is ignored
  * without amsgrad).
  */
-int cb200_adam_step(float* params, const float* grads, float* exp_avgs,
-                    float* exp_avg_sqs, float* max_exp_avg_sqs,
-                    float* state_steps, const float* lr, const float* beta1,
-                    const float* beta2, const float* eps,
-                    const float* weight_decay, const uint8_t* active_mask,
-                    int64_t n_rows, int64_t row_len, const int64_t* strides,
-                    int amsgrad, int maximize, int decoupled_weight_decay,
+int cb200_adam_step(int dtype, void* params, const void* grads, void* exp_avgs,
+                    void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps,
+                    const void* lr, const void* beta1, const void* beta2,
+                    const void* eps, const void* weight_decay,
+                    const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                    const int64_t* strides, int amsgrad, int maximize,
+                    int decoupled_weight_decay, int steps_already_bumped,
                     int64_t active_rows_hint, void* workspace,
                     size_t workspace_bytes, void* stream);
 
@@ -103,27 +112,28 @@ int cb200_adam_step(float* params, const float* grads, float* exp_avgs,
  * row by row (an extension: the reference schema has one flag per call).
  * Strides order: params, grads, momentum_buffers (3 pairs).
  */
-int cb200_sgd_step(float* params, const float* grads, float* momentum_buffers,
-                   float* state_steps, const float* lr, const float* momentum,
-                   const float* dampening, const float* weight_decay,
+int cb200_sgd_step(int dtype, void* params, const void* grads, void* momentum_buffers,
+                   void* state_steps, const void* lr, const void* momentum,
+                   const void* dampening, const void* weight_decay,
                    const uint8_t* active_mask, const uint8_t* nesterov_rows,
                    int64_t n_rows, int64_t row_len, const int64_t* strides,
-                   int nesterov, int maximize, int64_t active_rows_hint,
-                   void* workspace, size_t workspace_bytes, void* stream);
+                   int nesterov, int maximize, int steps_already_bumped,
+                   int64_t active_rows_hint, void* workspace,
+                   size_t workspace_bytes, void* stream);
 
 /*
- * Fused Adagrad step; fp32 storage and accumulator, fp64 parameter update.
+ * Fused Adagrad step; accumulator in the math type, fp64 parameter update.
  * Replaces `adagrad_step_cuda` + `adagrad_step_kernel`
  * (src/torchstrap/kernels/csrc/cuda/adagrad.cu:238-283, :69-198) behind
  * `torchstrap::adagrad_step_` (stubs.cpp:61-72).
  * Strides order: params, grads, state_sums (3 pairs).
  */
-int cb200_adagrad_step(float* params, const float* grads, float* state_sums,
-                       float* state_steps, const float* lr,
-                       const float* lr_decay, const float* weight_decay,
-                       const float* eps, const uint8_t* active_mask,
-                       int64_t n_rows, int64_t row_len, const int64_t* strides,
-                       int maximize, int64_t active_rows_hint, void* workspace,
+int cb200_adagrad_step(int dtype, void* params, const void* grads, void* state_sums,
+                       void* state_steps, const void* lr, const void* lr_decay,
+                       const void* weight_decay, const void* eps,
+                       const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                       const int64_t* strides, int maximize, int steps_already_bumped,
+                       int64_t active_rows_hint, void* workspace,
                        size_t workspace_bytes, void* stream);
 
 /*
@@ -144,8 +154,9 @@ int cb200_scatter_rows(float* dst, int64_t dst_row_stride, int64_t dst_row_len,
                        const int64_t* part_row_strides, void* stream);
 
 /*
- * The Adam step for callers that may not allocate device memory: same arguments
- * and same results as cb200_adam_step, but no workspace is passed -- the scratch
+ * The Adam step (fp32 storage) for callers that may not allocate device memory:
+ * the arguments and results of cb200_adam_step(CB200_F32, ...) with the counter
+ * bumped in the call, but no workspace is passed -- the scratch
  * is a fixed array inside the library (590,080 bytes that every GPU loading the
  * library holds until the process exits).  Meant for plugins of hosts that gave
  * all device memory to their own arenas at start-up, or that forbid allocator

@@ -50,24 +50,24 @@ def test_version_and_workspace_bytes():
     lib = _lib.lib()
     assert lib.cb200_version() >= 100
     assert lib.cb200_workspace_bytes(0) == 256
-    # header + ids rounded to 256 + 32 bytes per row
-    assert lib.cb200_workspace_bytes(1) == 256 + 256 + 32
-    assert lib.cb200_workspace_bytes(100) == 256 + 512 + 3200
-    assert lib.cb200_workspace_bytes(8192) == 256 + 8192 * 4 + 8192 * 32
+    # header + ids rounded to 256 + 64 bytes per row (the fp64 record; fp32 uses half)
+    assert lib.cb200_workspace_bytes(1) == 256 + 256 + 64
+    assert lib.cb200_workspace_bytes(100) == 256 + 512 + 6400
+    assert lib.cb200_workspace_bytes(8192) == 256 + 8192 * 4 + 8192 * 64
 
 
 def test_argument_errors_need_no_gpu():
     lib = _lib.lib()
     # zero rows: nothing to do, no CUDA call is made
-    assert lib.cb200_adam_step(None, None, None, None, None, None, None, None, None, None, None,
-                               None, 0, 16, None, 0, 0, 1, -1, None, 0, None) == _lib.OK
+    assert lib.cb200_adam_step(_lib.F32, None, None, None, None, None, None, None, None, None, None,
+                               None, None, 0, 16, None, 0, 0, 1, 0, -1, None, 0, None) == _lib.OK
     # amsgrad without its buffer
-    rc = lib.cb200_adam_step(None, None, None, None, None, None, None, None, None, None, None,
-                             None, 4, 16, None, 1, 0, 1, -1, None, 0, None)
+    rc = lib.cb200_adam_step(_lib.BF16, None, None, None, None, None, None, None, None, None, None,
+                             None, None, 4, 16, None, 1, 0, 1, 0, -1, None, 0, None)
     assert rc == _lib.ERR_INVALID_ARGUMENT
     assert "max_exp_avg_sqs" in _lib.last_error()
-    rc = lib.cb200_sgd_step(None, None, None, None, None, None, None, None, None, None,
-                            4, 16, None, 1, 0, -1, None, 0, None)
+    rc = lib.cb200_sgd_step(_lib.F32, None, None, None, None, None, None, None, None, None, None,
+                            4, 16, None, 1, 0, 0, -1, None, 0, None)
     assert rc == _lib.ERR_INVALID_ARGUMENT and "nesterov" in _lib.last_error()
     with pytest.raises(RuntimeError, match="nesterov"):
         _lib.check(rc, "torchstrap::sgd_step_")

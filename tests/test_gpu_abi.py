@@ -37,9 +37,9 @@ def test_adam_through_ctypes_matches_the_operator(cuda):
     ref = [b.clone() for b in bufs]
     ref_steps = steps.clone()
     ws = torch.empty(lib.cb200_workspace_bytes(R), dtype=torch.uint8, device=cuda)
-    rc = lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+    rc = lib.cb200_adam_step(_lib.F32, _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
                              _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
-                             0, 0, 1, -1, _ptr(ws), ws.numel(), _stream())
+                             0, 0, 1, 0, -1, _ptr(ws), ws.numel(), _stream())
     assert rc == _lib.OK, _lib.last_error()
     torch.ops.torchstrap.adam_step_(ref[0], ref[1], ref[2], ref[3], None, ref_steps, *side, mask,
                                     amsgrad=False, maximize=False, decoupled_weight_decay=True)
@@ -57,18 +57,22 @@ def test_error_codes(cuda):
     before = [b.clone() for b in bufs]
     ws = torch.empty(lib.cb200_workspace_bytes(R) + 256, dtype=torch.uint8, device=cuda)
     common = lambda w, wbytes: lib.cb200_adam_step(
-        _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
-        *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, -1, w, wbytes, _stream())
+        _lib.F32, _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
+        *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, 0, -1, w, wbytes, _stream())
     assert common(None, 0) == _lib.ERR_WORKSPACE
     assert common(_ptr(ws), 16) == _lib.ERR_WORKSPACE and "too small" in _lib.last_error()
     assert common(ctypes.c_void_p(ws.data_ptr() + 8), ws.numel() - 8) == _lib.ERR_WORKSPACE
-    rc = lib.cb200_adam_step(None, _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
-                             *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, -1, _ptr(ws),
+    rc = lib.cb200_adam_step(_lib.F32, None, _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None, _ptr(steps),
+                             *[_ptr(s) for s in side], _ptr(mask), R, T, None, 0, 0, 1, 0, -1, _ptr(ws),
                              ws.numel(), _stream())
     assert rc == _lib.ERR_INVALID_ARGUMENT and "params" in _lib.last_error()
-    assert lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+    assert lib.cb200_adam_step(_lib.F32, _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
                                _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), -1, T, None,
-                               0, 0, 1, -1, _ptr(ws), ws.numel(), _stream()) == _lib.ERR_INVALID_ARGUMENT
+                               0, 0, 1, 0, -1, _ptr(ws), ws.numel(), _stream()) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.cb200_adam_step(7, _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+                               _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
+                               0, 0, 1, 0, -1, _ptr(ws), ws.numel(), _stream()) == _lib.ERR_INVALID_ARGUMENT
+    assert "dtype" in _lib.last_error()
     torch.cuda.synchronize()
     # a rejected call launches nothing: buffers and clock untouched
     for a, b in zip(bufs, before):
@@ -92,8 +96,11 @@ def test_operator_errors_are_runtime_errors(cuda):
     with pytest.raises(RuntimeError, match="nesterov"):
         ops.sgd_step_(bufs[0], bufs[1], None, steps, side[0], side[1], side[1], side[1], mask,
                       nesterov=True, maximize=False)
-    with pytest.raises(RuntimeError, match="float32"):
-        ops.adam_step_(bufs[0].double(), bufs[1].double(), bufs[2].double(), bufs[3].double(), None,
+    with pytest.raises(RuntimeError, match="storage must be"):
+        ops.adam_step_(bufs[0].to(torch.int32), bufs[1], bufs[2], bufs[3], None,
+                       steps, *side, mask, amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    with pytest.raises(RuntimeError, match="must be torch.float32"):
+        ops.adam_step_(bufs[0], bufs[1].double(), bufs[2], bufs[3], None,
                        steps, *side, mask, amsgrad=False, maximize=False, decoupled_weight_decay=True)
     cpu = [b.cpu() for b in bufs]
     from conftest import HAVE_REFERENCE
@@ -159,9 +166,9 @@ def test_active_rows_hint_never_changes_results(cuda, hint):
     ref = [b.clone() for b in bufs]
     ref_steps = steps.clone()
     ws = torch.empty(lib.cb200_workspace_bytes(R), dtype=torch.uint8, device=cuda)
-    rc = lib.cb200_adam_step(_ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
+    rc = lib.cb200_adam_step(_lib.F32, _ptr(bufs[0]), _ptr(bufs[1]), _ptr(bufs[2]), _ptr(bufs[3]), None,
                              _ptr(steps), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
-                             0, 0, 1, hint, _ptr(ws), ws.numel(), _stream())
+                             0, 0, 1, 0, hint, _ptr(ws), ws.numel(), _stream())
     assert rc == _lib.OK, _lib.last_error()
     torch.ops.torchstrap.adam_step_(ref[0], ref[1], ref[2], ref[3], None, ref_steps, *side, mask,
                                     amsgrad=False, maximize=False, decoupled_weight_decay=True)

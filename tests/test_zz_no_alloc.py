@@ -70,9 +70,9 @@ def test_static_scratch_matches_caller_workspace_on_two_calls_in_a_row(cuda, ams
             int(amsgrad), 0, 1, -1, _stream())
         assert rc == _lib.OK, _lib.last_error()
         rc = lib.cb200_adam_step(
-            _ptr(b[0]), _ptr(g), _ptr(b[2]), _ptr(b[3]), _ptr(b[4]) if amsgrad else None,
+            _lib.F32, _ptr(b[0]), _ptr(g), _ptr(b[2]), _ptr(b[3]), _ptr(b[4]) if amsgrad else None,
             _ptr(steps_b), *[_ptr(s) for s in side], _ptr(mask), R, T, None,
-            int(amsgrad), 0, 1, -1, _ptr(ws), ws.numel(), _stream())
+            int(amsgrad), 0, 1, 0, -1, _ptr(ws), ws.numel(), _stream())
         assert rc == _lib.OK, _lib.last_error()
     torch.cuda.synchronize()
 
@@ -115,8 +115,8 @@ def test_the_limit_itself_is_served(cuda):
         _ptr(mask), R, T, None, 0, 0, 0, -1, _stream())
     assert rc == _lib.OK, _lib.last_error()
     rc = lib.cb200_adam_step(
-        _ptr(b[0]), _ptr(b[1]), _ptr(b[2]), _ptr(b[3]), None, _ptr(sb), *[_ptr(s) for s in side],
-        _ptr(mask), R, T, None, 0, 0, 0, -1, _ptr(ws), ws.numel(), _stream())
+        _lib.F32, _ptr(b[0]), _ptr(b[1]), _ptr(b[2]), _ptr(b[3]), None, _ptr(sb), *[_ptr(s) for s in side],
+        _ptr(mask), R, T, None, 0, 0, 0, 0, -1, _ptr(ws), ws.numel(), _stream())
     assert rc == _lib.OK, _lib.last_error()
     torch.cuda.synchronize()
     for x, y in zip(a, b):
