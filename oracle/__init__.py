@@ -86,6 +86,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_set_cpu_fuse.restype = c_uint
         L.oracle_set_cpu_fuse.argtypes = [c_uint]
         L.oracle_default_cpu_fuse.restype = c_uint
+        L.oracle_set_storage.restype = c_int
+        L.oracle_set_storage.argtypes = [c_int]
         L.oracle_set_threads.restype = c_int
         L.oracle_set_threads.argtypes = [c_int]
         _lib = L
@@ -157,6 +159,14 @@ def set_cpu_fuse(mask: int) -> int:
 
 def default_cpu_fuse() -> int:
     return int(lib().oracle_default_cpu_fuse())
+
+
+STORE_F32, STORE_F16, STORE_BF16 = 0, 2, 3
+
+
+def set_storage(storage: int) -> int:
+    """Emulate fp16 / bf16 buffers in the CUDA formulation (see oracle.h); returns the old setting."""
+    return int(lib().oracle_set_storage(storage))
 
 
 def set_threads(n: int) -> int:

@@ -60,6 +60,24 @@ unsigned oracle_set_cpu_fuse(unsigned mask) {
 }
 unsigned oracle_default_cpu_fuse(void) { return ORACLE_DEFAULT_CPU_FUSE; }
 
+/* Storage type of the matrices, for the CUDA formulation: values are still handed
+ * over as floats, but every value written back is first rounded to nearest-even
+ * into the storage type and widened again, which is what a kernel that keeps
+ * fp16 / bf16 buffers and computes in fp32 does (ATen's opmath). */
+static int g_storage = ORACLE_STORE_F32;
+
+int oracle_set_storage(int storage) {
+  int old = g_storage;
+  g_storage = storage;
+  return old;
+}
+
+static inline float st(float x) {
+  if (g_storage == ORACLE_STORE_BF16) return (float)(__bf16)x;
+  if (g_storage == ORACLE_STORE_F16) return (float)(_Float16)x;
+  return x;
+}
+
 int oracle_set_threads(int n) {
 #ifdef _OPENMP
   if (n > 0) omp_set_num_threads(n);
@@ -143,16 +161,16 @@ static inline void adam_cuda_elem(float* p, float g, float* m, float* v, float* 
   float root;
   if (amsgrad) {
     const float x = std_max(*mx, ev);
-    *mx = x;
+    *mx = st(x);
     root = sqrtf(x);
   } else {
     root = sqrtf(ev);
   }
   const float denom = root / c->bc2_sqrt + c->eps;
   param = param - (c->step_size * em) / denom;
-  *p = param;
-  *m = em;
-  *v = ev;
+  *p = st(param);
+  *m = st(em);
+  *v = st(ev);
 }
 
 typedef struct {
@@ -295,10 +313,10 @@ static inline void sgd_cuda_elem(float* p, float g, float* buf, float lr, float 
     } else {
       b = fmaf(one_minus_damp, g, momentum * *buf);
     }
-    *buf = b;
+    *buf = st(b);
     g = nesterov ? fmaf(momentum, b, g) : b;
   }
-  *p = fmaf(-lr, g, param);
+  *p = st(fmaf(-lr, g, param));
 }
 
 typedef struct {
@@ -413,9 +431,9 @@ static inline void adagrad_cuda_elem(float* p, float g, float* sum, double clr, 
   if (maximize) g = -g;
   if (wd != 0.0) g = (float)fma((double)param, wd, (double)g);
   const float s = fmaf(g, g, *sum);
-  *sum = s;
+  *sum = st(s);
   const double denom = (double)sqrtf(s) + eps;
-  *p = (float)((double)param - (clr * (double)g) / denom);
+  *p = st((float)((double)param - (clr * (double)g) / denom));
 }
 
 typedef struct {

@@ -43,6 +43,12 @@ extern "C" {
 
 enum { ORACLE_FORM_CUDA = 0, ORACLE_FORM_CPU = 1 };
 
+/* Storage types the CUDA formulation can emulate on float matrices (values that the
+ * type represents exactly); fp32 math throughout, results rounded to nearest-even
+ * into the storage type.  Returns the previous setting. */
+enum { ORACLE_STORE_F32 = 0, ORACLE_STORE_F16 = 2, ORACLE_STORE_BF16 = 3 };
+int oracle_set_storage(int storage);
+
 typedef struct {
   float* ptr;
   int64_t stride_r;

@@ -11,6 +11,8 @@ Two fixture files, both small `.npz` archives:
       test_aten_*_parity.py) and therefore the bit-exact target of the sm_100a
       kernels.  Also the device's powf(beta, step) for every row, so that the
       CPU oracle can be compared bit for bit without depending on the host libm.
+  torch_fused_cuda_lowp.npz  the same for fp16 / bf16 storage (`--cuda-lowp`), values
+      widened exactly to fp32 for storage in the archive.
   reference_cpu.npz     outputs of the reference's own CPU kernels
       (oracle/_ref/torchstrap_ref_cpu.so built from its sources), the
       atol = rtol = 1e-5 target.
@@ -77,6 +79,40 @@ def all_cases():
     return list(adam_cases()) + list(sgd_cases()) + list(adagrad_cases())
 
 
+# Low-precision storage: fp16 / bf16 buffers, fp32 math.  Hyper-parameters are chosen to be
+# exact in both types (the operators read them through the storage type, as the reference does).
+LOWP = dict(lr=2.0 ** -7, beta1=0.875, beta2=0.96875, eps=2.0 ** -20, wd=2.0 ** -6,
+            momentum=0.875, dampening=0.25, lr_decay=2.0 ** -6)
+
+
+def lowp_cases():
+    out = []
+    for dtype in ("float16", "bfloat16"):
+        for r, t in ((3, 64), (3, 45)):
+            for amsgrad, adamw in ((False, True), (True, False)):
+                out.append(dict(opt="adam", dtype=dtype, r=r, t=t, amsgrad=amsgrad, adamw=adamw,
+                                maximize=False, wd=LOWP["wd"], beta1=LOWP["beta1"],
+                                beta2=LOWP["beta2"], eps=LOWP["eps"]))
+            for mom, damp, nesterov in ((0.0, 0.0, False), (LOWP["momentum"], LOWP["dampening"], False),
+                                        (LOWP["momentum"], 0.0, True)):
+                out.append(dict(opt="sgd", dtype=dtype, r=r, t=t, momentum=mom, dampening=damp,
+                                nesterov=nesterov, maximize=False, wd=LOWP["wd"]))
+            out.append(dict(opt="adagrad", dtype=dtype, r=r, t=t, lr_decay=LOWP["lr_decay"],
+                            wd=LOWP["wd"], eps=LOWP["eps"], maximize=True))
+    return out
+
+
+def lowp_inputs(case, index):
+    """`case_inputs` rounded into the case's storage type (held as exactly-widened floats)."""
+    dtype = getattr(torch, case["dtype"])
+    inp = case_inputs(case, 5000 + index)
+    for key, value in inp.items():
+        if value.dtype is torch.float32 and key not in ("steps0",):
+            inp[key] = value.to(dtype).float()
+    inp["lr"] = torch.tensor([2.0 ** -7, 2.0 ** -8, 2.0 ** -6][: case["r"]])
+    return inp
+
+
 def case_inputs(case, index):
     """Seeded, device-independent inputs of one case."""
     gen = torch.Generator().manual_seed(1000 + index)
@@ -104,12 +140,13 @@ STATE_KEYS = {"adam": ("exp_avgs", "exp_avg_sqs", "max_exp_avg_sqs"),
 def run_torch_fused(case, inp, dev):
     """torch's fused op, one call per active row per step (lr as a python float)."""
     r = case["r"]
-    p = inp["params"].to(dev).clone()
-    st = {k: inp[k].to(dev).clone() for k in STATE_KEYS[case["opt"]] if k in inp}
+    dtype = getattr(torch, case.get("dtype", "float32"))
+    p = inp["params"].to(dev, dtype).clone()
+    st = {k: inp[k].to(dev, dtype).clone() for k in STATE_KEYS[case["opt"]] if k in inp}
     steps = inp["steps0"].to(dev).clone()
     pows = torch.zeros(STEPS, r, 2)
     for it in range(STEPS):
-        g = inp["grads"][it].to(dev)
+        g = inp["grads"][it].to(dev, dtype)
         for row in range(r):
             if not inp["mask"][row]:
                 continue
@@ -138,8 +175,8 @@ def run_torch_fused(case, inp, dev):
                                       [steps[row]], lr=lr, lr_decay=case["lr_decay"],
                                       weight_decay=case["wd"], eps=case["eps"],
                                       maximize=case["maximize"], grad_scale=None, found_inf=None)
-    out = {"params": p.cpu(), "steps": steps.cpu(), "pows": pows}
-    out.update({k: v.cpu() for k, v in st.items()})
+    out = {"params": p.float().cpu(), "steps": steps.cpu(), "pows": pows}
+    out.update({k: v.float().cpu() for k, v in st.items()})
     return out
 
 
@@ -147,8 +184,9 @@ def op_args(case, inp, p, st, steps, g):
     """Positional arguments of torch.ops.torchstrap.<opt>_step_ for one step."""
     r = case["r"]
     dev = p.device
-    full = lambda x: torch.full((r,), x, dtype=torch.float32, device=dev)
-    lr, mask = inp["lr"].to(dev), inp["mask"].to(dev)
+    hyper = p.dtype if p.dtype in (torch.float16, torch.bfloat16) else torch.float32
+    full = lambda x: torch.full((r,), x, dtype=hyper, device=dev)
+    lr, mask = inp["lr"].to(dev, hyper), inp["mask"].to(dev)
     if case["opt"] == "adam":
         return (p, g, st["exp_avgs"], st["exp_avg_sqs"], st.get("max_exp_avg_sqs"), steps, lr,
                 full(case["beta1"]), full(case["beta2"]), full(case["eps"]), full(case["wd"]), mask,
@@ -164,13 +202,14 @@ def run_op(case, inp, dev, ops=None):
     """The consolidated op itself (reference CPU kernels on 'cpu', the sm_100a kernels on 'cuda')."""
     ops = ops or torch.ops.torchstrap
     op = getattr(ops, case["opt"] + "_step_")
-    p = inp["params"].to(dev).clone()
-    st = {k: inp[k].to(dev).clone() for k in STATE_KEYS[case["opt"]] if k in inp}
+    dtype = getattr(torch, case.get("dtype", "float32"))
+    p = inp["params"].to(dev, dtype).clone()
+    st = {k: inp[k].to(dev, dtype).clone() for k in STATE_KEYS[case["opt"]] if k in inp}
     steps = inp["steps0"].to(dev).clone()
     for it in range(STEPS):
-        op(*op_args(case, inp, p, st, steps, inp["grads"][it].to(dev)))
-    out = {"params": p.cpu(), "steps": steps.cpu()}
-    out.update({k: v.cpu() for k, v in st.items()})
+        op(*op_args(case, inp, p, st, steps, inp["grads"][it].to(dev, dtype)))
+    out = {"params": p.float().cpu(), "steps": steps.cpu()}
+    out.update({k: v.float().cpu() for k, v in st.items()})
     return out
 
 
@@ -199,6 +238,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--cuda", action="store_true")
     ap.add_argument("--cpu", action="store_true")
+    ap.add_argument("--cuda-lowp", action="store_true",
+                    help="on a GPU: torch's fused CUDA optimizers with fp16 / bf16 storage")
     ap.add_argument("--out-dir", default=str(HERE))
     args = ap.parse_args()
     cases = all_cases()
@@ -209,6 +250,13 @@ def main():
         outs = [run_torch_fused(c, case_inputs(c, i), dev) for i, c in enumerate(cases)]
         save(out_dir / "torch_fused_cuda.npz", cases, outs)
         print(f"wrote {len(cases)} cases to {out_dir / 'torch_fused_cuda.npz'} "
+              f"(torch {torch.__version__}, {torch.cuda.get_device_name(0)})")
+    if args.cuda_lowp:
+        dev = torch.device("cuda")
+        low = lowp_cases()
+        outs = [run_torch_fused(c, lowp_inputs(c, i), dev) for i, c in enumerate(low)]
+        save(out_dir / "torch_fused_cuda_lowp.npz", low, outs)
+        print(f"wrote {len(low)} cases to {out_dir / 'torch_fused_cuda_lowp.npz'} "
               f"(torch {torch.__version__}, {torch.cuda.get_device_name(0)})")
     if args.cpu:
         import oracle

@@ -194,7 +194,10 @@ def test_front_end_in_bf16(cuda):
     models = [Sequential(Linear(5, 3)).to(cuda).to(torch.bfloat16) for _ in range(3)]
     state = State.from_models(models)
     assert state.params.dtype is torch.bfloat16 and state.params.shape[1] == 24  # 18 -> 24
-    Adam.init(state, lr=2.0 ** -7, weight_decay=0.0)
+    # bf16 keeps 8 significant bits: the default beta2 = 0.999 would become 1.0 in the
+    # state's dtype (in the reference as well, whose State stores hyper-parameters in the
+    # parameter dtype), so a bf16 ensemble needs betas that bf16 can hold
+    Adam.init(state, lr=2.0 ** -7, beta1=B1, beta2=B2, eps=EPS, weight_decay=0.0)
     assert state.optimizer_state["exp_avgs"].dtype is torch.bfloat16
     before = state.params.clone()
     state.grads[:, :18] = 1.0

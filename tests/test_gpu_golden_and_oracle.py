@@ -218,3 +218,19 @@ def test_within_1e5_of_cpu_kernel_with_distinct_hparams(ops, cuda, opt, T):
     torch.cuda.synchronize()
     for a, b in zip(dev, bufs):
         torch.testing.assert_close(a.cpu(), b, rtol=1e-5, atol=1e-5)
+
+
+LOWP = mg.lowp_cases()
+
+
+@pytest.mark.parametrize("index", range(len(LOWP)), ids=lambda i: f"{i}-{LOWP[i]['opt']}-{LOWP[i]['dtype']}")
+def test_low_precision_storage_bit_exact_against_torch_fixtures(ops, cuda, index):
+    path = GOLDEN / "torch_fused_cuda_lowp.npz"
+    if not path.exists():
+        pytest.skip("tests/golden/torch_fused_cuda_lowp.npz not generated yet")
+    case = LOWP[index]
+    want = mg.load(path)[index]
+    got = mg.run_op(case, mg.lowp_inputs(case, index), cuda)
+    for name, value in want.items():
+        if name != "pows":
+            assert_bits_equal(f"{case}: {name}", got[name], value)

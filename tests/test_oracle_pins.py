@@ -144,3 +144,33 @@ def test_empty_and_degenerate_shapes():
         oracle.adagrad_step(oracle.CUDA_FORM, z(n, t), z(n, t), z(n, t), steps, v, v, v, v, mask, False)
         # the clock advances even when there is nothing to update (cuda/adam.cu:274-281)
         assert torch.equal(steps, torch.full((n,), 3.0))
+
+
+# ---------------------------------------------------------------------------
+# fp16 / bf16 storage: the CUDA formulation with its results rounded into the
+# storage type, against torch's fused CUDA optimizers run on fp16 / bf16 tensors
+# ---------------------------------------------------------------------------
+LOWP = mg.lowp_cases()
+
+
+@pytest.fixture(scope="module")
+def lowp_golden():
+    path = GOLDEN / "torch_fused_cuda_lowp.npz"
+    if not path.exists():
+        pytest.skip("tests/golden/torch_fused_cuda_lowp.npz not generated yet")
+    return mg.load(path)
+
+
+@pytest.mark.parametrize("index", range(len(LOWP)), ids=lambda i: f"{i}-{LOWP[i]['opt']}-{LOWP[i]['dtype']}")
+def test_cuda_form_with_low_precision_storage_matches_torch_fixtures(index, lowp_golden):
+    case = LOWP[index]
+    want = lowp_golden[index]
+    storage = oracle.STORE_F16 if case["dtype"] == "float16" else oracle.STORE_BF16
+    old = oracle.set_storage(storage)
+    try:
+        got = run_oracle(case, mg.lowp_inputs(case, index), oracle.CUDA_FORM, pows=want.get("pows"))
+    finally:
+        oracle.set_storage(old)
+    for name, value in want.items():
+        if name != "pows":
+            assert_bits_equal(f"{_ids(case)}: {name}", got[name], value)
