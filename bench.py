@@ -67,10 +67,15 @@ for _name, _shapes in (("c1", MLP_SHAPES), ("c2", MLP_SHAPES), ("c3", CNN_SHAPES
     WORKLOADS[_name]["shapes"] = _shapes
 
 
+ELEMENT_BYTES = {"f32": 4, "f64": 8, "f16": 2, "bf16": 2}
+
+
 def _bytes_per_elem(w) -> int:
+    """Algorithmic bytes per active element (fp32 storage figures scaled by the element size)."""
+    scale = ELEMENT_BYTES[w.get("dtype", "f32")]
     if w["opt"] == "adam":
-        return BYTES_PER_ELEM["adam_amsgrad" if w.get("amsgrad") else "adam"]
-    return BYTES_PER_ELEM[w["opt"]]
+        return BYTES_PER_ELEM["adam_amsgrad" if w.get("amsgrad") else "adam"] * scale // 4
+    return BYTES_PER_ELEM[w["opt"]] * scale // 4
 
 
 def _peak_gbs():
@@ -193,20 +198,25 @@ def build_state(w, n_rows, device, seed):
 
     gen = torch.Generator(device=device).manual_seed(seed)
     t = w["row_len"]
-    params = torch.empty(n_rows, t, device=device).normal_(0.0, 0.02, generator=gen)
-    grads = torch.empty(n_rows, t, device=device).normal_(0.0, 1e-3, generator=gen)
+    dtype = {"f32": torch.float32, "f64": torch.float64, "f16": torch.float16,
+             "bf16": torch.bfloat16}[w.get("dtype", "f32")]
+    params = torch.empty(n_rows, t, device=device, dtype=dtype).normal_(0.0, 0.02, generator=gen)
+    grads = torch.empty(n_rows, t, device=device, dtype=dtype).normal_(0.0, 1e-3, generator=gen)
     meta, offset = [], 0
     for i, shape in enumerate(w.get("shapes", [(t,)])):
         numel = math.prod(shape)
         meta.append((f"p{i}", torch.Size((n_rows, *shape)), offset, numel))
         offset += numel
-    assert offset <= t < offset + 4, (offset, t)
+    assert offset <= t < offset + 8, (offset, t)
     params[:, offset:] = 0  # alignment pad
     grads[:, offset:] = 0
-    state = State(params=params, buffers=torch.empty(n_rows, 0, device=device),
-                  param_meta=meta, buffer_meta=[], grads=grads)
+    state = State(params=params, buffers=torch.empty(n_rows, 0, device=device, dtype=dtype),
+                  param_meta=meta, buffer_meta=[], param_buffer_dtype=dtype, grads=grads)
     cls = {"adam": opts.Adam, "sgd": opts.SGD, "adagrad": opts.Adagrad}[w["opt"]]
-    cls.init(state, **_hyper(w, n_rows, gen, device))
+    hyper = _hyper(w, n_rows, gen, device)
+    if dtype in (torch.float16, torch.bfloat16) and w["opt"] == "adam":
+        hyper.update(beta1=0.875, beta2=0.96875, eps=2.0 ** -20)  # values the half types can hold
+    cls.init(state, **hyper)
     if w["frozen"] > 0:
         frozen = torch.rand(n_rows, device=device, generator=gen) < w["frozen"]
         state.active_mask.copy_(~frozen)
@@ -444,10 +454,9 @@ def run_ours(args, w, world, rank, local_rank):
 
     # ---- end to end: gradients from pinned host memory, step counters read back ----
     pin_rows = min(n_local, max(1, (1 << 30) // (t * 4)))
-    pinned = torch.empty(pin_rows, t, dtype=torch.float32).pin_memory()
-    pinned.normal_(0.0, 1e-3)
-    steps_host = torch.empty(n_local, dtype=torch.float32).pin_memory()
-    h2d = n_local * t * 4
+    pinned = torch.empty(pin_rows, t, dtype=torch.float32).normal_(0.0, 1e-3).to(state.grads.dtype).pin_memory()
+    steps_host = torch.empty(n_local, dtype=state.optimizer_state["state_steps"].dtype).pin_memory()
+    h2d = n_local * t * state.grads.element_size()
     d2h = n_local * 4
 
     def e2e_step():
@@ -481,7 +490,8 @@ def run_ours(args, w, world, rank, local_rank):
         peak, peak_kind = _peak_gbs()
         achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
         per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else ""))
-        traffic = per_elem * active_elems if per_elem is not None else None
+        # measured on fp32 storage; other storage types move proportionally fewer / more bytes
+        traffic = (per_elem * active_elems * ELEMENT_BYTES[args.dtype] / 4) if per_elem is not None else None
         line = {
             "metric": "param_updates_per_s",
             "value": job_elems * args.steps / (total_ms * 1e-3),
@@ -489,7 +499,7 @@ def run_ours(args, w, world, rank, local_rank):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
+            "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
                        "row_len": t, "active_rows_rank0": active_rows, "cuda_graph": bool(args.graph),
                        "apply_gradient": bool(args.apply_gradient),
@@ -536,6 +546,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference", "reference_cuda"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5_shard")
     ap.add_argument("--rows", type=int, default=0, help="override replicas per GPU (profiling small cases)")
+    ap.add_argument("--dtype", choices=sorted(ELEMENT_BYTES), default="f32",
+                    help="storage type of the (N, T) buffers (the headline metric is f32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--apply-gradient", action="store_true",
                     help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
@@ -549,6 +561,11 @@ def main():
     w = dict(WORKLOADS[args.workload])
     if args.rows:
         w["rows"] = args.rows
+    w["dtype"] = args.dtype
+    # rows are padded to 16 bytes by the State allocator: 8 elements for the 2-byte types
+    per_access = 16 // ELEMENT_BYTES[args.dtype]
+    if per_access > 4:
+        w["row_len"] += -w["row_len"] % per_access
     if args.impl == "reference":
         run_reference_arm(args, w, world, rank)
         return
