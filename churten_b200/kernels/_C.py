@@ -206,6 +206,11 @@ class _Call:
         self.n_rows, self.row_len = params.shape
         if state_steps.numel() != self.n_rows or active_mask.numel() != self.n_rows:
             raise RuntimeError(f"{op}: state_steps and active_mask must have one entry per row")
+        # every pointer handed to the library must be memory of params' device
+        if state_steps.device != self.device or active_mask.device != self.device:
+            raise RuntimeError(
+                f"{op}: state_steps is on {state_steps.device} and active_mask on "
+                f"{active_mask.device}, params on {self.device}")
         self.dtype, math = _DTYPES[params.dtype]
         # The bump lands in the caller's storage (a declared mutation).  A dense
         # counter of the math type is bumped by the prologue kernel; any other is
@@ -317,6 +322,8 @@ def sgd_step_cuda(
         lr_c, mom_c = _hyper(lr, params), _hyper(momentum, params)
         damp_c, wd_c = _hyper(dampening, params), _hyper(weight_decay, params)
         nrows_c = _mask(nesterov_rows) if nesterov_rows is not None else None
+        if nrows_c is not None and (nrows_c.device != params.device or nrows_c.numel() != call.n_rows):
+            raise RuntimeError(f"{op}: nesterov_rows must be a ({call.n_rows},) vector on {params.device}")
         status = _cb.cb200_sgd_step(
             call.dtype, params.data_ptr(), grads.data_ptr(),
             momentum_buffers.data_ptr() if momentum_buffers is not None else None,

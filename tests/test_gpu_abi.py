@@ -212,3 +212,21 @@ def test_hint_follows_mask_changes_through_the_operator(cuda):
     assert torch.equal(steps, ref_steps)
     slot = C._slots[(cuda.index or 0, torch.cuda.current_stream().cuda_stream)]
     assert slot.count == R  # the last mask (everything thawed) was counted on the device
+
+
+def test_side_inputs_on_another_device_are_refused(cuda):
+    """A host pointer must never reach the kernels: mask / counter / hyper-parameters on the
+    CPU raise before anything is launched."""
+    import churten_b200.kernels  # noqa: F401
+
+    ops = torch.ops.torchstrap
+    bufs, steps, side, mask = _adam_args(2, 8, cuda)
+    before = bufs[0].clone()
+    with pytest.raises(RuntimeError, match="active_mask on cpu"):
+        ops.adam_step_(bufs[0], bufs[1], bufs[2], bufs[3], None, steps, *side, mask.cpu(),
+                       amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    with pytest.raises(RuntimeError, match="hyper-parameter on cpu"):
+        ops.adam_step_(bufs[0], bufs[1], bufs[2], bufs[3], None, steps, side[0].cpu(), *side[1:], mask,
+                       amsgrad=False, maximize=False, decoupled_weight_decay=True)
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[0], before) and steps.abs().sum() == 0
