@@ -1,0 +1,70 @@
+"""Shared machinery of the three optimizer front-ends.
+
+Each optimizer is described by a small table: which `(N,)` hyper-parameters it
+keeps, which `(N, T)` state buffers (always present or created on a condition),
+which static flags, and in which order its operator wants them.  `populate` is
+what `Opt.init` does with that table, `step` what `Opt.update` does: gather the
+entries from `state.optimizer_state` and make ONE operator call over the whole
+ensemble (reference: src/torchstrap/optimizer/adam.py:33-112, sgd.py:45-113,
+adagrad.py:33-90).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+
+from churten_b200.state import State, _as_1d, _as_2d
+
+
+@dataclass(frozen=True)
+class FusedSpec:
+    op: Callable                       # the torch.ops.torchstrap.*_step_ handle
+    hypers: tuple[str, ...]            # (N,) vectors, in the operator's order
+    buffers: tuple[str, ...]           # (N, T) state buffers after params and grads, in order
+    optional: frozenset                # buffers that may be absent (passed as None)
+    flags: tuple[str, ...]             # static flags, in the operator's keyword order
+
+
+def populate(spec: FusedSpec, state: State, hypers: dict[str, Any], buffers: tuple[str, ...],
+             flags: dict[str, Any], extra_meta: dict[str, Any] | None = None) -> State:
+    """Fill `state.optimizer_state`: vectors (a scalar is broadcast), zeroed buffers, flags."""
+    for name in spec.hypers:
+        state.add_optim_state(name, hypers[name])
+    state.add_optim_state("state_steps", 0)
+    for name in buffers:
+        state.add_optim_state(name, per_param=True)
+    # flags are stored because `apply_gradient` calls `update(state)` without arguments
+    for name in spec.flags:
+        state.add_optim_meta(name, flags[name])
+    for name, value in (extra_meta or {}).items():
+        state.add_optim_meta(name, value)
+    return state
+
+
+def step(spec: FusedSpec, state: State, defaults: dict[str, Any]) -> State:
+    """One fused launch; flags stored by `init` win over the call's defaults."""
+    opt = state.optimizer_state
+    flags = {name: bool(opt.get(name, defaults[name])) for name in spec.flags}
+    buffers = []
+    for name in spec.buffers:
+        value = opt.get(name)
+        if value is None and name not in spec.optional:
+            raise KeyError(f"optimizer state has no {name!r}: was init() called?")
+        buffers.append(_as_2d(value) if value is not None else None)
+    spec.op(
+        _as_2d(state.flat_params),
+        _as_2d(state.flat_grads),
+        *buffers,
+        _as_1d(opt["state_steps"]),
+        *[_as_1d(opt[name]) for name in spec.hypers],
+        _as_1d(state.active_mask),
+        **flags,
+    )
+    return state
+
+
+def any_nonzero(value: float | torch.Tensor) -> bool:
+    return bool(torch.as_tensor(value).ne(0).any())

@@ -1,14 +1,23 @@
-"""`Adagrad` front-end (reference: src/torchstrap/optimizer/adagrad.py:18-90)."""
+"""`Adagrad` (reference: src/torchstrap/optimizer/adagrad.py:18-90)."""
 
 from __future__ import annotations
 
 import torch
 
 from churten_b200.kernels.adagrad import adagrad_step_
+from churten_b200.optimizer import _fused
 from churten_b200.optimizer.grad_transform import GradientTransformation
-from churten_b200.state import State, _as_1d, _as_2d
+from churten_b200.state import State
 
 __all__ = ["Adagrad", "adagrad_step_"]
+
+_SPEC = _fused.FusedSpec(
+    op=adagrad_step_,
+    hypers=("lr", "lr_decay", "weight_decay", "eps"),
+    buffers=("state_sums",),
+    optional=frozenset(),
+    flags=("maximize",),
+)
 
 
 class Adagrad(metaclass=GradientTransformation):
@@ -24,34 +33,16 @@ class Adagrad(metaclass=GradientTransformation):
         initial_accumulator_value: float | torch.Tensor = 0.0,
         maximize: bool = False,
     ) -> State:
-        for key, value in (("lr", lr), ("lr_decay", lr_decay), ("weight_decay", weight_decay),
-                           ("eps", eps), ("state_steps", 0)):
-            state.add_optim_state(key, value)
-        state.add_optim_state("state_sums", per_param=True)
-        # torch.optim.Adagrad seeds the accumulator with a constant; the fill covers
-        # the pad lanes too, which no view reaches and no gradient is written to.
+        _fused.populate(_SPEC, state, locals(), _SPEC.buffers, locals())
+        # torch.optim.Adagrad seeds the accumulator with a constant; the fill covers the
+        # pad lanes too, which no view reaches and no gradient is written to.
         sums = state.optimizer_state["state_sums"]
         if isinstance(initial_accumulator_value, torch.Tensor):
             sums.copy_(initial_accumulator_value.expand_as(sums))
         elif initial_accumulator_value != 0.0:
             sums.fill_(initial_accumulator_value)
-        state.add_optim_meta("maximize", maximize)
         return state
 
     @classmethod
     def update(cls, state: State, maximize: bool = False) -> State:
-        opt = state.optimizer_state
-        maximize = bool(opt.get("maximize", maximize))
-        adagrad_step_(
-            _as_2d(state.flat_params),
-            _as_2d(state.flat_grads),
-            _as_2d(opt["state_sums"]),
-            _as_1d(opt["state_steps"]),
-            _as_1d(opt["lr"]),
-            _as_1d(opt["lr_decay"]),
-            _as_1d(opt["weight_decay"]),
-            _as_1d(opt["eps"]),
-            _as_1d(state.active_mask),
-            maximize=maximize,
-        )
-        return state
+        return _fused.step(_SPEC, state, locals())

@@ -1,18 +1,23 @@
-"""`SGD` front-end (reference: src/torchstrap/optimizer/sgd.py:25-113)."""
+"""`SGD` with per-replica momentum (reference: src/torchstrap/optimizer/sgd.py:25-113)."""
 
 from __future__ import annotations
 
 import torch
 
 from churten_b200.kernels.sgd import sgd_step_
+from churten_b200.optimizer import _fused
 from churten_b200.optimizer.grad_transform import GradientTransformation
-from churten_b200.state import State, _as_1d, _as_2d
+from churten_b200.state import State
 
 __all__ = ["SGD", "sgd_step_"]
 
-
-def _any_nonzero(value: float | torch.Tensor) -> bool:
-    return bool(torch.as_tensor(value).ne(0).any())
+_SPEC = _fused.FusedSpec(
+    op=sgd_step_,
+    hypers=("lr", "momentum", "dampening", "weight_decay"),
+    buffers=("momentum_buffers",),
+    optional=frozenset({"momentum_buffers"}),
+    flags=("nesterov", "maximize"),
+)
 
 
 class SGD(metaclass=GradientTransformation):
@@ -29,38 +34,15 @@ class SGD(metaclass=GradientTransformation):
         maximize: bool = False,
     ) -> State:
         # torch.optim.SGD's validation, over the whole ensemble
-        if nesterov and (not _any_nonzero(momentum) or _any_nonzero(dampening)):
+        has_momentum = _fused.any_nonzero(momentum)
+        if nesterov and (not has_momentum or _fused.any_nonzero(dampening)):
             raise ValueError("Nesterov momentum requires a non-zero momentum and zero dampening")
-        for key, value in (("lr", lr), ("momentum", momentum), ("dampening", dampening),
-                           ("weight_decay", weight_decay), ("state_steps", 0)):
-            state.add_optim_state(key, value)
-        # The buffer exists for the whole ensemble as soon as one replica has
-        # momentum; its value stays per replica.
-        has_momentum = _any_nonzero(momentum)
-        if has_momentum:
-            state.add_optim_state("momentum_buffers", per_param=True)
-        state.add_optim_meta("nesterov", nesterov)
-        state.add_optim_meta("maximize", maximize)
-        state.add_optim_meta("has_momentum", has_momentum)
-        return state
+        # The buffer exists for the whole ensemble as soon as one replica has momentum;
+        # its value stays per replica (a replica with momentum 0 does plain SGD).
+        buffers = ("momentum_buffers",) if has_momentum else ()
+        return _fused.populate(_SPEC, state, locals(), buffers, locals(),
+                               extra_meta={"has_momentum": has_momentum})
 
     @classmethod
     def update(cls, state: State, nesterov: bool = False, maximize: bool = False) -> State:
-        opt = state.optimizer_state
-        nesterov = bool(opt.get("nesterov", nesterov))
-        maximize = bool(opt.get("maximize", maximize))
-        buffers = opt.get("momentum_buffers")
-        sgd_step_(
-            _as_2d(state.flat_params),
-            _as_2d(state.flat_grads),
-            _as_2d(buffers) if buffers is not None else None,
-            _as_1d(opt["state_steps"]),
-            _as_1d(opt["lr"]),
-            _as_1d(opt["momentum"]),
-            _as_1d(opt["dampening"]),
-            _as_1d(opt["weight_decay"]),
-            _as_1d(state.active_mask),
-            nesterov=nesterov,
-            maximize=maximize,
-        )
-        return state
+        return _fused.step(_SPEC, state, locals())

@@ -1,9 +1,9 @@
-"""`StatelessModule`: N replicas of one architecture run through `functional_call`.
+"""`StatelessModule`: N replicas of one architecture evaluated through `functional_call`.
 
-A thin restatement of the reference's src/torchstrap/stateless.py:45-137 -- just
-enough to build a `State` from a model and an optimizer and to evaluate the model
-on the consolidated views inside `vmap`.  Data-loading, dtype policies and the
-compiled-eval caches of the reference are not part of this library.
+Just enough of the reference's src/torchstrap/stateless.py:45-137 to build a `State`
+from a model and an optimizer and to run the model on the consolidated views inside
+`vmap`; the data-loading, dtype policies and compiled-eval caches of the reference
+are not part of this library.
 """
 
 from __future__ import annotations
@@ -19,28 +19,18 @@ from torch.nn import Module, ModuleList
 from churten_b200.state import State
 
 
-def _init_models(
-    model: Module | Callable[..., Module],
-    init_randomness: Literal["same", "different"],
-    *args: Any,
-    num_replicas: int = 1,
-    requires_grad: bool = False,
-    **kwargs: Any,
-) -> ModuleList:
-    if init_randomness == "different":
-        # N independently initialised replicas; an instance contributes its class
-        factory = type(model) if isinstance(model, Module) else model
-        return ModuleList(
-            factory(*args, **kwargs).requires_grad_(requires_grad) for _ in range(num_replicas)
-        )
-    if init_randomness == "same":
+def _replicas(model, how: str, args, kwargs, count: int, requires_grad: bool) -> ModuleList:
+    """`count` replicas: independently constructed ("different") or clones of one base ("same")."""
+    if how == "different":
+        build = type(model) if isinstance(model, Module) else model  # an instance lends its class
+        made = [build(*args, **kwargs) for _ in range(count)]
+    elif how == "same":
         base = model if isinstance(model, Module) else model(*args, **kwargs)
-        to_kwargs = {k: kwargs[k] for k in ("device", "dtype") if k in kwargs}
-        return ModuleList(
-            deepcopy(base).to(**to_kwargs).requires_grad_(requires_grad)
-            for _ in range(num_replicas)
-        )
-    raise ValueError(f"init_randomness must be 'same' or 'different', got {init_randomness!r}")
+        placement = {k: v for k, v in kwargs.items() if k in ("device", "dtype")}
+        made = [deepcopy(base).to(**placement) for _ in range(count)]
+    else:
+        raise ValueError(f"init_randomness must be 'same' or 'different', got {how!r}")
+    return ModuleList(m.requires_grad_(requires_grad) for m in made)
 
 
 class StatelessModule(Module):
@@ -61,13 +51,10 @@ class StatelessModule(Module):
         **kwargs,
     ):
         """-> `(module, state)`: the shared stateless module and the ensemble's `State`."""
-        models = _init_models(
-            model, init_randomness, *args,
-            num_replicas=num_replicas, requires_grad=requires_grad, **kwargs,
-        )
-        state = State.from_models(models)
+        replicas = _replicas(model, init_randomness, args, kwargs, num_replicas, requires_grad)
+        state = State.from_models(replicas)
         optimizer.init(state, **(optimizer_kwargs or {}))
-        return cls(models[0]), state
+        return cls(replicas[0]), state
 
     def forward(self, params: dict[str, Tensor], buffers: dict[str, Tensor], *args, **kwargs):
         return functional_call(self._base_model, (params, buffers), args, kwargs)
