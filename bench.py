@@ -554,6 +554,100 @@ TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {
 }
 
 
+def run_snapshot_leg(args, w):
+    """`--snapshot`: commit / restore of best rows (churten_b200.checkpoint.Snapshot) on one GPU.
+
+    Prints one JSON line: GB/s of state rows moved, for the one-launch masked row copy
+    (device -> pinned mirror, device -> device stage, pinned -> device restore), next to
+    a copy-engine transfer of the whole state and to the reference's procedure
+    (mask to host, index list, gather, staged copy, sync, host scatter;
+    callbacks/training.py:46-88) written with the same torch calls.
+    """
+    import torch
+
+    from churten_b200.checkpoint import Snapshot, _leaves
+
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    n = args.rows or min(w["rows"], 128)
+    state, _ = build_state(w, n, device, seed=0)
+    state.active_mask.fill_(True)
+    leaves = _leaves(state)
+    row_bytes = sum(t.numel() // n * t.element_size() for t in leaves.values())
+    snap = Snapshot(state, device_stage=True)
+    gen = torch.Generator(device=device).manual_seed(1)
+
+    def timed(fn, reps):
+        times = []
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e-3)
+        times.sort()
+        return times[len(times) // 2]
+
+    from churten_b200.kernels import _C
+
+    mirror, stage = snap._mirror, snap._stage
+    staging = {k: torch.empty_like(v).pin_memory() for k, v in mirror.items()}
+    results = {}
+    for fraction in (1.0, 0.25):
+        mask = torch.rand(n, device=device, generator=gen) < fraction if fraction < 1 else \
+            torch.ones(n, dtype=torch.bool, device=device)
+        k = int(mask.sum())
+        moved = k * row_bytes / 1e9
+
+        def to_mirror():
+            _C.copy_rows_masked([(mirror[name], leaf) for name, leaf in leaves.items()], mask, device)
+
+        def to_stage():
+            _C.copy_rows_masked([(stage[name], leaf) for name, leaf in leaves.items()], mask, device)
+
+        def from_mirror():
+            _C.copy_rows_masked([(leaf, mirror[name]) for name, leaf in leaves.items()], mask, device)
+
+        def reference_procedure():
+            idx_cpu = mask.to("cpu").nonzero(as_tuple=False).flatten()
+            idx_dev = idx_cpu.to(device)
+            for name, leaf in leaves.items():
+                staging[name][:k].copy_(leaf[idx_dev], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            for name in leaves:
+                mirror[name][idx_cpu] = staging[name][:k]
+
+        for fn in (to_mirror, to_stage, from_mirror):
+            fn()
+        tag = f"{fraction:g}"
+        results[tag] = {
+            "rows": k, "gb": round(moved, 3),
+            "device_to_pinned_gbs": round(moved / timed(to_mirror, args.steps), 2),
+            "device_to_stage_gbs": round(moved / timed(to_stage, args.steps), 1),
+            "pinned_to_device_gbs": round(moved / timed(from_mirror, args.steps), 2),
+        }
+        t0 = time.perf_counter()
+        reference_procedure()
+        reference_procedure()
+        results[tag]["reference_procedure_gbs"] = round(2 * moved / (time.perf_counter() - t0), 2)
+
+    def copy_engine():
+        for name, leaf in leaves.items():
+            mirror[name].copy_(leaf, non_blocking=True)
+
+    copy_engine()
+    whole = n * row_bytes / 1e9
+    results["copy_engine_whole_state_gbs"] = round(whole / timed(copy_engine, args.steps), 2)
+    print(json.dumps({
+        "metric": "snapshot_rows_moved", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "config": {"workload": f"{args.workload}: {n} replicas x {w['row_len']} {w['dtype']}, "
+                               f"{len(leaves)} leaves, {row_bytes} bytes per replica"},
+        "selected_fraction": results, "data": "synthetic",
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -569,6 +663,8 @@ def main():
                     help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
     ap.add_argument("--graph", action="store_true",
                     help="replay the step from a CUDA graph (churten_b200.graphs.GraphedUpdate)")
+    ap.add_argument("--snapshot", action="store_true",
+                    help="time the best-row snapshot (masked row copy) of the workload's state instead")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -587,6 +683,9 @@ def main():
         return
     if args.impl == "reference_cuda":
         run_reference_cuda_arm(args, w, world, rank, local_rank)
+        return
+    if args.snapshot:
+        run_snapshot_leg(args, w)
         return
     if args.gpus != world and world == 1 and args.gpus > 1:
         sys.exit("launch with torch.distributed.run for --gpus > 1")

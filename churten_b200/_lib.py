@@ -62,6 +62,11 @@ SIGNATURES = {
         # dst dst_row_stride dst_row_len n_rows n_parts parts offsets numels row_strides stream
         [_P, c_int64, c_int64, c_int64, c_int, _P, _P, _P, _P, _P],
     ),
+    "cb200_copy_rows_masked": (
+        c_int,
+        # n_leaves dst src row_bytes dst_strides src_strides row_mask invert_mask n_rows stream
+        [c_int, _P, _P, _P, _P, _P, _P, c_int, c_int64, _P],
+    ),
     "cb200_adam_step_static_scratch": (
         c_int,
         # the arguments of cb200_adam_step without workspace and workspace_bytes

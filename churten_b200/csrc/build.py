@@ -27,7 +27,8 @@ LIB = PKG / "libchurten_b200.so"
 PROBE_LIB = PKG / "libchurten_b200_probe.so"
 HBM_PROBE = PKG / "hbm_stream_probe"
 
-LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu", "scatter.cu"]
+LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu", "scatter.cu",
+               "rowcopy.cu"]
 PROBE_SOURCES = ["probe.cu"]
 HEADERS = ["rowmath.cuh", "stream.cuh", "contraction.h", "../../include/churten_b200.h"]
 

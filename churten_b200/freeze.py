@@ -20,8 +20,9 @@ Decision rule, replica by replica, identical to the reference's:
     done       = no replica is active any more
 
 Frozen replicas keep their counters and thresholds.  `best_epoch_` records the
-last epoch a replica improved.  Snapshots of best weights (the reference's
-`track_best`) are not part of this class.
+last epoch a replica improved.  With `track_best` the improved replicas' rows are
+committed to a pinned host mirror by one masked row-copy launch
+(`churten_b200.checkpoint.Snapshot`) and `restore_best` writes them back.
 """
 
 from __future__ import annotations
@@ -29,22 +30,11 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from churten_b200._flag import DeviceFlag
 
-class StopFlag:
-    """Result of one early-stopping call: a 0-dim bool tensor on the device.
 
-    `bool(flag)` synchronises (like the reference's return value); `flag.tensor`
-    does not, for callers that poll it later or combine it on the device.
-    """
-
-    def __init__(self, tensor: torch.Tensor):
-        self.tensor = tensor
-
-    def __bool__(self) -> bool:
-        return bool(self.tensor.item())
-
-    def __repr__(self) -> str:
-        return f"StopFlag({self.tensor!r})"
+class StopFlag(DeviceFlag):
+    """Result of one early-stopping call: "every replica is frozen"."""
 
 
 class EarlyStopping:
@@ -54,6 +44,7 @@ class EarlyStopping:
         threshold: float = 1e-4,
         threshold_mode: str = "rel",
         lower_is_better: bool = True,
+        track_best: bool = True,
         group=None,
     ):
         if threshold_mode not in ("rel", "abs"):
@@ -62,7 +53,9 @@ class EarlyStopping:
         self.threshold = float(threshold)
         self.threshold_mode = threshold_mode
         self.lower_is_better = bool(lower_is_better)
+        self.track_best = bool(track_best)
         self.group = group
+        self.best_weights_ = None
         self.misses_: torch.Tensor | None = None
         self.dynamic_threshold_: torch.Tensor | None = None
         self.best_epoch_: torch.Tensor | None = None
@@ -96,6 +89,12 @@ class EarlyStopping:
         moved = score - margin if self.lower_is_better else score + margin
         self.dynamic_threshold_ = torch.where(active, moved, threshold)
         self.best_epoch_ = torch.where(improved, torch.full_like(self.best_epoch_, self._epoch), self.best_epoch_)
+        if self.track_best:
+            if self.best_weights_ is None:
+                from churten_b200.checkpoint import Snapshot
+
+                self.best_weights_ = Snapshot(state)
+            self.best_weights_.update(state, improved)   # before the freeze below: gated by this epoch's mask
 
         newly_stopped = (self.misses_ >= self.patience) & active
         remaining = active & ~newly_stopped
@@ -110,9 +109,18 @@ class EarlyStopping:
             done = flag.to(torch.bool)
         return StopFlag(done)
 
+    @torch.no_grad()
+    def restore_best(self, state) -> None:
+        """Write back the best rows of every replica whose best epoch is not the last one
+        (the reference's `restore_best`, training.py:308-320).  The mask leaf is part of
+        a row, so a restored replica is active again, as in the reference."""
+        if self.best_weights_ is None or self.best_epoch_ is None:
+            return
+        self.best_weights_.restore_to_live(state, self.best_epoch_ != self._epoch - 1)
+
     def rearm(self, state) -> None:
         """Thaw every replica and forget the counters (the reference re-arms with
         `active_mask.fill_(True)`)."""
         state.active_mask.fill_(True)
-        self.misses_ = self.dynamic_threshold_ = self.best_epoch_ = None
+        self.misses_ = self.dynamic_threshold_ = self.best_epoch_ = self.best_weights_ = None
         self._epoch = 0

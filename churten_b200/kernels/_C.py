@@ -385,6 +385,53 @@ def scatter_rows(dst: torch.Tensor, parts: list[tuple[torch.Tensor, int, int]]) 
     _lib.check(status, "cb200_scatter_rows")
 
 
+def copy_rows_masked(pairs: list[tuple[torch.Tensor, torch.Tensor]], mask: torch.Tensor | None,
+                     device: torch.device, invert: bool = False) -> None:
+    """Copy the rows `mask` selects from `src` to `dst` for every `(dst, src)` pair, one launch
+    per 16 pairs (`cb200_copy_rows_masked`).
+
+    Every tensor is `(N, ...)` with dense rows; each side is on `device` or in pinned host
+    memory.  `mask` is a `(N,)` bool/uint8 tensor on `device`, or None for every row.
+    """
+    if not pairs:
+        return
+    n_rows = pairs[0][0].shape[0]
+    for dst, src in pairs:
+        if dst.shape != src.shape or dst.dtype != src.dtype or dst.shape[0] != n_rows:
+            raise ValueError("copy_rows_masked: a pair differs in shape, dtype or row count")
+        for t in (dst, src):
+            if t.numel() == 0:
+                continue   # nothing to address (and an empty host tensor is never "pinned")
+            if not (t.device == device or (t.device.type == "cpu" and t.is_pinned())):
+                raise ValueError(f"copy_rows_masked: a leaf is neither on {device} nor pinned")
+            if t.dim() > 1 and n_rows > 0 and t.numel() > 0 and not t[0].is_contiguous():
+                raise ValueError("copy_rows_masked: rows must be dense")
+    if mask is not None:
+        if mask.device != device or mask.dtype not in (torch.bool, torch.uint8):
+            raise ValueError(f"copy_rows_masked: the mask must be a bool/uint8 tensor on {device}")
+        if mask.numel() != n_rows or not mask.is_contiguous():
+            raise ValueError("copy_rows_masked: the mask must be a dense (N,) vector")
+    k = len(pairs)
+    row_bytes = [(d.numel() // n_rows if n_rows else 0) * d.element_size() for d, _ in pairs]
+
+    def stride(t: torch.Tensor) -> int:
+        # a single row has no meaningful stride(0): use its own length
+        elements = t.stride(0) if n_rows > 1 else t.numel()
+        return elements * t.element_size()
+
+    c_dst = (ctypes.c_void_p * k)(*[d.data_ptr() for d, _ in pairs])
+    c_src = (ctypes.c_void_p * k)(*[s.data_ptr() for _, s in pairs])
+    c_bytes = (ctypes.c_int64 * k)(*row_bytes)
+    c_dstride = (ctypes.c_int64 * k)(*[stride(d) for d, _ in pairs])
+    c_sstride = (ctypes.c_int64 * k)(*[stride(s) for _, s in pairs])
+    with torch.cuda.device(device):
+        status = _cb.cb200_copy_rows_masked(
+            k, c_dst, c_src, c_bytes, c_dstride, c_sstride,
+            mask.data_ptr() if mask is not None else None, int(invert), n_rows,
+            torch._C._cuda_getCurrentRawStream(device.index))
+    _lib.check(status, "cb200_copy_rows_masked")
+
+
 def launch_count() -> int:
     """Kernels launched by the step entry points in this process."""
     return int(_cb.cb200_launch_count())

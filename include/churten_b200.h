@@ -154,6 +154,27 @@ int cb200_scatter_rows(float* dst, int64_t dst_row_stride, int64_t dst_row_len,
                        const int64_t* part_row_strides, void* stream);
 
 /*
+ * Copy the selected rows of any number of row-major matrices ("leaves" of an
+ * ensemble state: parameters, moments, counters, the mask itself) with one launch
+ * per 16 leaves; row r of a source lands in row r of its destination.  Leaf k is
+ * n_rows rows of row_bytes[k] bytes, rows dst_row_stride_bytes[k] /
+ * src_row_stride_bytes[k] bytes apart; the five tables are HOST arrays of n_leaves
+ * entries.  `row_mask` is a DEVICE vector of n_rows bytes (a torch.bool tensor's
+ * storage) or NULL for every row; a row is copied when its byte is non-zero, or
+ * when it is zero if `invert_mask` is set.  Either side of a leaf may be device
+ * memory or page-locked host memory, so the call is the device->mirror update,
+ * the mirror->device restore and the on-device stage of a checkpoint alike; no
+ * host synchronisation, and the host never learns which rows moved.
+ * Replaces the gather / staged copy / host scatter of `Snapshot.update` and the
+ * indexed assignment of `Snapshot.restore_to_live`
+ * (src/torchstrap/callbacks/training.py:46-88, 90-117).
+ */
+int cb200_copy_rows_masked(int n_leaves, void* const* dst, const void* const* src,
+                           const int64_t* row_bytes, const int64_t* dst_row_stride_bytes,
+                           const int64_t* src_row_stride_bytes, const uint8_t* row_mask,
+                           int invert_mask, int64_t n_rows, void* stream);
+
+/*
  * The Adam step (fp32 storage) for callers that may not allocate device memory:
  * the arguments and results of cb200_adam_step(CB200_F32, ...) with the counter
  * bumped in the call, but no workspace is passed -- the scratch

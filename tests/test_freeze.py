@@ -57,7 +57,8 @@ def test_matches_the_reference_rule(mode, lower, patience):
         scores = -scores
     want = reference_rule(scores.tolist(), patience, 1e-2, mode, lower)
     state = _MaskOnly(n)
-    early = EarlyStopping(patience=patience, threshold=1e-2, threshold_mode=mode, lower_is_better=lower)
+    early = EarlyStopping(patience=patience, threshold=1e-2, threshold_mode=mode, lower_is_better=lower,
+                          track_best=False)
     for epoch in range(epochs):
         done = early(state, scores[epoch])
         mask, misses, thr, best, all_done = want[epoch]
@@ -74,7 +75,7 @@ def test_mask_is_updated_in_place_and_frozen_rows_hold_their_state():
     state = _MaskOnly(4)
     alias = state.active_mask
     state.active_mask[2] = False  # frozen from the start by someone else
-    early = EarlyStopping(patience=2, threshold=0.0, threshold_mode="abs")
+    early = EarlyStopping(patience=2, threshold=0.0, threshold_mode="abs", track_best=False)
     early(state, torch.tensor([1.0, 1.0, 1.0, 1.0]))
     early(state, torch.tensor([0.5, 2.0, 0.1, 2.0]))
     flag = early(state, torch.tensor([0.4, 3.0, 0.0, 3.0]))
@@ -92,7 +93,7 @@ def test_argument_checks():
     with pytest.raises(ValueError, match="threshold mode"):
         EarlyStopping(threshold_mode="ratio")
     with pytest.raises(ValueError, match="entries"):
-        EarlyStopping()(_MaskOnly(3), torch.zeros(4))
+        EarlyStopping(track_best=False)(_MaskOnly(3), torch.zeros(4))
 
 
 @pytest.mark.gpu
@@ -104,7 +105,7 @@ def test_runs_on_the_device_and_the_optimizer_honours_the_mask(cuda):
     models = [Sequential(Linear(4, 3)).to(cuda) for _ in range(5)]
     state = State.from_models(models)
     SGD.init(state, lr=0.1)
-    early = EarlyStopping(patience=1, threshold=0.0, threshold_mode="abs")
+    early = EarlyStopping(patience=1, threshold=0.0, threshold_mode="abs", track_best=False)
     early(state, torch.tensor([5.0, 4.0, 3.0, 2.0, 1.0], device=cuda))
     flag = early(state, torch.tensor([4.0, 9.0, 2.0, 9.0, 0.5], device=cuda))  # replicas 1 and 3 stall
     assert early.misses_.device.type == "cuda" and flag.tensor.device.type == "cuda"

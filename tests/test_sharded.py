@@ -75,7 +75,7 @@ def _worker(rank, world, port, n_rows, result_dir):
         class _S:
             active_mask = torch.ones(b - a, dtype=torch.bool)
 
-        early = EarlyStopping(patience=1, threshold=0.0, threshold_mode="abs")
+        early = EarlyStopping(patience=1, threshold=0.0, threshold_mode="abs", track_best=False)
         first = early(_S, torch.ones(b - a))
         # rank 0's replicas stall at once, rank 1's keep improving for one more epoch
         second = early(_S, torch.full((b - a,), 2.0 if rank == 0 else 0.5))
