@@ -9,7 +9,9 @@
 //     CTA per tile, and capped grids in between;
 //   * 128-bit (ld.global.v4) against 256-bit (ld.global.v8, sm_100) accesses;
 //   * default caching against streaming (.cs / L2::evict_first) hints;
-//   * pure reads and pure writes, as the ceilings.
+//   * pure reads and pure writes, as the ceilings;
+//   * the FP64 pipe (fused multiply-adds, IEEE divisions), the other candidate bound
+//     of the Adagrad formulation.
 //
 // Build:  python -m churten_b200.csrc.build --probe     Run:  churten_b200/hbm_stream_probe
 // Each buffer is 2 GiB (8-10 GiB on the device in total); every line is the
@@ -199,6 +201,25 @@ float median_ms(F launch) {
   return ts[ts.size() / 2];
 }
 
+// FP64 pipe ceilings for the Adagrad formulation: kChains independent dependent
+// chains per thread of fused multiply-adds, or of IEEE divisions.
+constexpr int kChains = 8;
+
+template <bool DIVIDE>
+__global__ void __launch_bounds__(256) fp64_chain_kernel(double* out, int iters, double a, double b) {
+  double x[kChains];
+#pragma unroll
+  for (int c = 0; c < kChains; ++c) x[c] = 1.0 + 1e-3 * (threadIdx.x + c);
+  for (int i = 0; i < iters; ++i) {
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) x[c] = DIVIDE ? __ddiv_rn(a, x[c]) + b : __fma_rn(x[c], a, b);
+  }
+  double sum = 0.0;
+#pragma unroll
+  for (int c = 0; c < kChains; ++c) sum += x[c];
+  if (sum == 123456.789) out[0] = sum;  // never true: keeps the chains alive
+}
+
 int main() {
   const int64_t n = static_cast<int64_t>(1) << 29;  // 2 GiB per buffer
   Ptrs d;
@@ -258,5 +279,16 @@ int main() {
   RUN128(5, 4, 1, 1, 256, 0); RUN128(5, 4, 2, 1, 512, -2);
   RUN128(3, 2, 1, 1, 256, 0); RUN128(3, 2, 2, 1, 512, -2);
   RUN128(2, 1, 1, 1, 256, 0);
+  // FP64 pipe: fused multiply-adds and divisions per second over the whole GPU
+  {
+    double* sink = reinterpret_cast<double*>(d.p[0]);
+    const int grid = sms * 8, iters = 1 << 15;
+    const double ops = static_cast<double>(grid) * 256 * kChains * iters;
+    float ms = median_ms([&] { fp64_chain_kernel<false><<<grid, 256>>>(sink, iters, 0.999, 1e-3); });
+    std::printf("fp64 dfma grid %d: %.3f ms, %.2f T fma/s (%.1f TFLOP/s)\n", grid, ms, ops / ms / 1e9,
+                2 * ops / ms / 1e9);
+    ms = median_ms([&] { fp64_chain_kernel<true><<<grid, 256>>>(sink, iters / 8, 1.5, 1e-3); });
+    std::printf("fp64 ddiv+dadd grid %d: %.3f ms, %.3f T div/s\n", grid, ms, ops / 8 / ms / 1e9);
+  }
   return 0;
 }

@@ -206,7 +206,7 @@ int cb200_adam_step_static_scratch(
  * Launch geometry of the streaming kernels, for benchmarking sweeps.
  * `threads` in {128, 256, 512} and `unroll` in {1, 2, 4} 16-byte accesses per
  * thread per buffer per tile; -1 restores the default, which is per optimizer
- * (Adam and SGD 256 x 1, Adagrad 128 x 2);
+ * and storage type (fp32: Adam and SGD 256 x 1, Adagrad 128 x 2);
  * `ctas_per_sm` > 0 runs a persistent grid of (SM count x ctas_per_sm) CTAs that
  * stride over the work, -1 restores the default of one CTA per tile.  0 keeps a
  * field as it is.  Process-wide and not synchronised: set it before launching,
