@@ -659,6 +659,59 @@ def run_snapshot_leg(args, w):
     }))
 
 
+def run_lr_schedule_leg(args):
+    """`--lr-schedule`: one tick of each learning-rate policy over N replicas on one GPU,
+    the one-launch kernel (cb200_lr_schedule) against the chain of (N,) tensor expressions
+    the reference issues (callbacks/lr_scheduler.py); wall-clock microseconds per tick with a
+    synchronisation at the end of the series, i.e. what a training loop pays per batch."""
+    import types
+
+    import torch
+
+    from churten_b200 import lr_schedule
+    from churten_b200.kernels import _C
+
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    n = args.rows or 1024
+
+    class TensorPath(lr_schedule.LRScheduler):
+        def _launch(self, *a):
+            return False
+
+    policies = {
+        "StepLR": dict(step_size=5), "MultiStepLR": dict(milestones=[10, 20, 30]),
+        "ExponentialLR": dict(gamma=0.99), "CosineAnnealingLR": dict(T_max=100),
+        "WarmRestartLR": dict(), "ReduceLROnPlateau": dict(patience=2),
+    }
+    ticks = max(args.steps, 20)
+    out = {}
+    for name, kwargs in policies.items():
+        row = {}
+        for label, cls in (("one_launch", lr_schedule.LRScheduler), ("tensor_expressions", TensorPath)):
+            state = types.SimpleNamespace(
+                optimizer_state={"lr": torch.full((n,), 1e-3, device=device)},
+                active_mask=torch.rand(n, device=device) < 0.9)
+            sched = cls(name, **kwargs)
+            score = torch.rand(n, device=device)
+            needs = getattr(lr_schedule, name).needs_score
+            for _ in range(3):
+                sched(state, score=score if needs else None)
+            torch.cuda.synchronize()
+            launches = _C.launch_count()
+            t0 = time.perf_counter()
+            for _ in range(ticks):
+                sched(state, score=score if needs else None)
+            torch.cuda.synchronize()
+            row[label + "_us"] = round((time.perf_counter() - t0) / ticks * 1e6, 1)
+            if label == "one_launch":
+                row["launches_per_tick"] = (_C.launch_count() - launches) / ticks
+        out[name] = row
+    print(json.dumps({"metric": "lr_schedule_tick", "unit": "us/tick (host wall clock, synchronised series)",
+                      "n_gpus": 1, "ticks": ticks, "config": {"workload": f"{n} replicas, 90 % active"},
+                      "policies": out}))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -676,6 +729,8 @@ def main():
                     help="replay the step from a CUDA graph (churten_b200.graphs.GraphedUpdate)")
     ap.add_argument("--no-l2-flush", action="store_true",
                     help="small workloads: do not evict L2 between timed steps")
+    ap.add_argument("--lr-schedule", action="store_true",
+                    help="time one tick of each learning-rate policy (one launch vs tensor expressions) instead")
     ap.add_argument("--snapshot", action="store_true",
                     help="time the best-row snapshot (masked row copy) of the workload's state instead")
     args = ap.parse_args()
@@ -699,6 +754,9 @@ def main():
         return
     if args.snapshot:
         run_snapshot_leg(args, w)
+        return
+    if args.lr_schedule:
+        run_lr_schedule_leg(args)
         return
     if args.gpus != world and world == 1 and args.gpus > 1:
         sys.exit("launch with torch.distributed.run for --gpus > 1")

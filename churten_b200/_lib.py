@@ -67,6 +67,11 @@ SIGNATURES = {
         # n_leaves dst src row_bytes dst_strides src_strides row_mask invert_mask n_rows stream
         [c_int, _P, _P, _P, _P, _P, _P, c_int, c_int64, _P],
     ),
+    "cb200_lr_schedule": (
+        c_int,
+        # policy base_lrs clock lr active_mask lower upper best num_bad cooldown_counter score n stream
+        [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P],
+    ),
     "cb200_adam_step_static_scratch": (
         c_int,
         # the arguments of cb200_adam_step without workspace and workspace_bytes
@@ -97,6 +102,24 @@ PROBE_SIGNATURES = {
     ),
     "cb200_probe_powf": (c_int, [_P, _P, _P, c_int64, _P]),
 }
+
+
+# enum cb200_lr_kind
+LR_STEP, LR_MULTISTEP, LR_EXPONENTIAL, LR_COSINE, LR_WARM_RESTART, LR_PLATEAU = range(6)
+LR_MAX_MILESTONES = 32
+
+
+class LrPolicy(ctypes.Structure):
+    """struct cb200_lr_policy."""
+
+    _fields_ = [
+        ("kind", c_int), ("gamma", c_double), ("step_size", c_double), ("t_max", c_double),
+        ("eta_min", c_double), ("base_period", c_double), ("period_mult", c_double),
+        ("max_restarts", c_int), ("n_milestones", c_int),
+        ("milestones", c_double * LR_MAX_MILESTONES),
+        ("mode_max", c_int), ("threshold_rel", c_int), ("threshold", c_double),
+        ("factor", c_double), ("patience", c_double), ("cooldown", c_double),
+    ]
 
 
 class LibraryMissing(ImportError):

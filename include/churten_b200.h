@@ -175,6 +175,58 @@ int cb200_copy_rows_masked(int n_leaves, void* const* dst, const void* const* sr
                            int invert_mask, int64_t n_rows, void* stream);
 
 /*
+ * One tick of a per-replica learning-rate schedule, in one launch: for every
+ * replica r,  clock[r] += active_mask[r];  lr[r] = policy(clock[r], ...).
+ * All vectors are fp32 DEVICE vectors of n_rows entries; `active_mask` is n_rows
+ * bytes.  Which vectors a policy reads (the others may be NULL):
+ *   STEP, MULTISTEP, EXPONENTIAL, COSINE   base_lrs (the rates captured at the start)
+ *   WARM_RESTART                           lower, upper (per-replica min and max rate)
+ *   PLATEAU                                lower (min rate), score, and the state
+ *                                          vectors best / num_bad / cooldown_counter,
+ *                                          updated in place; frozen replicas keep their
+ *                                          state and their rate
+ * The scalars of `policy` are the Python numbers of the reference's constructors;
+ * the arithmetic reproduces, operation by operation, what the reference's tensor
+ * expressions compute on a CUDA device, so the rates are identical bit for bit.
+ * Replaces `LRScheduler.__call__` with the policies StepLR, MultiStepLR,
+ * ExponentialLR, CosineAnnealingLR, WarmRestartLR and ReduceLROnPlateau
+ * (src/torchstrap/callbacks/lr_scheduler.py:70-110, 132-274, 322-354), which issue
+ * 10 to about 260 launches per tick.
+ */
+enum cb200_lr_kind {
+  CB200_LR_STEP = 0,          /* base * gamma ** floor(t / step_size) */
+  CB200_LR_MULTISTEP = 1,     /* base * gamma ** #{milestones <= t} */
+  CB200_LR_EXPONENTIAL = 2,   /* base * gamma ** t */
+  CB200_LR_COSINE = 3,        /* eta_min + 0.5 (base - eta_min) (1 + cos(pi t / t_max)) */
+  CB200_LR_WARM_RESTART = 4,  /* cosine between lower and upper with periods base_period * period_mult^k */
+  CB200_LR_PLATEAU = 5        /* lr = max(lr * factor, lower) after more than `patience` bad ticks */
+};
+#define CB200_LR_MAX_MILESTONES 32
+typedef struct cb200_lr_policy {
+  int kind;
+  double gamma;
+  double step_size;
+  double t_max;
+  double eta_min;
+  double base_period;
+  double period_mult;
+  int max_restarts;
+  int n_milestones;
+  double milestones[CB200_LR_MAX_MILESTONES];  /* ascending */
+  int mode_max;        /* PLATEAU: 0 = lower score is better, 1 = higher */
+  int threshold_rel;   /* PLATEAU: 1 = relative threshold, 0 = absolute */
+  double threshold;
+  double factor;
+  double patience;
+  double cooldown;
+} cb200_lr_policy;
+int cb200_lr_schedule(const cb200_lr_policy* policy, const float* base_lrs, float* clock,
+                      float* lr, const uint8_t* active_mask, const float* lower,
+                      const float* upper, float* best, float* num_bad,
+                      float* cooldown_counter, const float* score, int64_t n_rows,
+                      void* stream);
+
+/*
  * The Adam step (fp32 storage) for callers that may not allocate device memory:
  * the arguments and results of cb200_adam_step(CB200_F32, ...) with the counter
  * bumped in the call, but no workspace is passed -- the scratch
