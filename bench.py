@@ -410,8 +410,12 @@ def run_ours(args, w, world, rank, local_rank):
         # are scattered into the consolidated buffer, then the fused step runs
         part_grads = {name: state.grads[:, off:off + numel].reshape(shape).contiguous()
                       for name, shape, off, numel in state.param_meta}
-        update = (lambda: opt.apply_gradient(state, part_grads))
-        bpe += 8
+        if args.in_place_grads:
+            # the step reads the gradient tensors where they are: no consolidated copy
+            update = (lambda: opt.apply_gradient(state, part_grads, materialize=False))
+        else:
+            update = (lambda: opt.apply_gradient(state, part_grads))
+            bpe += 8
     if args.graph:
         from churten_b200.graphs import GraphedUpdate
 
@@ -526,6 +530,7 @@ def run_ours(args, w, world, rank, local_rank):
             "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
                        "row_len": t, "active_rows_rank0": active_rows, "cuda_graph": bool(args.graph),
                        "apply_gradient": bool(args.apply_gradient),
+                       "in_place_grads": bool(args.apply_gradient and args.in_place_grads),
                        "l2": "inputs larger than L2 (no flush needed)"
                              if not fits_l2 else ("working set fits in L2: not flushed (warm figure)"
                                                   if flush_buf is None else
@@ -725,6 +730,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--apply-gradient", action="store_true",
                     help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
+    ap.add_argument("--in-place-grads", action="store_true",
+                    help="with --apply-gradient: apply_gradient(..., materialize=False)")
     ap.add_argument("--graph", action="store_true",
                     help="replay the step from a CUDA graph (churten_b200.graphs.GraphedUpdate)")
     ap.add_argument("--no-l2-flush", action="store_true",

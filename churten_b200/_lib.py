@@ -57,6 +57,22 @@ SIGNATURES = {
          # workspace workspace_bytes stream
          _P, c_size_t, _P],
     ),
+    "cb200_adam_step_from_parts": (
+        c_int,
+        # the arguments of cb200_adam_step with `grads` replaced by a cb200_grad_parts*
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_int64, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P],
+    ),
+    "cb200_sgd_step_from_parts": (
+        c_int,
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, _P, c_int, c_int,
+         c_int, c_int64, _P, c_size_t, _P],
+    ),
+    "cb200_adagrad_step_from_parts": (
+        c_int,
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, _P, c_int, c_int, c_int64,
+         _P, c_size_t, _P],
+    ),
     "cb200_scatter_rows": (
         c_int,
         # dst dst_row_stride dst_row_len n_rows n_parts parts offsets numels row_strides stream
@@ -107,6 +123,21 @@ PROBE_SIGNATURES = {
 # enum cb200_lr_kind
 LR_STEP, LR_MULTISTEP, LR_EXPONENTIAL, LR_COSINE, LR_WARM_RESTART, LR_PLATEAU = range(6)
 LR_MAX_MILESTONES = 32
+
+
+MAX_GRAD_PARTS = 96
+
+
+class GradPartsTable(ctypes.Structure):
+    """struct cb200_grad_parts."""
+
+    _fields_ = [
+        ("n_parts", c_int),
+        ("ptr", c_void_p * MAX_GRAD_PARTS),
+        ("row_stride", c_int64 * MAX_GRAD_PARTS),
+        ("offset", c_int64 * MAX_GRAD_PARTS),
+        ("numel", c_int64 * MAX_GRAD_PARTS),
+    ]
 
 
 class LrPolicy(ctypes.Structure):

@@ -57,6 +57,7 @@ struct AdagradArgs {
   void* workspace;
   size_t workspace_bytes;
   cudaStream_t stream;
+  const cb200_grad_parts* parts;
 };
 
 template <class T>
@@ -71,26 +72,34 @@ int adagrad_run(const AdagradArgs& a) {
                               static_cast<const M*>(a.weight_decay), static_cast<const M*>(a.eps)};
   return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
                                  a.row_len, a.flags, a.bump, a.hint, a.workspace,
-                                 a.workspace_bytes, a.stream);
+                                 a.workspace_bytes, a.stream, a.parts);
 }
 
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_adagrad_step(int dtype, void* params, const void* grads, void* state_sums,
+namespace cb200 {
+namespace {
+
+int adagrad_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts,
+                  void* state_sums,
                                   void* state_steps, const void* lr, const void* lr_decay,
                                   const void* weight_decay, const void* eps,
                                   const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
                                   const int64_t* strides, int maximize, int steps_already_bumped,
                                   int64_t active_rows_hint, void* workspace,
                                   size_t workspace_bytes, void* stream) {
-  using namespace cb200;
   if (n_rows > 0 && (!lr || !lr_decay || !weight_decay || !eps)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }
+  if (parts) {
+    if (int rc = check_grad_parts(parts, row_len)) return rc;
+  }
   AdagradArgs a;
+  a.parts = parts;
   a.ptrs[0] = params;
-  a.ptrs[1] = const_cast<void*>(grads);
+  // with parts the gradient slot is never dereferenced; any non-NULL value passes the table checks
+  a.ptrs[1] = parts ? params : const_cast<void*>(grads);
   a.ptrs[2] = state_sums;
   a.state_steps = state_steps;
   a.lr = lr;
@@ -114,4 +123,33 @@ extern "C" int cb200_adagrad_step(int dtype, void* params, const void* grads, vo
     case kBF16: return adagrad_run<__nv_bfloat16>(a);
     default: return fail(CB200_ERR_INVALID_ARGUMENT, "dtype must be CB200_F32, _F64, _F16 or _BF16");
   }
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" int cb200_adagrad_step(int dtype, void* params, const void* grads, void* state_sums,
+                                  void* state_steps, const void* lr, const void* lr_decay,
+                                  const void* weight_decay, const void* eps,
+                                  const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                                  const int64_t* strides, int maximize, int steps_already_bumped,
+                                  int64_t active_rows_hint, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  return cb200::adagrad_entry(dtype, params, grads, nullptr, state_sums, state_steps, lr, lr_decay,
+                              weight_decay, eps, active_mask, n_rows, row_len, strides, maximize,
+                              steps_already_bumped, active_rows_hint, workspace, workspace_bytes,
+                              stream);
+}
+
+extern "C" int cb200_adagrad_step_from_parts(
+    int dtype, void* params, const cb200_grad_parts* grad_parts, void* state_sums,
+    void* state_steps, const void* lr, const void* lr_decay, const void* weight_decay,
+    const void* eps, const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+    const int64_t* strides, int maximize, int steps_already_bumped, int64_t active_rows_hint,
+    void* workspace, size_t workspace_bytes, void* stream) {
+  if (!grad_parts) return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "grad_parts must not be NULL");
+  return cb200::adagrad_entry(dtype, params, nullptr, grad_parts, state_sums, state_steps, lr,
+                              lr_decay, weight_decay, eps, active_mask, n_rows, row_len, strides,
+                              maximize, steps_already_bumped, active_rows_hint, workspace,
+                              workspace_bytes, stream);
 }

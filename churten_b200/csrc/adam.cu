@@ -60,6 +60,7 @@ struct AdamArgs {
   void* workspace;
   size_t workspace_bytes;
   cudaStream_t stream;
+  const cb200_grad_parts* parts;
 };
 
 template <class T, bool AMSGRAD, bool ADAMW>
@@ -76,7 +77,7 @@ int adam_run(const AdamArgs& a) {
                            static_cast<const M*>(a.weight_decay)};
   return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
                                  a.row_len, a.flags, a.bump, a.hint, a.workspace,
-                                 a.workspace_bytes, a.stream);
+                                 a.workspace_bytes, a.stream, a.parts);
 }
 
 template <class T>
@@ -88,7 +89,10 @@ int adam_variant(const AdamArgs& a) {
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_adam_step(int dtype, void* params, const void* grads, void* exp_avgs,
+namespace cb200 {
+namespace {
+
+int adam_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts, void* exp_avgs,
                                void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps,
                                const void* lr, const void* beta1, const void* beta2,
                                const void* eps, const void* weight_decay,
@@ -97,7 +101,6 @@ extern "C" int cb200_adam_step(int dtype, void* params, const void* grads, void*
                                int decoupled_weight_decay, int steps_already_bumped,
                                int64_t active_rows_hint, void* workspace,
                                size_t workspace_bytes, void* stream) {
-  using namespace cb200;
   // (an empty matrix has no storage, so a NULL there says nothing)
   if (amsgrad && !max_exp_avg_sqs && n_rows > 0 && row_len > 0) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "amsgrad=True requires max_exp_avg_sqs");
@@ -105,9 +108,14 @@ extern "C" int cb200_adam_step(int dtype, void* params, const void* grads, void*
   if (n_rows > 0 && (!lr || !beta1 || !beta2 || !eps || !weight_decay)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }
+  if (parts) {
+    if (int rc = check_grad_parts(parts, row_len)) return rc;
+  }
   AdamArgs a;
+  a.parts = parts;
   a.ptrs[0] = params;
-  a.ptrs[1] = const_cast<void*>(grads);
+  // with parts the gradient slot is never dereferenced; any non-NULL value passes the table checks
+  a.ptrs[1] = parts ? params : const_cast<void*>(grads);
   a.ptrs[2] = exp_avgs;
   a.ptrs[3] = exp_avg_sqs;
   a.ptrs[4] = max_exp_avg_sqs;
@@ -136,4 +144,38 @@ extern "C" int cb200_adam_step(int dtype, void* params, const void* grads, void*
     case kBF16: return adam_variant<__nv_bfloat16>(a);
     default: return fail(CB200_ERR_INVALID_ARGUMENT, "dtype must be CB200_F32, _F64, _F16 or _BF16");
   }
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" int cb200_adam_step(int dtype, void* params, const void* grads, void* exp_avgs,
+                               void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps,
+                               const void* lr, const void* beta1, const void* beta2,
+                               const void* eps, const void* weight_decay,
+                               const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                               const int64_t* strides, int amsgrad, int maximize,
+                               int decoupled_weight_decay, int steps_already_bumped,
+                               int64_t active_rows_hint, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  return cb200::adam_entry(dtype, params, grads, nullptr, exp_avgs, exp_avg_sqs, max_exp_avg_sqs,
+                           state_steps, lr, beta1, beta2, eps, weight_decay, active_mask, n_rows,
+                           row_len, strides, amsgrad, maximize, decoupled_weight_decay,
+                           steps_already_bumped, active_rows_hint, workspace, workspace_bytes,
+                           stream);
+}
+
+extern "C" int cb200_adam_step_from_parts(
+    int dtype, void* params, const cb200_grad_parts* grad_parts, void* exp_avgs,
+    void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps, const void* lr,
+    const void* beta1, const void* beta2, const void* eps, const void* weight_decay,
+    const uint8_t* active_mask, int64_t n_rows, int64_t row_len, const int64_t* strides,
+    int amsgrad, int maximize, int decoupled_weight_decay, int steps_already_bumped,
+    int64_t active_rows_hint, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!grad_parts) return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "grad_parts must not be NULL");
+  return cb200::adam_entry(dtype, params, nullptr, grad_parts, exp_avgs, exp_avg_sqs,
+                           max_exp_avg_sqs, state_steps, lr, beta1, beta2, eps, weight_decay,
+                           active_mask, n_rows, row_len, strides, amsgrad, maximize,
+                           decoupled_weight_decay, steps_already_bumped, active_rows_hint,
+                           workspace, workspace_bytes, stream);
 }

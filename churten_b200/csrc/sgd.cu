@@ -58,6 +58,7 @@ struct SgdArgs {
   void* workspace;
   size_t workspace_bytes;
   cudaStream_t stream;
+  const cb200_grad_parts* parts;
 };
 
 template <class T, bool HAS_BUF>
@@ -73,7 +74,7 @@ int sgd_run(const SgdArgs& a) {
                           a.nesterov_rows, a.nesterov};
   return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
                                  a.row_len, a.flags, a.bump, a.hint, a.workspace,
-                                 a.workspace_bytes, a.stream);
+                                 a.workspace_bytes, a.stream, a.parts);
 }
 
 template <class T>
@@ -84,7 +85,11 @@ int sgd_variant(const SgdArgs& a) {
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_sgd_step(int dtype, void* params, const void* grads, void* momentum_buffers,
+namespace cb200 {
+namespace {
+
+int sgd_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts,
+              void* momentum_buffers,
                               void* state_steps, const void* lr, const void* momentum,
                               const void* dampening, const void* weight_decay,
                               const uint8_t* active_mask, const uint8_t* nesterov_rows,
@@ -92,7 +97,6 @@ extern "C" int cb200_sgd_step(int dtype, void* params, const void* grads, void* 
                               int nesterov, int maximize, int steps_already_bumped,
                               int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
                               void* stream) {
-  using namespace cb200;
   // (an empty matrix has no storage, so a NULL there says nothing)
   if ((nesterov || nesterov_rows) && !momentum_buffers && n_rows > 0 && row_len > 0) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "nesterov=True requires momentum_buffers");
@@ -100,9 +104,14 @@ extern "C" int cb200_sgd_step(int dtype, void* params, const void* grads, void* 
   if (n_rows > 0 && (!lr || !momentum || !dampening || !weight_decay)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }
+  if (parts) {
+    if (int rc = check_grad_parts(parts, row_len)) return rc;
+  }
   SgdArgs a;
+  a.parts = parts;
   a.ptrs[0] = params;
-  a.ptrs[1] = const_cast<void*>(grads);
+  // with parts the gradient slot is never dereferenced; any non-NULL value passes the table checks
+  a.ptrs[1] = parts ? params : const_cast<void*>(grads);
   a.ptrs[2] = momentum_buffers;
   a.state_steps = state_steps;
   a.lr = lr;
@@ -128,4 +137,35 @@ extern "C" int cb200_sgd_step(int dtype, void* params, const void* grads, void* 
     case kBF16: return sgd_variant<__nv_bfloat16>(a);
     default: return fail(CB200_ERR_INVALID_ARGUMENT, "dtype must be CB200_F32, _F64, _F16 or _BF16");
   }
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" int cb200_sgd_step(int dtype, void* params, const void* grads, void* momentum_buffers,
+                              void* state_steps, const void* lr, const void* momentum,
+                              const void* dampening, const void* weight_decay,
+                              const uint8_t* active_mask, const uint8_t* nesterov_rows,
+                              int64_t n_rows, int64_t row_len, const int64_t* strides,
+                              int nesterov, int maximize, int steps_already_bumped,
+                              int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+  return cb200::sgd_entry(dtype, params, grads, nullptr, momentum_buffers, state_steps, lr, momentum,
+                          dampening, weight_decay, active_mask, nesterov_rows, n_rows, row_len,
+                          strides, nesterov, maximize, steps_already_bumped, active_rows_hint,
+                          workspace, workspace_bytes, stream);
+}
+
+extern "C" int cb200_sgd_step_from_parts(
+    int dtype, void* params, const cb200_grad_parts* grad_parts, void* momentum_buffers,
+    void* state_steps, const void* lr, const void* momentum, const void* dampening,
+    const void* weight_decay, const uint8_t* active_mask, const uint8_t* nesterov_rows,
+    int64_t n_rows, int64_t row_len, const int64_t* strides, int nesterov, int maximize,
+    int steps_already_bumped, int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
+    void* stream) {
+  if (!grad_parts) return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "grad_parts must not be NULL");
+  return cb200::sgd_entry(dtype, params, nullptr, grad_parts, momentum_buffers, state_steps, lr,
+                          momentum, dampening, weight_decay, active_mask, nesterov_rows, n_rows,
+                          row_len, strides, nesterov, maximize, steps_already_bumped,
+                          active_rows_hint, workspace, workspace_bytes, stream);
 }

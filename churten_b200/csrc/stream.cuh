@@ -37,11 +37,14 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <type_traits>
 #include <stdint.h>
 
 #include <atomic>
 #include <string>
 
+#include "../../include/churten_b200.h"
 #include "rowmath.cuh"
 
 namespace cb200 {
@@ -144,6 +147,58 @@ __device__ __forceinline__ void store1(T* p, T v) {
   } else {
     *p = v;
   }
+}
+
+// ---------------------------------------------------------------------------
+// Where buffer 1 (the gradients) comes from.
+//
+// DenseGrads: the consolidated (n_rows, row_len) matrix, like every other buffer.
+// cb200_grad_parts: the K per-parameter gradient tensors themselves, each
+//   (n_rows, numel[k]) and owning the columns [offset[k], offset[k] + numel[k]) of the
+//   consolidated row, read in place: the consolidated gradient matrix is then
+//   neither written nor read (8 of the 36 bytes per element that scatter + step
+//   move).  Columns no part covers (the alignment pad) read as zero.
+// ---------------------------------------------------------------------------
+struct DenseGrads {};
+
+// One 16-byte group of a row's gradients (4 consecutive fp32 columns from `col0`,
+// a multiple of 4) gathered from the parts.
+template <bool STREAM>
+__device__ __forceinline__ uint4 gather16(const cb200_grad_parts& gp, int64_t r, int64_t col0) {
+  // p: the last part that starts at or before col0 (offsets ascend; no part is empty)
+  int lo = 0, hi = gp.n_parts;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (gp.offset[mid] <= col0) {
+      lo = mid + 1;
+    } else {
+      hi = mid;
+    }
+  }
+  int p = lo - 1;
+  if (p >= 0) {
+    const int64_t j = col0 - gp.offset[p];
+    const float* src = static_cast<const float*>(gp.ptr[p]) + r * gp.row_stride[p] + j;
+    // the common case: the whole group inside one part, and 16-byte aligned there
+    if (j + 4 <= gp.numel[p] && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+      return load16<STREAM>(src);
+    }
+  }
+  float g[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t col = col0 + k;
+    if (p + 1 < gp.n_parts && col >= gp.offset[p + 1]) ++p;  // at most one part starts per column
+    g[k] = 0.0f;
+    if (p >= 0) {
+      const int64_t j = col - gp.offset[p];
+      if (j < gp.numel[p]) {
+        g[k] = load1<STREAM>(static_cast<const float*>(gp.ptr[p]) + r * gp.row_stride[p] + j);
+      }
+    }
+  }
+  return make_uint4(__float_as_uint(g[0]), __float_as_uint(g[1]), __float_as_uint(g[2]),
+                    __float_as_uint(g[3]));
 }
 
 // Storage <-> math conversions.  `Pack<T>` views one 16-byte access as kVec
@@ -319,10 +374,11 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 // Requires element stride 1, 16-byte aligned rows, row_len % (16 / sizeof(Storage)) == 0.
 // A 16-byte access holds kVec = 4 fp32, 8 fp16/bf16 or 2 fp64 elements.
 // ---------------------------------------------------------------------------
-template <class Op, int UNROLL, bool STREAM>
+template <class Op, int UNROLL, bool STREAM, class Grads>
 __global__ void __launch_bounds__(512)
 stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
-              int flags) {
+              int flags, Grads grads) {
+  constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
   using T = typename Op::Storage;
@@ -362,7 +418,15 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
     for (int u = 0; u < UNROLL; ++u) {
       if (e0 + u * lane_elems < row_len) {
 #pragma unroll
-        for (int b = 0; b < NB; ++b) raw[u][b] = load16<STREAM>(base[b] + u * lane_elems);
+        for (int b = 0; b < NB; ++b) {
+          if constexpr (kGather) {
+            if (b == 1) {
+              raw[u][b] = gather16<STREAM>(grads, r, e0 + u * lane_elems);
+              continue;
+            }
+          }
+          raw[u][b] = load16<STREAM>(base[b] + u * lane_elems);
+        }
       }
     }
 #pragma unroll
@@ -452,9 +516,10 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
 // Host launcher.
 // ---------------------------------------------------------------------------
 template <int NB>
-inline bool vector_layout_ok(const Bufs<NB>& b, int64_t row_len, int vec) {
+inline bool vector_layout_ok(const Bufs<NB>& b, int64_t row_len, int vec, int skip = -1) {
   if (row_len % vec != 0) return false;
   for (int i = 0; i < NB; ++i) {
+    if (i == skip) continue;
     if (b.stride_t[i] != 1) return false;
     if (b.stride_r[i] % vec != 0) return false;
     if (reinterpret_cast<uintptr_t>(b.ptr[i]) % 16 != 0) return false;
@@ -485,7 +550,8 @@ template <class VecOp, class ElemOp>
 inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* state_steps,
                     const uint8_t* active_mask, const Bufs<VecOp::kBufs>& bufs, int64_t n_rows,
                     int64_t row_len, int flags, int bump_steps, int64_t active_rows_hint,
-                    void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                    void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                    const cb200_grad_parts* grad_parts = nullptr) {
   static_assert(VecOp::kBufs == ElemOp::kBufs, "same optimizer");
   using T = typename VecOp::Storage;
   constexpr int kVec = Pack<T>::kVec;
@@ -506,7 +572,11 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   if (int rc = device_info(&sm_count, &l2_bytes)) return rc;
 
   const WsView ws = ws_view(workspace, n_rows);
-  const bool vec = vector_layout_ok(bufs, row_len, kVec);
+  const bool vec = vector_layout_ok(bufs, row_len, kVec, grad_parts ? 1 : -1);
+  if (grad_parts && (!vec || !std::is_same<T, float>::value)) {
+    return fail(4, "gradients are read from their parts only for fp32 buffers with dense, "
+                   "16-byte aligned rows");
+  }
 
   // The row records are built with the fusion mask of the path that reads them.
   if (vec) {
@@ -545,7 +615,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
                                 : n_rows;
   const double max_items = static_cast<double>(grid_rows) * static_cast<double>(tiles_per_row);
 
-  auto go = [&](auto kernel) -> int {
+  auto go = [&](auto kernel, auto... extra) -> int {
     // Default: one CTA per (row, tile) work item, sized for the case that every
     // row is active; CTAs beyond the active work exit at once.  A persistent grid
     // (geo.ctas_per_sm > 0) strides over the items instead.
@@ -555,31 +625,42 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
     if (want < 1) want = 1;
     const unsigned grid = static_cast<unsigned>(want);
     cudaError_t e = launch_dependent(kernel, dim3(grid), dim3(threads), stream, bufs, ws, row_len,
-                                     tiles_per_row, flags);
+                                     tiles_per_row, flags, extra...);
     if (e != cudaSuccess) return cuda_fail(e, "step kernel launch");
     count_launches(1);
     return 0;
   };
 
-#define CB200_PICK(KERNEL, OP)                                            \
-  do {                                                                    \
-    if (stream_hint) {                                                    \
-      if (unroll == 4) return go(KERNEL<OP, 4, true>);                    \
-      if (unroll == 2) return go(KERNEL<OP, 2, true>);                    \
-      return go(KERNEL<OP, 1, true>);                                     \
-    } else {                                                              \
-      if (unroll == 4) return go(KERNEL<OP, 4, false>);                   \
-      if (unroll == 2) return go(KERNEL<OP, 2, false>);                   \
-      return go(KERNEL<OP, 1, false>);                                    \
-    }                                                                     \
+#define CB200_PICK(KERNEL, ...)                                      \
+  do {                                                               \
+    if (stream_hint) {                                               \
+      if (unroll == 4) return go(KERNEL(4, true), ##__VA_ARGS__);    \
+      if (unroll == 2) return go(KERNEL(2, true), ##__VA_ARGS__);    \
+      return go(KERNEL(1, true), ##__VA_ARGS__);                     \
+    } else {                                                         \
+      if (unroll == 4) return go(KERNEL(4, false), ##__VA_ARGS__);   \
+      if (unroll == 2) return go(KERNEL(2, false), ##__VA_ARGS__);   \
+      return go(KERNEL(1, false), ##__VA_ARGS__);                    \
+    }                                                                \
   } while (0)
+#define CB200_DENSE(U, S) stream_kernel<VecOp, U, S, DenseGrads>
+#define CB200_GATHER(U, S) stream_kernel<VecOp, U, S, cb200_grad_parts>
+#define CB200_ELEMENT(U, S) element_kernel<ElemOp, U, S>
 
-  if (vec) {
-    CB200_PICK(stream_kernel, VecOp);
+  if (grad_parts) {
+    // only instantiated for fp32 storage (checked above)
+    if constexpr (std::is_same<T, float>::value) {
+      CB200_PICK(CB200_GATHER, *grad_parts);
+    }
+  } else if (vec) {
+    CB200_PICK(CB200_DENSE, DenseGrads{});
   } else {
-    CB200_PICK(element_kernel, ElemOp);
+    CB200_PICK(CB200_ELEMENT);
   }
 #undef CB200_PICK
+#undef CB200_DENSE
+#undef CB200_GATHER
+#undef CB200_ELEMENT
   return 0;
 }
 
@@ -595,6 +676,25 @@ inline int fill_bufs(Bufs<NB>* out, void* const* ptrs, const int64_t* strides, i
     out->stride_r[i] = strides ? strides[2 * i] : row_len;
     out->stride_t[i] = strides ? strides[2 * i + 1] : 1;
   }
+  return 0;
+}
+
+// Checks a gradient-parts table against the row it stands for.
+inline int check_grad_parts(const cb200_grad_parts* gp, int64_t row_len) {
+  if (!gp) return fail(1, "grad_parts must not be NULL");
+  if (gp->n_parts < 1 || gp->n_parts > CB200_MAX_GRAD_PARTS) {
+    return fail(1, "grad_parts.n_parts must be in [1, " + std::to_string(CB200_MAX_GRAD_PARTS) + "]");
+  }
+  int64_t end = 0;
+  for (int k = 0; k < gp->n_parts; ++k) {
+    const std::string which = "gradient part " + std::to_string(k);
+    if (!gp->ptr[k]) return fail(1, which + " is NULL");
+    if (gp->numel[k] < 1) return fail(1, which + " is empty");
+    if (gp->offset[k] < end) return fail(1, which + " overlaps its predecessor or is out of order");
+    if (gp->row_stride[k] < 0) return fail(1, which + " has a negative row stride");
+    end = gp->offset[k] + gp->numel[k];
+  }
+  if (end > row_len) return fail(1, "the gradient parts reach past the end of a row");
   return 0;
 }
 

@@ -197,6 +197,46 @@ def _same_layout_args(op: str, params: torch.Tensor, others: list[tuple[str, tor
     return (ctypes.c_int64 * len(flat))(*flat)
 
 
+class GradParts:
+    """The per-parameter gradient tensors of one step, to be read in place by the step kernel
+    (`cb200_*_step_from_parts`) instead of a consolidated `(N, T)` gradient matrix.
+
+    `parts` holds `(tensor, first_column, columns)`; each tensor is `(N, ...)` fp32 on the
+    parameters' device with dense rows.  `GradParts.build` returns None when the step cannot
+    read these gradients in place (the caller then scatters them and takes the plain step).
+    """
+
+    def __init__(self, table, keep_alive):
+        self.table, self.keep_alive = table, keep_alive
+
+    @classmethod
+    def build(cls, parts: list[tuple[torch.Tensor, int, int]], params: torch.Tensor) -> "GradParts | None":
+        parts = sorted((p for p in parts if p[2] > 0), key=lambda p: p[1])
+        if not 0 < len(parts) <= _lib.MAX_GRAD_PARTS or params.dtype is not torch.float32:
+            return None
+        n_rows = params.shape[0]
+        table = _lib.GradPartsTable()
+        table.n_parts = len(parts)
+        for k, (t, offset, numel) in enumerate(parts):
+            if not (t.dtype is torch.float32 and t.device == params.device and t.dim() >= 1
+                    and t.shape[0] == n_rows and t.numel() == n_rows * numel and t[0].is_contiguous()):
+                return None
+            table.ptr[k] = t.data_ptr()
+            table.row_stride[k] = t.stride(0) if n_rows > 1 else numel
+            table.offset[k] = offset
+            table.numel[k] = numel
+        return cls(table, [p[0] for p in parts])
+
+
+def _grads_argument(op: str, grads, strides):
+    """`(entry point suffix, C argument)` for a dense gradient matrix or a `GradParts`."""
+    if not isinstance(grads, GradParts):
+        return "", grads.data_ptr()
+    if strides is not None:
+        raise RuntimeError(f"{op}: gradients are read from their parts only for dense fp32 buffers")
+    return "_from_parts", ctypes.byref(grads.table)
+
+
 class _Call:
     """What every wrapper does around the C call: guard, steps, mask, scratch, hint."""
 
@@ -285,14 +325,15 @@ def adam_step_cuda(
     others = [("grads", grads), ("exp_avgs", exp_avgs), ("exp_avg_sqs", exp_avg_sqs)]
     if amsgrad:
         others.append(("max_exp_avg_sqs", max_exp_avg_sqs))
-    strides = _same_layout_args(op, params, others)
+    strides = _same_layout_args(op, params, [o for o in others if isinstance(o[1], torch.Tensor)])
     if strides is not None and not amsgrad:
         strides = (ctypes.c_int64 * 10)(*strides, 0, 0)
+    suffix, grads_c = _grads_argument(op, grads, strides)
     with _Call(op, params, state_steps, active_mask) as call:
         lr_c, b1_c, b2_c = _hyper(lr, params), _hyper(beta1, params), _hyper(beta2, params)
         eps_c, wd_c = _hyper(eps, params), _hyper(weight_decay, params)
-        status = _cb.cb200_adam_step(
-            call.dtype, params.data_ptr(), grads.data_ptr(), exp_avgs.data_ptr(), exp_avg_sqs.data_ptr(),
+        status = getattr(_cb, "cb200_adam_step" + suffix)(
+            call.dtype, params.data_ptr(), grads_c, exp_avgs.data_ptr(), exp_avg_sqs.data_ptr(),
             max_exp_avg_sqs.data_ptr() if amsgrad else None,
             call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
             eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(),
@@ -315,17 +356,18 @@ def sgd_step_cuda(
     others = [("grads", grads)]
     if momentum_buffers is not None:
         others.append(("momentum_buffers", momentum_buffers))
-    strides = _same_layout_args(op, params, others)
+    strides = _same_layout_args(op, params, [o for o in others if isinstance(o[1], torch.Tensor)])
     if strides is not None and momentum_buffers is None:
         strides = (ctypes.c_int64 * 6)(*strides, 0, 0)
+    suffix, grads_c = _grads_argument(op, grads, strides)
     with _Call(op, params, state_steps, active_mask) as call:
         lr_c, mom_c = _hyper(lr, params), _hyper(momentum, params)
         damp_c, wd_c = _hyper(dampening, params), _hyper(weight_decay, params)
         nrows_c = _mask(nesterov_rows) if nesterov_rows is not None else None
         if nrows_c is not None and (nrows_c.device != params.device or nrows_c.numel() != call.n_rows):
             raise RuntimeError(f"{op}: nesterov_rows must be a ({call.n_rows},) vector on {params.device}")
-        status = _cb.cb200_sgd_step(
-            call.dtype, params.data_ptr(), grads.data_ptr(),
+        status = getattr(_cb, "cb200_sgd_step" + suffix)(
+            call.dtype, params.data_ptr(), grads_c,
             momentum_buffers.data_ptr() if momentum_buffers is not None else None,
             call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(),
             wd_c.data_ptr(), call.mask.data_ptr(),
@@ -342,12 +384,14 @@ def adagrad_step_cuda(
 ):
     op = "torchstrap::adagrad_step_"
     _check_consolidated(params, op)
-    strides = _same_layout_args(op, params, [("grads", grads), ("state_sums", state_sums)])
+    others = [("grads", grads), ("state_sums", state_sums)]
+    strides = _same_layout_args(op, params, [o for o in others if isinstance(o[1], torch.Tensor)])
+    suffix, grads_c = _grads_argument(op, grads, strides)
     with _Call(op, params, state_steps, active_mask) as call:
         lr_c, lrd_c = _hyper(lr, params), _hyper(lr_decay, params)
         wd_c, eps_c = _hyper(weight_decay, params), _hyper(eps, params)
-        status = _cb.cb200_adagrad_step(
-            call.dtype, params.data_ptr(), grads.data_ptr(), state_sums.data_ptr(),
+        status = getattr(_cb, "cb200_adagrad_step" + suffix)(
+            call.dtype, params.data_ptr(), grads_c, state_sums.data_ptr(),
             call.steps.data_ptr(), lr_c.data_ptr(), lrd_c.data_ptr(), wd_c.data_ptr(),
             eps_c.data_ptr(), call.mask.data_ptr(),
             call.n_rows, call.row_len, strides, int(maximize), call.bumped, call.hint,

@@ -22,6 +22,8 @@ from churten_b200.state import State, _as_1d, _as_2d
 @dataclass(frozen=True)
 class FusedSpec:
     op: Callable                       # the torch.ops.torchstrap.*_step_ handle
+    direct: Callable                   # the same step called past the dispatcher (accepts GradParts)
+    flag_defaults: dict                # defaults of `update`'s flags
     hypers: tuple[str, ...]            # (N,) vectors, in the operator's order
     buffers: tuple[str, ...]           # (N, T) state buffers after params and grads, in order
     optional: frozenset                # buffers that may be absent (passed as None)
@@ -44,8 +46,9 @@ def populate(spec: FusedSpec, state: State, hypers: dict[str, Any], buffers: tup
     return state
 
 
-def step(spec: FusedSpec, state: State, defaults: dict[str, Any]) -> State:
-    """One fused launch; flags stored by `init` win over the call's defaults."""
+def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None) -> State:
+    """One fused launch; flags stored by `init` win over the call's defaults.  `grads`: the
+    consolidated matrix (default) or a `GradParts` for the dispatcher-free call."""
     opt = state.optimizer_state
     flags = {name: bool(opt.get(name, defaults[name])) for name in spec.flags}
     buffers = []
@@ -54,9 +57,9 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any]) -> State:
         if value is None and name not in spec.optional:
             raise KeyError(f"optimizer state has no {name!r}: was init() called?")
         buffers.append(_as_2d(value) if value is not None else None)
-    spec.op(
+    (spec.op if grads is None else spec.direct)(
         _as_2d(state.flat_params),
-        _as_2d(state.flat_grads),
+        _as_2d(state.flat_grads) if grads is None else grads,
         *buffers,
         _as_1d(opt["state_steps"]),
         *[_as_1d(opt[name]) for name in spec.hypers],
@@ -64,6 +67,30 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any]) -> State:
         **flags,
     )
     return state
+
+
+def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
+    """The step with the gradients read in place from the per-parameter tensors `grads`
+    (name -> `(N, *shape)`), leaving `state.grads` untouched.  Returns False, having done
+    nothing, when that is not possible here: the caller then scatters and steps."""
+    params = state.flat_params
+    if not params.is_cuda or params.dtype is not torch.float32 or not params.is_contiguous():
+        return False
+    windows = state._windows
+    if grads.keys() != windows.keys():
+        return False     # a parameter without a gradient keeps its old one in `state.grads`
+    from churten_b200.kernels._C import GradParts
+
+    with torch.no_grad():
+        parts = GradParts.build([(grads[name], *windows[name]) for name in windows], _as_2d(params))
+        if parts is None:
+            return False
+        for name in spec.buffers:
+            value = state.optimizer_state.get(name)
+            if value is not None and not value.is_contiguous():
+                return False
+        step(spec, state, spec.flag_defaults, grads=parts)
+    return True
 
 
 def any_nonzero(value: float | torch.Tensor) -> bool:

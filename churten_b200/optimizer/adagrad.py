@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from churten_b200.kernels.adagrad import adagrad_step_
+from churten_b200.kernels import _C
 from churten_b200.optimizer import _fused
 from churten_b200.optimizer.grad_transform import GradientTransformation
 from churten_b200.state import State
@@ -13,6 +14,8 @@ __all__ = ["Adagrad", "adagrad_step_"]
 
 _SPEC = _fused.FusedSpec(
     op=adagrad_step_,
+    direct=_C.adagrad_step_cuda,
+    flag_defaults=dict(maximize=False),
     hypers=("lr", "lr_decay", "weight_decay", "eps"),
     buffers=("state_sums",),
     optional=frozenset(),
@@ -21,6 +24,8 @@ _SPEC = _fused.FusedSpec(
 
 
 class Adagrad(metaclass=GradientTransformation):
+    _spec = _SPEC
+
     @classmethod
     def init(
         cls,

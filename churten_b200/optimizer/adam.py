@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from churten_b200.kernels.adam import adam_step_
+from churten_b200.kernels import _C
 from churten_b200.optimizer import _fused
 from churten_b200.optimizer.grad_transform import GradientTransformation
 from churten_b200.state import State
@@ -14,6 +15,8 @@ __all__ = ["Adam", "adam_step_"]
 
 _SPEC = _fused.FusedSpec(
     op=adam_step_,
+    direct=_C.adam_step_cuda,
+    flag_defaults=dict(amsgrad=False, maximize=False, decoupled_weight_decay=True),
     hypers=("lr", "beta1", "beta2", "eps", "weight_decay"),
     buffers=("exp_avgs", "exp_avg_sqs", "max_exp_avg_sqs"),
     optional=frozenset({"max_exp_avg_sqs"}),
@@ -22,6 +25,8 @@ _SPEC = _fused.FusedSpec(
 
 
 class Adam(metaclass=GradientTransformation):
+    _spec = _SPEC
+
     @classmethod
     def init(
         cls,

@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from churten_b200.kernels.sgd import sgd_step_
+from churten_b200.kernels import _C
 from churten_b200.optimizer import _fused
 from churten_b200.optimizer.grad_transform import GradientTransformation
 from churten_b200.state import State
@@ -13,6 +14,8 @@ __all__ = ["SGD", "sgd_step_"]
 
 _SPEC = _fused.FusedSpec(
     op=sgd_step_,
+    direct=_C.sgd_step_cuda,
+    flag_defaults=dict(nesterov=False, maximize=False),
     hypers=("lr", "momentum", "dampening", "weight_decay"),
     buffers=("momentum_buffers",),
     optional=frozenset({"momentum_buffers"}),
@@ -21,6 +24,8 @@ _SPEC = _fused.FusedSpec(
 
 
 class SGD(metaclass=GradientTransformation):
+    _spec = _SPEC
+
     @classmethod
     def init(
         cls,

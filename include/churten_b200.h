@@ -137,6 +137,54 @@ int cb200_adagrad_step(int dtype, void* params, const void* grads, void* state_s
                        size_t workspace_bytes, void* stream);
 
 /*
+ * The three steps with the gradients read IN PLACE from the K per-parameter gradient
+ * tensors autograd produced, instead of from the consolidated gradient matrix: part k
+ * is an fp32 device matrix of n_rows rows x numel[k] columns (rows row_stride[k]
+ * elements apart, element stride 1) and stands for the columns
+ * [offset[k], offset[k] + numel[k]) of every row; offsets ascend, parts do not overlap
+ * and none is empty; columns no part covers read as zero.  All other arguments as in
+ * cb200_adam_step / cb200_sgd_step / cb200_adagrad_step; `strides` still has one
+ * (row, element) pair per buffer in the usual order, the pair of the gradient buffer
+ * being ignored.  fp32 storage with dense, 16-byte aligned rows only
+ * (CB200_ERR_UNSUPPORTED otherwise: scatter and call the plain step).
+ * Replaces `apply_gradient` = `_consolidated_grads.update_(grads)` + `update(state)`
+ * (src/torchstrap/optimizer/grad_transform.py:28-31) for callers that do not read the
+ * consolidated gradients afterwards: 28 instead of 36 bytes per element for Adam.
+ */
+#define CB200_MAX_GRAD_PARTS 96
+typedef struct cb200_grad_parts {
+  int n_parts;
+  const void* ptr[CB200_MAX_GRAD_PARTS];
+  int64_t row_stride[CB200_MAX_GRAD_PARTS];
+  int64_t offset[CB200_MAX_GRAD_PARTS];
+  int64_t numel[CB200_MAX_GRAD_PARTS];
+} cb200_grad_parts;
+int cb200_adam_step_from_parts(int dtype, void* params, const cb200_grad_parts* grad_parts,
+                               void* exp_avgs, void* exp_avg_sqs, void* max_exp_avg_sqs,
+                               void* state_steps, const void* lr, const void* beta1,
+                               const void* beta2, const void* eps, const void* weight_decay,
+                               const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                               const int64_t* strides, int amsgrad, int maximize,
+                               int decoupled_weight_decay, int steps_already_bumped,
+                               int64_t active_rows_hint, void* workspace,
+                               size_t workspace_bytes, void* stream);
+int cb200_sgd_step_from_parts(int dtype, void* params, const cb200_grad_parts* grad_parts,
+                              void* momentum_buffers, void* state_steps, const void* lr,
+                              const void* momentum, const void* dampening,
+                              const void* weight_decay, const uint8_t* active_mask,
+                              const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len,
+                              const int64_t* strides, int nesterov, int maximize,
+                              int steps_already_bumped, int64_t active_rows_hint,
+                              void* workspace, size_t workspace_bytes, void* stream);
+int cb200_adagrad_step_from_parts(int dtype, void* params, const cb200_grad_parts* grad_parts,
+                                  void* state_sums, void* state_steps, const void* lr,
+                                  const void* lr_decay, const void* weight_decay,
+                                  const void* eps, const uint8_t* active_mask, int64_t n_rows,
+                                  int64_t row_len, const int64_t* strides, int maximize,
+                                  int steps_already_bumped, int64_t active_rows_hint,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Scatter K per-parameter gradient tensors into the consolidated (n_rows,
  * dst_row_len) gradient buffer with one launch (per 24 parts).  Part k is an fp32
  * device matrix of n_rows rows x part_numels[k] columns (row stride
