@@ -75,20 +75,13 @@ int adagrad_run(const AdagradArgs& a) {
                                  a.workspace_bytes, a.stream, a.parts);
 }
 
-}  // namespace
-}  // namespace cb200
-
-namespace cb200 {
-namespace {
-
+// The body of both entry points: exactly one of `grads` and `parts` is given.
 int adagrad_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts,
-                  void* state_sums,
-                                  void* state_steps, const void* lr, const void* lr_decay,
-                                  const void* weight_decay, const void* eps,
-                                  const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
-                                  const int64_t* strides, int maximize, int steps_already_bumped,
-                                  int64_t active_rows_hint, void* workspace,
-                                  size_t workspace_bytes, void* stream) {
+                  void* state_sums, void* state_steps, const void* lr, const void* lr_decay,
+                  const void* weight_decay, const void* eps, const uint8_t* active_mask,
+                  int64_t n_rows, int64_t row_len, const int64_t* strides, int maximize,
+                  int steps_already_bumped, int64_t active_rows_hint, void* workspace,
+                  size_t workspace_bytes, void* stream) {
   if (n_rows > 0 && (!lr || !lr_decay || !weight_decay || !eps)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "hyper-parameter vectors must not be NULL");
   }

@@ -86,21 +86,14 @@ int adam_variant(const AdamArgs& a) {
   return a.adamw ? adam_run<T, false, true>(a) : adam_run<T, false, false>(a);
 }
 
-}  // namespace
-}  // namespace cb200
-
-namespace cb200 {
-namespace {
-
-int adam_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts, void* exp_avgs,
-                               void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps,
-                               const void* lr, const void* beta1, const void* beta2,
-                               const void* eps, const void* weight_decay,
-                               const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
-                               const int64_t* strides, int amsgrad, int maximize,
-                               int decoupled_weight_decay, int steps_already_bumped,
-                               int64_t active_rows_hint, void* workspace,
-                               size_t workspace_bytes, void* stream) {
+// The body of both entry points: exactly one of `grads` and `parts` is given.
+int adam_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts,
+               void* exp_avgs, void* exp_avg_sqs, void* max_exp_avg_sqs, void* state_steps,
+               const void* lr, const void* beta1, const void* beta2, const void* eps,
+               const void* weight_decay, const uint8_t* active_mask, int64_t n_rows,
+               int64_t row_len, const int64_t* strides, int amsgrad, int maximize,
+               int decoupled_weight_decay, int steps_already_bumped, int64_t active_rows_hint,
+               void* workspace, size_t workspace_bytes, void* stream) {
   // (an empty matrix has no storage, so a NULL there says nothing)
   if (amsgrad && !max_exp_avg_sqs && n_rows > 0 && row_len > 0) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "amsgrad=True requires max_exp_avg_sqs");

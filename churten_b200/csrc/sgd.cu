@@ -82,21 +82,13 @@ int sgd_variant(const SgdArgs& a) {
   return a.ptrs[2] ? sgd_run<T, true>(a) : sgd_run<T, false>(a);
 }
 
-}  // namespace
-}  // namespace cb200
-
-namespace cb200 {
-namespace {
-
+// The body of both entry points: exactly one of `grads` and `parts` is given.
 int sgd_entry(int dtype, void* params, const void* grads, const cb200_grad_parts* parts,
-              void* momentum_buffers,
-                              void* state_steps, const void* lr, const void* momentum,
-                              const void* dampening, const void* weight_decay,
-                              const uint8_t* active_mask, const uint8_t* nesterov_rows,
-                              int64_t n_rows, int64_t row_len, const int64_t* strides,
-                              int nesterov, int maximize, int steps_already_bumped,
-                              int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
-                              void* stream) {
+              void* momentum_buffers, void* state_steps, const void* lr, const void* momentum,
+              const void* dampening, const void* weight_decay, const uint8_t* active_mask,
+              const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len,
+              const int64_t* strides, int nesterov, int maximize, int steps_already_bumped,
+              int64_t active_rows_hint, void* workspace, size_t workspace_bytes, void* stream) {
   // (an empty matrix has no storage, so a NULL there says nothing)
   if ((nesterov || nesterov_rows) && !momentum_buffers && n_rows > 0 && row_len > 0) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "nesterov=True requires momentum_buffers");
