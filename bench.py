@@ -725,6 +725,7 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference", "reference_cuda"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5_shard")
     ap.add_argument("--rows", type=int, default=0, help="override replicas per GPU (profiling small cases)")
+    ap.add_argument("--row-len", type=int, default=0, help="override elements per replica (T)")
     ap.add_argument("--dtype", choices=sorted(ELEMENT_BYTES), default="f32",
                     help="storage type of the (N, T) buffers (the headline metric is f32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -748,6 +749,9 @@ def main():
     w = dict(WORKLOADS[args.workload])
     if args.rows:
         w["rows"] = args.rows
+    if args.row_len:
+        w["row_len"] = args.row_len
+        w.pop("shapes", None)   # one flat parameter tensor of that length
     w["dtype"] = args.dtype
     # rows are padded to 16 bytes by the State allocator: 8 elements for the 2-byte types
     per_access = 16 // ELEMENT_BYTES[args.dtype]

@@ -304,6 +304,43 @@ struct Pack<__nv_bfloat16> {
 //               __device__ static Row make_row(const Hyper&, int r, Math step).
 // `bump` = 0: the caller has already advanced the counters of the active rows.
 // ---------------------------------------------------------------------------
+// Rows with a non-zero mask byte among the first `count` rows, summed over the CTA.
+__device__ __forceinline__ int count_active_before(const uint8_t* __restrict__ mask, int count,
+                                                   int* scratch /* kPrologueThreads / 32 ints */) {
+  const int tid = threadIdx.x;
+  int mine = 0;
+  // 16 mask bytes per load where the vector is aligned, single bytes around it
+  const uintptr_t address = reinterpret_cast<uintptr_t>(mask);
+  int head = static_cast<int>((16 - (address & 15)) & 15);
+  if (head > count) head = count;
+  const int groups = (count - head) / 16;
+  const uint4* __restrict__ wide = reinterpret_cast<const uint4*>(mask + head);
+  for (int i = tid; i < groups; i += kPrologueThreads) {
+    const uint4 v = wide[i];
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      // bit 7 of every byte that is not zero
+      mine += __popc((((w[k] & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w[k]) & 0x80808080u);
+    }
+  }
+  for (int i = tid; i < head; i += kPrologueThreads) mine += mask[i] != 0;
+  for (int i = head + groups * 16 + tid; i < count; i += kPrologueThreads) mine += mask[i] != 0;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) mine += __shfl_down_sync(0xffffffffu, mine, d);
+  if ((tid & 31) == 0) scratch[tid >> 5] = mine;
+  __syncthreads();
+  int total = 0;
+  for (int w = 0; w < kPrologueThreads / 32; ++w) total += scratch[w];
+  __syncthreads();
+  return total;
+}
+
+// CTA b owns rows [b * kPrologueThreads, (b + 1) * kPrologueThreads): it bumps their
+// counters, builds their records and appends the active ones to the list in row
+// order.  Its position in the list is the number of active rows before its block,
+// which it counts itself from the mask (at most n_rows bytes, from L2): no CTA waits
+// for another and the workspace needs no initial state.
 template <class Op>
 __global__ void __launch_bounds__(kPrologueThreads)
 prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_steps,
@@ -318,48 +355,45 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 
   __shared__ int warp_count[kPrologueThreads / 32];
   __shared__ int warp_offset[kPrologueThreads / 32];
-  __shared__ int chunk_total;
+  __shared__ int block_total;
 
   const int tid = threadIdx.x;
   const int lane_id = tid & 31;
   const int warp_id = tid >> 5;
-  int running = 0;
+  const int base = static_cast<int>(blockIdx.x) * kPrologueThreads;
+  const int before = blockIdx.x == 0 ? 0 : count_active_before(active_mask, base, warp_count);
 
-  for (int base = 0; base < n_rows; base += kPrologueThreads) {
-    const int r = base + tid;
-    const bool active = (r < n_rows) && (active_mask[r] != 0);
-    const unsigned ballot = __ballot_sync(0xffffffffu, active);
-    if (lane_id == 0) warp_count[warp_id] = __popc(ballot);
-    __syncthreads();
-    if (warp_id == 0) {
-      const int mine = warp_count[lane_id];
-      int incl = mine;
+  const int r = base + tid;
+  const bool active = (r < n_rows) && (active_mask[r] != 0);
+  const unsigned ballot = __ballot_sync(0xffffffffu, active);
+  if (lane_id == 0) warp_count[warp_id] = __popc(ballot);
+  __syncthreads();
+  if (warp_id == 0) {
+    const int mine = warp_count[lane_id];
+    int incl = mine;
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane_id >= d) incl += up;
-      }
-      warp_offset[lane_id] = incl - mine;
-      if (lane_id == 31) chunk_total = incl;
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane_id >= d) incl += up;
     }
-    __syncthreads();
-    if (active) {
-      const int slot = running + warp_offset[warp_id] + __popc(ballot & ((1u << lane_id) - 1u));
-      // The reference bumps with `state_steps.add_(mask.to(dtype))`
-      // (cuda/adam.cu:277): an add of 1 in the counter's own type.
-      M step = state_steps[r];
-      if (bump) {
-        step = add_rn(step, M(1));
-        state_steps[r] = step;
-      }
-      ws.ids[slot] = r;
-      rows[slot] = Op::make_row(hyper, r, step);
-    }
-    running += chunk_total;
-    __syncthreads();
+    warp_offset[lane_id] = incl - mine;
+    if (lane_id == 31) block_total = incl;
   }
-  if (tid == 0) {
-    ws.header->n_active = running;
+  __syncthreads();
+  if (active) {
+    const int slot = before + warp_offset[warp_id] + __popc(ballot & ((1u << lane_id) - 1u));
+    // The reference bumps with `state_steps.add_(mask.to(dtype))`
+    // (cuda/adam.cu:277): an add of 1 in the counter's own type.
+    M step = state_steps[r];
+    if (bump) {
+      step = add_rn(step, M(1));
+      state_steps[r] = step;
+    }
+    ws.ids[slot] = r;
+    rows[slot] = Op::make_row(hyper, r, step);
+  }
+  if (tid == 0 && blockIdx.x == gridDim.x - 1) {
+    ws.header->n_active = before + block_total;
     ws.header->n_rows = n_rows;
   }
 }
@@ -579,11 +613,13 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   }
 
   // The row records are built with the fusion mask of the path that reads them.
+  const unsigned prologue_ctas =
+      static_cast<unsigned>((n_rows + kPrologueThreads - 1) / kPrologueThreads);
   if (vec) {
-    prologue_kernel<VecOp><<<1, kPrologueThreads, 0, stream>>>(
+    prologue_kernel<VecOp><<<prologue_ctas, kPrologueThreads, 0, stream>>>(
         hyper, state_steps, active_mask, static_cast<int>(n_rows), bump_steps, ws);
   } else {
-    prologue_kernel<ElemOp><<<1, kPrologueThreads, 0, stream>>>(
+    prologue_kernel<ElemOp><<<prologue_ctas, kPrologueThreads, 0, stream>>>(
         hyper, state_steps, active_mask, static_cast<int>(n_rows), bump_steps, ws);
   }
   cudaError_t err = cudaGetLastError();
@@ -594,7 +630,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   if (row_len == 0) return 0;
 
   const LaunchGeometry geo = geometry();
-  const int threads = geo.threads > 0 ? geo.threads : VecOp::kThreads;
+  int threads = geo.threads > 0 ? geo.threads : VecOp::kThreads;
   const int64_t per_thread = vec ? kVec : 1;
   // Streaming hints once the step's traffic no longer fits in L2.
   const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) *
@@ -607,6 +643,16 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   // buffer); the element-wise kernel keeps four scalar accesses per thread in flight.
   int unroll = geo.unroll;
   if (unroll == 0) unroll = vec ? VecOp::kUnroll : 4;
+  // Rows shorter than a tile (ensembles of very small models): shrink the CTA to the row
+  // instead of leaving most of its threads idle.
+  if (geo.threads <= 0 && geo.unroll == 0) {
+    const int64_t lanes = (row_len + per_thread - 1) / per_thread;  // accesses that cover a row
+    if (lanes < static_cast<int64_t>(threads) * unroll) {
+      unroll = 1;
+      const int64_t rounded = (lanes + 31) / 32 * 32;
+      if (rounded < threads) threads = static_cast<int>(rounded);
+    }
+  }
   const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
   const int64_t tiles_per_row = (row_len + tile - 1) / tile;
   // Grid: one CTA per tile of every row that can be active.

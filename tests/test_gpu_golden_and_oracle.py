@@ -75,7 +75,8 @@ def _problem(R, T, seed, nbuf):
     return bufs, mask, steps, lr, gen
 
 
-@pytest.mark.parametrize("R,T", [(1, 64), (7, 45), (5, 1000), (16, 4100), (3, 70004), (33, 260)])
+@pytest.mark.parametrize("R,T", [(1, 64), (7, 45), (5, 1000), (16, 4100), (3, 70004), (33, 260),
+                                 (2500, 16), (4097, 9)])   # the last two: several prologue CTAs
 @pytest.mark.parametrize("amsgrad", [False, True])
 @pytest.mark.parametrize("adamw", [False, True])
 def test_adam_bit_exact_against_c_oracle(ops, cuda, R, T, amsgrad, adamw):
@@ -157,7 +158,7 @@ def test_sgd_per_row_nesterov_in_one_launch(ops, cuda):
     assert torch.equal(sa, sb)
 
 
-@pytest.mark.parametrize("R,T", [(1, 64), (7, 45), (5, 1000), (16, 4100), (3, 70004)])
+@pytest.mark.parametrize("R,T", [(1, 64), (7, 45), (5, 1000), (16, 4100), (3, 70004), (3000, 12)])
 def test_adagrad_bit_exact_against_c_oracle(ops, cuda, R, T):
     bufs, mask, steps, lr, gen = _problem(R, T, 300 + R + T, 3)
     bufs[2].abs_()

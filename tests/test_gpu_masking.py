@@ -203,3 +203,42 @@ def test_guard_regions_survive(ops, cuda, T):
     torch.cuda.synchronize()
     for slab in slabs:
         assert (slab[:guard] == poison).all() and (slab[-guard:] == poison).all()
+
+
+@pytest.mark.parametrize("offset", [0, 3])
+def test_many_rows_are_compacted_by_several_ctas(ops, cuda, offset):
+    """More rows than one prologue CTA owns (1024): every CTA counts the active rows before
+    its block itself, from a mask that need not be 16-byte aligned; whole blocks may be
+    frozen.  Plain SGD, so the expected result is one line of tensor arithmetic."""
+    R, T = 5000, 20
+    gen = torch.Generator(device=cuda).manual_seed(9)
+    p = torch.randn(R, T, device=cuda, generator=gen)
+    g = torch.randn(R, T, device=cuda, generator=gen)
+    backing = torch.rand(R + 8, device=cuda, generator=gen) < 0.6
+    backing[offset + 1024: offset + 2048] = False      # a block with nothing to do
+    backing[offset + 2048: offset + 3072] = True       # and a full one
+    mask = backing[offset: offset + R]                 # data pointer offset by `offset` bytes
+    steps = torch.zeros(R, device=cuda)
+    lr = torch.rand(R, device=cuda, generator=gen) * 0.1
+    # expected: the same step taken 1000 rows at a time (one prologue CTA each)
+    want, want_steps = p.clone(), steps.clone()
+    for lo in range(0, R, 1000):
+        rows = slice(lo, lo + 1000)
+        ops.sgd_step_(want[rows], g[rows], None, want_steps[rows], lr[rows], full(1000, 0.0, cuda),
+                      full(1000, 0.0, cuda), full(1000, 0.0, cuda), mask[rows].clone(),
+                      nesterov=False, maximize=False)
+    frozen = p.clone()
+    ops.sgd_step_(p, g, None, steps, lr, full(R, 0.0, cuda), full(R, 0.0, cuda), full(R, 0.0, cuda),
+                  mask, nesterov=False, maximize=False)
+    assert_bits_equal("params", p, want)
+    assert torch.equal(p[~mask], frozen[~mask]) and not torch.equal(p[mask], frozen[mask])
+    torch.testing.assert_close(p[mask], (frozen - lr[:, None] * g)[mask])
+    assert torch.equal(steps, mask.float()) and torch.equal(want_steps, steps)
+    # the list of active rows the step kernel walked: the workspace header holds its length
+    from churten_b200.kernels import _C
+
+    slot = _C._slots[(cuda.index or 0, torch.cuda.current_stream(cuda).cuda_stream)]
+    header = slot.ws[:8].view(torch.int32).tolist()
+    ids = slot.ws[256: 256 + 4 * header[0]].view(torch.int32)
+    assert header == [int(mask.sum()), R]
+    assert torch.equal(ids.long(), mask.nonzero().flatten())       # in row order
