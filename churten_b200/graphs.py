@@ -14,6 +14,10 @@ replayed: one graph launch per step.
         state._consolidated_grads.update_(grads)
         step()                       # == Adam.update(state)
 
+Per-batch learning-rate schedules can ride in the same graph
+(`GraphedUpdate(Adam, state, schedulers=[sched])`: step, then one tick of each schedule):
+their one-launch form reads clocks, mask and rates on the device like the step does.
+
 In-place changes to `state.active_mask` and to the hyper-parameter vectors between
 replays are honoured, exactly as with the eager call.  What is frozen at capture
 time: the set of buffers (rebuild the object after replacing a `State`), the
@@ -30,11 +34,15 @@ from churten_b200.state import State
 
 
 class GraphedUpdate:
-    def __init__(self, optimizer, state: State, active_rows: int | None = None):
+    def __init__(self, optimizer, state: State, active_rows: int | None = None, schedulers=()):
         if state.device.type != "cuda":
             raise ValueError("GraphedUpdate needs a State on a CUDA device")
         self.optimizer = optimizer
         self.state = state
+        self.schedulers = tuple(schedulers)
+        for sched in self.schedulers:
+            if sched._policy_class().needs_score:
+                raise ValueError("a schedule that needs the epoch score is ticked per epoch, outside the graph")
         self.graph = torch.cuda.CUDAGraph()
         mask = state.active_mask
         saved = mask.clone()
@@ -46,12 +54,21 @@ class GraphedUpdate:
             # advancing any clock.
             mask.fill_(False)
             optimizer.update(state)
+            # A tick with every row frozen advances no clock but captures the schedule's
+            # starting rates and rewrites the rates from clock 0; put the caller's back.
+            rates = state.optimizer_state["lr"].clone() if self.schedulers else None
+            for sched in self.schedulers:
+                sched(state)
+            if rates is not None:
+                state.optimizer_state["lr"].copy_(rates)
             mask.copy_(saved)
             stream.synchronize()
             _C.set_capture_hint(active_rows)
             try:
                 with torch.cuda.graph(self.graph, stream=stream):
                     optimizer.update(state)
+                    for sched in self.schedulers:
+                        sched(state)
             finally:
                 _C.set_capture_hint(None)
         torch.cuda.current_stream(state.device).wait_stream(stream)

@@ -259,6 +259,10 @@ class LRScheduler:
             score = None
         if device.type == "cuda" and self._launch(policy, lr, active, score):
             return lr.detach()
+        if device.type == "cuda" and torch.cuda.is_current_stream_capturing():
+            # the expressions below rebind `t_` to fresh tensors, which a replay would not see
+            raise RuntimeError(f"{type(policy).__name__} on {lr.dtype} rates has no one-launch form "
+                               "and cannot be captured in a CUDA graph")
         self.t_ = self.t_ + active.to(self.t_.dtype)
         ctx = ScheduleContext(self.base_lrs_, self.t_, lr.detach().reshape(-1), active, score)
         lr.copy_(policy(ctx).reshape(lr.shape))

@@ -71,3 +71,51 @@ def test_a_small_grid_hint_is_still_correct(cuda):
     step()
     torch.cuda.synchronize()
     assert_bits_equal("params", graphed.params, eager.params)
+
+
+@pytest.mark.parametrize("policy,kwargs", [("WarmRestartLR", dict(min_lr=1e-4, max_lr=2e-2, base_period=3)),
+                                           ("StepLR", dict(step_size=2, gamma=0.5))])
+def test_a_per_batch_schedule_rides_in_the_graph(cuda, policy, kwargs):
+    import churten_b200.optimizer as O
+    from churten_b200.graphs import GraphedUpdate
+    from churten_b200.lr_schedule import LRScheduler
+
+    lr0 = torch.tensor([1e-2, 2e-2, 3e-2, 4e-2, 5e-2, 6e-2], device=cuda)
+    eager, graphed = _state(cuda, O.Adam, lr=lr0), _state(cuda, O.Adam, lr=lr0)
+    sched_eager, sched_graphed = LRScheduler(policy, **kwargs), LRScheduler(policy, **kwargs)
+    step = GraphedUpdate(O.Adam, graphed, schedulers=[sched_graphed])
+    # capturing advanced no clock and left the caller's rates alone
+    assert_bits_equal("rates after capture", graphed.optimizer_state["lr"], lr0)
+    assert not sched_graphed.t_.any()
+    gen = torch.Generator(device=cuda).manual_seed(2)
+    for it in range(9):
+        g = torch.randn(eager.params.shape, device=cuda, generator=gen)
+        g[:, -2:] = 0
+        for st in (eager, graphed):
+            st.grads.copy_(g)
+            if it == 3:
+                st.active_mask[2] = False          # its step clock and its schedule clock both stop
+            if it == 7:
+                st.active_mask[2] = True
+        O.Adam.update(eager)
+        sched_eager(eager)
+        step()
+        assert_bits_equal(f"rates after batch {it}", graphed.optimizer_state["lr"], eager.optimizer_state["lr"])
+    assert_bits_equal("params", graphed.params, eager.params)
+    assert torch.equal(sched_graphed.t_, sched_eager.t_)
+    assert sched_eager.t_.tolist() == [9.0, 9.0, 5.0, 9.0, 9.0, 9.0]
+
+
+def test_schedules_that_cannot_be_captured_are_refused(cuda):
+    import churten_b200.optimizer as O
+    from churten_b200.graphs import GraphedUpdate
+    from churten_b200.lr_schedule import LRScheduler
+
+    state = _state(cuda, O.Adam, lr=1e-2)
+    with pytest.raises(ValueError, match="per epoch"):
+        GraphedUpdate(O.Adam, state, schedulers=[LRScheduler("ReduceLROnPlateau")])
+    with pytest.raises(RuntimeError, match="cannot be captured"):
+        GraphedUpdate(O.Adam, state, schedulers=[LRScheduler("LambdaLR", lr_lambda=lambda t: 0.5)])
+    torch.cuda.synchronize()
+    O.Adam.update(state)       # the device and the state are still usable
+    torch.cuda.synchronize()
