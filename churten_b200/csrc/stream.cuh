@@ -411,7 +411,7 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 template <class Op, int UNROLL, bool STREAM, class Grads>
 __global__ void __launch_bounds__(512)
 stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
-              int flags, Grads grads) {
+              int flags, int rows_per_cta, Grads grads) {
   constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
@@ -423,25 +423,37 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
   pdl_wait();
 
   const int n_active = ws.header->n_active;
-  const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
+  // rows_per_cta > 1: rows shorter than half a CTA; each CTA takes that many whole rows,
+  // blockDim / rows_per_cta threads side by side on each (tiles_per_row is 1).
+  const int64_t total = rows_per_cta > 1 ? (n_active + rows_per_cta - 1) / rows_per_cta
+                                         : static_cast<int64_t>(n_active) * tiles_per_row;
   const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * VEC * UNROLL;
   const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * VEC;
   const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
-    int64_t a, tile;
-    if (total <= 0x7fffffffLL) {
-      const uint32_t it = static_cast<uint32_t>(item);
-      const uint32_t tpr = static_cast<uint32_t>(tiles_per_row);
-      a = it / tpr;
-      tile = it - static_cast<uint32_t>(a) * tpr;
+    int64_t a, e0;
+    if (rows_per_cta > 1) {
+      const int width = blockDim.x / rows_per_cta;
+      const int sub = threadIdx.x / width;
+      a = item * rows_per_cta + sub;
+      if (a >= n_active) continue;
+      e0 = static_cast<int64_t>(threadIdx.x - sub * width) * VEC;
     } else {
-      a = item / tiles_per_row;
-      tile = item - a * tiles_per_row;
+      int64_t tile;
+      if (total <= 0x7fffffffLL) {
+        const uint32_t it = static_cast<uint32_t>(item);
+        const uint32_t tpr = static_cast<uint32_t>(tiles_per_row);
+        a = it / tpr;
+        tile = it - static_cast<uint32_t>(a) * tpr;
+      } else {
+        a = item / tiles_per_row;
+        tile = item - a * tiles_per_row;
+      }
+      e0 = tile * tile_elems + static_cast<int64_t>(threadIdx.x) * VEC;
     }
     const int64_t r = ws.ids[a];
     const Row c = rows[a];
-    const int64_t e0 = tile * tile_elems + static_cast<int64_t>(threadIdx.x) * VEC;
 
     T* base[NB];
 #pragma unroll
@@ -496,7 +508,7 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
 template <class Op, int UNROLL, bool STREAM>
 __global__ void __launch_bounds__(512)
 element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
-               int flags) {
+               int flags, int rows_per_cta) {
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
   using T = typename Op::Storage;
@@ -506,16 +518,25 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
   pdl_wait();
 
   const int n_active = ws.header->n_active;
-  const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
+  const int64_t total = rows_per_cta > 1 ? (n_active + rows_per_cta - 1) / rows_per_cta
+                                         : static_cast<int64_t>(n_active) * tiles_per_row;
   const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * UNROLL;
   const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
-    const int64_t a = item / tiles_per_row;
-    const int64_t tile = item - a * tiles_per_row;
+    int64_t a, e0;
+    if (rows_per_cta > 1) {   // several short rows per CTA, as in stream_kernel
+      const int width = blockDim.x / rows_per_cta;
+      const int sub = threadIdx.x / width;
+      a = item * rows_per_cta + sub;
+      if (a >= n_active) continue;
+      e0 = threadIdx.x - sub * width;
+    } else {
+      a = item / tiles_per_row;
+      e0 = (item - a * tiles_per_row) * tile_elems + threadIdx.x;
+    }
     const int64_t r = ws.ids[a];
     const Row c = rows[a];
-    const int64_t e0 = tile * tile_elems + threadIdx.x;
 
     M x[UNROLL][NB];
 #pragma unroll
@@ -645,12 +666,22 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   if (unroll == 0) unroll = vec ? VecOp::kUnroll : 4;
   // Rows shorter than a tile (ensembles of very small models): shrink the CTA to the row
   // instead of leaving most of its threads idle.
+  // Rows shorter than a tile (ensembles of very small models): a CTA takes several whole
+  // rows, a power-of-two group of threads on each, or shrinks to the row, instead of leaving
+  // most of its threads idle.
+  int rows_per_cta = 1;
   if (geo.threads <= 0 && geo.unroll == 0) {
     const int64_t lanes = (row_len + per_thread - 1) / per_thread;  // accesses that cover a row
     if (lanes < static_cast<int64_t>(threads) * unroll) {
       unroll = 1;
-      const int64_t rounded = (lanes + 31) / 32 * 32;
-      if (rounded < threads) threads = static_cast<int>(rounded);
+      int width = 1;
+      while (width < lanes) width <<= 1;
+      if (width * 2 <= threads && (threads & (threads - 1)) == 0) {
+        rows_per_cta = threads / width;
+      } else {
+        const int64_t rounded = (lanes + 31) / 32 * 32;
+        if (rounded < threads) threads = static_cast<int>(rounded);
+      }
     }
   }
   const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
@@ -659,7 +690,9 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   const int64_t grid_rows = (active_rows_hint >= 0 && active_rows_hint < n_rows)
                                 ? (active_rows_hint > 0 ? active_rows_hint : 1)
                                 : n_rows;
-  const double max_items = static_cast<double>(grid_rows) * static_cast<double>(tiles_per_row);
+  const double max_items =
+      rows_per_cta > 1 ? static_cast<double>((grid_rows + rows_per_cta - 1) / rows_per_cta)
+                       : static_cast<double>(grid_rows) * static_cast<double>(tiles_per_row);
 
   auto go = [&](auto kernel, auto... extra) -> int {
     // Default: one CTA per (row, tile) work item, sized for the case that every
@@ -671,7 +704,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
     if (want < 1) want = 1;
     const unsigned grid = static_cast<unsigned>(want);
     cudaError_t e = launch_dependent(kernel, dim3(grid), dim3(threads), stream, bufs, ws, row_len,
-                                     tiles_per_row, flags, extra...);
+                                     tiles_per_row, flags, rows_per_cta, extra...);
     if (e != cudaSuccess) return cuda_fail(e, "step kernel launch");
     count_launches(1);
     return 0;
