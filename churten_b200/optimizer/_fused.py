@@ -30,24 +30,26 @@ class FusedSpec:
     flags: tuple[str, ...]             # static flags, in the operator's keyword order
 
 
-def populate(spec: FusedSpec, state: State, hypers: dict[str, Any], buffers: tuple[str, ...],
-             flags: dict[str, Any], extra_meta: dict[str, Any] | None = None) -> State:
-    """Fill `state.optimizer_state`: vectors (a scalar is broadcast), zeroed buffers, flags."""
+def populate(spec: FusedSpec, state: State, given: dict[str, Any], buffers: tuple[str, ...],
+             extra_meta: dict[str, Any] | None = None) -> State:
+    """Fill `state.optimizer_state` from `given` (the arguments of `init` by name): the
+    hyper-parameter vectors (a scalar is broadcast), zeroed buffers, the static flags."""
     for name in spec.hypers:
-        state.add_optim_state(name, hypers[name])
+        state.add_optim_state(name, given[name])
     state.add_optim_state("state_steps", 0)
     for name in buffers:
         state.add_optim_state(name, per_param=True)
     # flags are stored because `apply_gradient` calls `update(state)` without arguments
     for name in spec.flags:
-        state.add_optim_meta(name, flags[name])
+        state.add_optim_meta(name, given[name])
     for name, value in (extra_meta or {}).items():
         state.add_optim_meta(name, value)
     return state
 
 
 def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None) -> State:
-    """One fused launch; flags stored by `init` win over the call's defaults.  `grads`: the
+    """One fused launch; `defaults` holds the flags passed to `update`, over which the flags
+    stored by `init` win.  `grads`: the
     consolidated matrix (default) or a `GradParts` for the dispatcher-free call."""
     opt = state.optimizer_state
     flags = {name: bool(opt.get(name, defaults[name])) for name in spec.flags}

@@ -38,7 +38,8 @@ class Adagrad(metaclass=GradientTransformation):
         initial_accumulator_value: float | torch.Tensor = 0.0,
         maximize: bool = False,
     ) -> State:
-        _fused.populate(_SPEC, state, locals(), _SPEC.buffers, locals())
+        given = dict(lr=lr, lr_decay=lr_decay, weight_decay=weight_decay, eps=eps, maximize=maximize)
+        _fused.populate(_SPEC, state, given, _SPEC.buffers)
         # torch.optim.Adagrad seeds the accumulator with a constant; the fill covers the
         # pad lanes too, which no view reaches and no gradient is written to.
         sums = state.optimizer_state["state_sums"]
@@ -50,4 +51,4 @@ class Adagrad(metaclass=GradientTransformation):
 
     @classmethod
     def update(cls, state: State, maximize: bool = False) -> State:
-        return _fused.step(_SPEC, state, locals())
+        return _fused.step(_SPEC, state, dict(maximize=maximize))

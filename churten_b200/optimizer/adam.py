@@ -42,8 +42,10 @@ class Adam(metaclass=GradientTransformation):
         decoupled_weight_decay: bool = True,
     ) -> State:
         """Per-replica hyper-parameters, zero moments; the max buffer only with AMSGrad."""
+        given = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad,
+                     maximize=maximize, decoupled_weight_decay=decoupled_weight_decay)
         buffers = ("exp_avgs", "exp_avg_sqs") + (("max_exp_avg_sqs",) if amsgrad else ())
-        return _fused.populate(_SPEC, state, locals(), buffers, locals())
+        return _fused.populate(_SPEC, state, given, buffers)
 
     @classmethod
     def update(
@@ -53,4 +55,5 @@ class Adam(metaclass=GradientTransformation):
         maximize: bool = False,
         amsgrad: bool = False,
     ) -> State:
-        return _fused.step(_SPEC, state, locals())
+        return _fused.step(_SPEC, state, dict(amsgrad=amsgrad, maximize=maximize,
+                                              decoupled_weight_decay=decoupled_weight_decay))

@@ -45,9 +45,10 @@ class SGD(metaclass=GradientTransformation):
         # The buffer exists for the whole ensemble as soon as one replica has momentum;
         # its value stays per replica (a replica with momentum 0 does plain SGD).
         buffers = ("momentum_buffers",) if has_momentum else ()
-        return _fused.populate(_SPEC, state, locals(), buffers, locals(),
-                               extra_meta={"has_momentum": has_momentum})
+        given = dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay,
+                     nesterov=nesterov, maximize=maximize)
+        return _fused.populate(_SPEC, state, given, buffers, extra_meta={"has_momentum": has_momentum})
 
     @classmethod
     def update(cls, state: State, nesterov: bool = False, maximize: bool = False) -> State:
-        return _fused.step(_SPEC, state, locals())
+        return _fused.step(_SPEC, state, dict(nesterov=nesterov, maximize=maximize))
