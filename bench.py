@@ -581,14 +581,14 @@ def run_snapshot_leg(args, w):
     """
     import torch
 
-    from churten_b200.checkpoint import Snapshot, _leaves
+    from churten_b200.checkpoint import Snapshot, state_leaves
 
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     n = args.rows or min(w["rows"], 128)
     state, _ = build_state(w, n, device, seed=0)
     state.active_mask.fill_(True)
-    leaves = _leaves(state)
+    leaves = state_leaves(state)
     row_bytes = sum(t.numel() // n * t.element_size() for t in leaves.values())
     snap = Snapshot(state, device_stage=True)
     gen = torch.Generator(device=device).manual_seed(1)
@@ -608,7 +608,7 @@ def run_snapshot_leg(args, w):
 
     from churten_b200.kernels import _C
 
-    mirror, stage = snap._mirror, snap._stage
+    mirror, stage = snap.mirror, snap.stage
     staging = {k: torch.empty_like(v).pin_memory() for k, v in mirror.items()}
     results = {}
     for fraction in (1.0, 0.25):

@@ -38,7 +38,7 @@ import torch
 from churten_b200._flag import DeviceFlag
 from churten_b200.state import OptimizerState, State
 
-__all__ = ["Snapshot", "Checkpoint", "RowsMoved"]
+__all__ = ["Snapshot", "Checkpoint", "RowsMoved", "state_leaves"]
 
 FORMAT = "churten_b200.snapshot/1"
 _OPT = "optimizer_state/"
@@ -48,7 +48,7 @@ class RowsMoved(DeviceFlag):
     """Result of `Snapshot.update`: "at least one row was committed"."""
 
 
-def _leaves(state: State) -> dict[str, torch.Tensor]:
+def state_leaves(state: State) -> dict[str, torch.Tensor]:
     """Every `(N, ...)` tensor of the state, by a stable name."""
     out = {"params": state.params, "buffers": state.buffers, "grads": state.grads,
            "active_mask": state.active_mask}
@@ -84,7 +84,7 @@ class Snapshot:
     def __init__(self, state: State, device_stage: bool = False):
         self.device = torch.device(state.device)
         self._cuda = self.device.type == "cuda"
-        live = _leaves(state)
+        live = state_leaves(state)
         self._meta = _describe(state)
         self._mirror: dict[str, torch.Tensor] = {}
         for name, leaf in live.items():
@@ -109,7 +109,7 @@ class Snapshot:
         Nothing is synchronised; the returned flag tells, when read, whether any row
         moved.  Reading the mirror (`mirror`, `to_file`) waits for the copy.
         """
-        live = _leaves(state)
+        live = state_leaves(state)
         self._check(live)
         select = state.active_mask.reshape(-1)
         if extra_mask is not None:
@@ -151,6 +151,11 @@ class Snapshot:
         self.synchronize()
         return self._mirror
 
+    @property
+    def stage(self) -> dict[str, torch.Tensor] | None:
+        """The device-resident stage (`device_stage=True`), by leaf name; None without one."""
+        return self._stage
+
     # -- mirror -> live -------------------------------------------------------------
     @torch.no_grad()
     def restore_to_live(self, state: State, mask=None) -> None:
@@ -158,7 +163,7 @@ class Snapshot:
         in place.  Not gated by `active_mask`: the frozen replicas are the ones that
         trained past their best epoch.  The mask leaf travels too, so a restored
         replica gets back the `active_mask` value it had when it was committed."""
-        live = _leaves(state)
+        live = state_leaves(state)
         self._check(live)
         device = torch.device(state.device)
         rows = None if mask is None else _row_mask(mask, state.active_mask.shape[0], device)
@@ -296,7 +301,7 @@ def _describe(state: State) -> dict[str, Any]:
         "format": FORMAT,
         "n_rows": int(state.active_mask.shape[0]),
         "leaves": {name: {"dtype": str(leaf.dtype).removeprefix("torch."), "shape": list(leaf.shape)}
-                   for name, leaf in _leaves(state).items()},
+                   for name, leaf in state_leaves(state).items()},
         "param_meta": rows(state.param_meta),
         "buffer_meta": rows(state.buffer_meta),
         "optimizer_meta": dict(state.optimizer_state.meta()),
