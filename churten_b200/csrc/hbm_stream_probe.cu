@@ -10,6 +10,8 @@
 //   * 128-bit (ld.global.v4) against 256-bit (ld.global.v8, sm_100) accesses;
 //   * default caching against streaming (.cs / L2::evict_first) hints;
 //   * pure reads and pure writes, as the ceilings;
+//   * the same streams staged through shared memory by the bulk-copy engine
+//     (cp.async.bulk + mbarrier), one tile per CTA and multi-stage persistent rings;
 //   * the FP64 pipe (fused multiply-adds, IEEE divisions), the other candidate bound
 //     of the Adagrad formulation.
 //
@@ -178,6 +180,144 @@ __global__ void __launch_bounds__(512) write128(Ptrs bufs, int64_t n, float val)
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same streams staged through shared memory by the bulk-copy engine (TMA without a
+// tensor map: cp.async.bulk global -> shared completing on an mbarrier, and
+// cp.async.bulk shared -> global in bulk groups).  One thread issues the copies; the
+// CTA computes out of shared memory.  Every wait is bounded: when the limit is hit the
+// CTA raises `*error`, gives its copies a second bounded chance to land and returns.
+// ---------------------------------------------------------------------------
+constexpr int kBulkThreads = 256;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ unsigned smem_address(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void barrier_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void barrier_expect(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, unsigned src, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
+               : "memory");
+}
+// true once the phase with this parity has completed; false after kSpinLimit polls
+__device__ __forceinline__ bool barrier_wait(unsigned bar, unsigned parity) {
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+// STAGES tiles of TILE floats per buffer in flight per CTA; the grid strides over the tiles
+// (gridDim = number of tiles and STAGES = 1: one short CTA per tile).  n % TILE == 0.
+template <int NR, int NW, int TILE, int STAGES>
+__global__ void __launch_bounds__(kBulkThreads) bulk_stream(Ptrs bufs, int64_t n, float scale, int* error) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  float* ring = reinterpret_cast<float*>(smem_raw);  // [STAGES][NR][TILE]
+  __shared__ __align__(8) unsigned long long full[STAGES];
+  constexpr unsigned kTileBytes = TILE * sizeof(float);
+  constexpr int kPerThread = TILE / (4 * kBulkThreads);  // float4 per thread per buffer
+  static_assert(TILE % (4 * kBulkThreads) == 0, "whole float4 per thread");
+  const int64_t ntiles = n / TILE;
+  const int64_t mine = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) barrier_init(smem_address(&full[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int64_t k) {  // thread 0: loads of this CTA's k-th tile into stage k % STAGES
+    const int s = static_cast<int>(k % STAGES);
+    const int64_t e0 = (blockIdx.x + k * gridDim.x) * TILE;
+    const unsigned bar = smem_address(&full[s]);
+    barrier_expect(bar, NR * kTileBytes);
+#pragma unroll
+    for (int b = 0; b < NR; ++b) {
+      bulk_load(smem_address(ring + (static_cast<int64_t>(s) * NR + b) * TILE), bufs.p[b] + e0, kTileBytes, bar);
+    }
+  };
+  if (threadIdx.x == 0) {
+    for (int64_t k = 0; k < STAGES - 1 && k < mine; ++k) issue(k);
+    if (STAGES == 1 && mine > 0) issue(0);
+  }
+
+  float acc = 0.f;
+  for (int64_t k = 0; k < mine; ++k) {
+    const int s = static_cast<int>(k % STAGES);
+    const unsigned bar = smem_address(&full[s]);
+    const unsigned parity = static_cast<unsigned>((k / STAGES) & 1);
+    // the whole CTA agrees on the outcome, so nobody is left behind at a barrier
+    if (__syncthreads_or(!barrier_wait(bar, parity))) {
+      if (threadIdx.x == 0) atomicExch(error, 1);
+      barrier_wait(bar, parity);  // one more bounded chance for the copies in flight
+      break;
+    }
+    float* stage = ring + static_cast<int64_t>(s) * NR * TILE;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int at = (i * kBulkThreads + threadIdx.x) * 4;
+      float4 sum = *reinterpret_cast<const float4*>(stage + at);
+#pragma unroll
+      for (int b = 1; b < NR; ++b) {
+        const float4 x = *reinterpret_cast<const float4*>(stage + b * TILE + at);
+        sum.x += x.x * scale;
+        sum.y += x.y * scale;
+        sum.z += x.z * scale;
+        sum.w += x.w * scale;
+      }
+      if (NW == 0) acc += sum.x + sum.y + sum.z + sum.w;
+#pragma unroll
+      for (int b = 0; b < NW; ++b) {
+        *reinterpret_cast<float4*>(stage + (b == 0 ? 0 : b + (NR - NW)) * TILE + at) = sum;
+      }
+    }
+    if (NW > 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> async proxy
+    __syncthreads();  // every thread is done with this stage (and, a fortiori, with the previous one)
+    if (threadIdx.x == 0) {
+      if (NW > 0) {
+        const int64_t e0 = (blockIdx.x + k * gridDim.x) * TILE;
+#pragma unroll
+        for (int b = 0; b < NW; ++b) {
+          const int slot = b == 0 ? 0 : b + (NR - NW);
+          bulk_store(bufs.p[slot] + e0, smem_address(stage + slot * TILE), kTileBytes);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+      // Refill.  The next tile to fetch goes into the stage of tile k - 1 (this very stage when
+      // STAGES == 1), whose stores must have finished reading shared memory: with tile k's group
+      // just committed, "at most 1 group pending" is exactly that (0 when the stage is this one).
+      const int64_t next = k + (STAGES > 1 ? STAGES - 1 : 1);
+      if (next < mine) {
+        if (NW > 0) {
+          if (STAGES > 1) {
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          } else {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
+        }
+        issue(next);
+      }
+    }
+  }
+  if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (NW == 0 && acc == 123.456f) bufs.p[0][0] = acc;
+}
+
 template <class F>
 float median_ms(F launch) {
   cudaEvent_t a, b;
@@ -279,6 +419,37 @@ int main() {
   RUN128(5, 4, 1, 1, 256, 0); RUN128(5, 4, 2, 1, 512, -2);
   RUN128(3, 2, 1, 1, 256, 0); RUN128(3, 2, 2, 1, 512, -2);
   RUN128(2, 1, 1, 1, 256, 0);
+  // staged through shared memory by the bulk-copy engine
+  {
+    int* error = nullptr;
+    CK(cudaMalloc(&error, sizeof(int)));
+    CK(cudaMemset(error, 0, sizeof(int)));
+#define RUNBULK(NR, NW, TILE, STAGES, G)                                                              \
+  do {                                                                                                \
+    const int64_t ntiles = n / (TILE);                                                                \
+    const int grid = (G) < 0 ? sms * -(G) : static_cast<int>(ntiles);                                 \
+    const size_t smem = static_cast<size_t>(STAGES) * (NR) * (TILE) * sizeof(float);                  \
+    CK(cudaFuncSetAttribute(bulk_stream<NR, NW, TILE, STAGES>,                                        \
+                            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));    \
+    const float ms = median_ms(                                                                       \
+        [&] { bulk_stream<NR, NW, TILE, STAGES><<<grid, kBulkThreads, smem>>>(d, n, 0.5f, error); }); \
+    int flag = 0;                                                                                     \
+    CK(cudaMemcpy(&flag, error, sizeof(int), cudaMemcpyDeviceToHost));                                \
+    std::printf("bulk %d %d tile %d stages %d grid %d: %.3f ms %.0f GB/s%s\n", NR, NW, TILE, STAGES,  \
+                grid, ms, static_cast<double>(NR + NW) * n * 4 / ms / 1e6,                            \
+                flag ? "  (a wait ran out: number invalid)" : "");                                    \
+    if (flag) return 1;                                                                               \
+  } while (0)
+    RUNBULK(4, 3, 1024, 1, 0);   // one short CTA per 4 KB tile
+    RUNBULK(4, 3, 2048, 1, 0);
+    RUNBULK(4, 3, 4096, 1, 0);
+    RUNBULK(4, 3, 2048, 2, -2);  // persistent, double- and triple-buffered
+    RUNBULK(4, 3, 2048, 3, -2);
+    RUNBULK(4, 3, 2048, 3, -4);
+    RUNBULK(4, 3, 4096, 3, -2);
+    RUNBULK(4, 0, 2048, 3, -4);  // pure read through the same path
+    RUNBULK(2, 1, 2048, 3, -4);
+  }
   // FP64 pipe: fused multiply-adds and divisions per second over the whole GPU
   {
     double* sink = reinterpret_cast<double*>(d.p[0]);
