@@ -355,6 +355,44 @@ class State:
         """A State over the contiguous replica block `[start, stop)`, aliasing this one."""
         return self._rebuild(lambda t: t[start:stop])
 
+    # -- whole-state tensor operations (what the reference gets from TensorClass) --------
+    def clone(self) -> "State":
+        return self._rebuild(lambda t: t.clone())
+
+    def detach(self) -> "State":
+        return self._rebuild(lambda t: t.detach())
+
+    def cpu(self) -> "State":
+        return self.to("cpu")
+
+    def _tensor_leaves(self) -> list[torch.Tensor]:
+        return [self.params, self.buffers, self.grads, self.active_mask,
+                *self.optimizer_state.tensors().values()]
+
+    def copy_(self, other: "State") -> "State":
+        """In-place copy of every leaf of `other` (same structure); identities are kept."""
+        mine, theirs = self._tensor_leaves(), other._tensor_leaves()
+        if len(mine) != len(theirs) or self.optimizer_state.tensors().keys() != other.optimizer_state.tensors().keys():
+            raise ValueError("copy_: the two states do not hold the same leaves")
+        with torch.no_grad():
+            for dst, src in zip(mine, theirs):
+                dst.copy_(src)
+        return self
+
+    def __getitem__(self, index) -> "State":
+        """Rows of every leaf: a slice aliases this state, an index tensor / list / mask gathers
+        a copy (as fancy indexing of the reference's TensorClass does)."""
+        if isinstance(index, int):
+            index = slice(index, index + 1) if index != -1 else slice(-1, None)
+        return self._rebuild(lambda t: t[index])
+
+    def __setitem__(self, index, other: "State") -> None:
+        """`state[index] = rows`: in-place row assignment across every leaf."""
+        theirs = other._tensor_leaves()
+        with torch.no_grad():
+            for dst, src in zip(self._tensor_leaves(), theirs):
+                dst[index] = src.to(dst.device)
+
     def state_dict(self) -> dict[str, Any]:
         return {
             "params": self.params, "buffers": self.buffers, "grads": self.grads,

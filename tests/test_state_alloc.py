@@ -142,3 +142,57 @@ def test_state_dict_round_trip():
 def test_consolidate_rejects_a_wrong_batch_dim():
     with pytest.raises(ValueError, match="incompatible shape"):
         consolidate_params_and_bufffers_dict(({"w": torch.zeros(2, 3)}, {}), batch_size=(4,))
+
+
+def _populated(n=5):
+    torch.manual_seed(0)
+    state = State.from_models(make_models(n))
+    state.add_optim_state("lr", torch.arange(float(n)))
+    state.add_optim_state("m", per_param=True)
+    state.optimizer_state["m"].normal_()
+    state.add_optim_meta("flag", True)
+    return state
+
+
+def test_clone_detach_cpu_and_copy():
+    state = _populated()
+    twin = state.clone()
+    assert twin.params.data_ptr() != state.params.data_ptr() and torch.equal(twin.params, state.params)
+    assert twin.optimizer_state["flag"] is True and twin.batch_size == state.batch_size
+    twin.params.add_(1.0)
+    twin.optimizer_state["lr"].mul_(2.0)
+    assert not torch.equal(twin.params, state.params)
+    storage = state.params.data_ptr()
+    state.copy_(twin)                                       # in place: identities kept
+    assert state.params.data_ptr() == storage and torch.equal(state.params, twin.params)
+    assert state.optimizer_state["lr"].tolist() == [0.0, 2.0, 4.0, 6.0, 8.0]
+    assert state.cpu() is state and not state.detach().params.requires_grad
+    other = _populated()
+    other.add_optim_state("extra")
+    with pytest.raises(ValueError, match="same leaves"):
+        state.copy_(other)
+
+
+def test_row_indexing_follows_tensor_rules():
+    state = _populated()
+    tail = state[3:]                                        # a slice aliases
+    assert tail.batch_size == torch.Size([2]) and tail.params.data_ptr() == state.params[3].data_ptr()
+    one = state[1]
+    assert one.batch_size == torch.Size([1]) and torch.equal(one.params[0], state.params[1])
+    picked = state[torch.tensor([4, 0])]                    # an index tensor gathers a copy
+    assert picked.params.data_ptr() != state.params.data_ptr()
+    assert torch.equal(picked.params, state.params[[4, 0]])
+    assert picked.optimizer_state["lr"].tolist() == [4.0, 0.0]
+    assert picked.params_dict["0.weight"].shape[0] == 2
+    masked = state[torch.tensor([True, False, True, False, False])]
+    assert masked.batch_size == torch.Size([2])
+    # row assignment is in place across every leaf
+    donor = state.clone()
+    donor.params.zero_()
+    donor.optimizer_state["lr"].fill_(-1.0)
+    storage = state.params.data_ptr()
+    idx = torch.tensor([0, 2])
+    state[idx] = donor[idx]
+    assert state.params.data_ptr() == storage
+    assert not state.params[idx].any() and state.params[1].any()
+    assert state.optimizer_state["lr"].tolist() == [-1.0, 1.0, -1.0, 3.0, 4.0]
