@@ -138,6 +138,11 @@ class OptimizerState(Mapping):
     def __setitem__(self, key: str, value: Any) -> None:
         self._entries[key] = value
 
+    def get(self, key: str, default: Any = None) -> Any:
+        # Mapping.get goes through __getitem__ and an exception for a missing key; this is
+        # on the per-step path (an absent optional buffer is looked up every step)
+        return self._entries.get(key, default)
+
     def __iter__(self) -> Iterator[str]:
         return iter(self._entries)
 
