@@ -408,7 +408,7 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 // Requires element stride 1, 16-byte aligned rows, row_len % (16 / sizeof(Storage)) == 0.
 // A 16-byte access holds kVec = 4 fp32, 8 fp16/bf16 or 2 fp64 elements.
 // ---------------------------------------------------------------------------
-template <class Op, int UNROLL, bool STREAM, class Grads>
+template <class Op, int UNROLL, bool STREAM, class Grads, bool PACKED = false>
 __global__ void __launch_bounds__(512)
 stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
               int flags, int rows_per_cta, Grads grads) {
@@ -423,17 +423,18 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
   pdl_wait();
 
   const int n_active = ws.header->n_active;
-  // rows_per_cta > 1: rows shorter than half a CTA; each CTA takes that many whole rows,
-  // blockDim / rows_per_cta threads side by side on each (tiles_per_row is 1).
-  const int64_t total = rows_per_cta > 1 ? (n_active + rows_per_cta - 1) / rows_per_cta
-                                         : static_cast<int64_t>(n_active) * tiles_per_row;
+  // PACKED (rows shorter than half a CTA): each CTA takes rows_per_cta whole rows,
+  // blockDim / rows_per_cta threads side by side on each; tiles_per_row and UNROLL are 1.
+  // A variant of its own so that the index arithmetic costs the main path no registers.
+  const int64_t total = PACKED ? (n_active + rows_per_cta - 1) / rows_per_cta
+                               : static_cast<int64_t>(n_active) * tiles_per_row;
   const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * VEC * UNROLL;
   const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * VEC;
   const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
     int64_t a, e0;
-    if (rows_per_cta > 1) {
+    if constexpr (PACKED) {
       const int width = blockDim.x / rows_per_cta;
       const int sub = threadIdx.x / width;
       a = item * rows_per_cta + sub;
@@ -505,7 +506,7 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
 // Launch 2b: element-wise kernel for any strides, alignment and row length.
 // Same work-item scheme; a tile is blockDim x UNROLL elements.
 // ---------------------------------------------------------------------------
-template <class Op, int UNROLL, bool STREAM>
+template <class Op, int UNROLL, bool STREAM, bool PACKED = false>
 __global__ void __launch_bounds__(512)
 element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
                int flags, int rows_per_cta) {
@@ -518,14 +519,14 @@ element_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_p
   pdl_wait();
 
   const int n_active = ws.header->n_active;
-  const int64_t total = rows_per_cta > 1 ? (n_active + rows_per_cta - 1) / rows_per_cta
-                                         : static_cast<int64_t>(n_active) * tiles_per_row;
+  const int64_t total = PACKED ? (n_active + rows_per_cta - 1) / rows_per_cta
+                               : static_cast<int64_t>(n_active) * tiles_per_row;
   const int64_t tile_elems = static_cast<int64_t>(blockDim.x) * UNROLL;
   const Row* __restrict__ rows = static_cast<const Row*>(ws.rows);
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
     int64_t a, e0;
-    if (rows_per_cta > 1) {   // several short rows per CTA, as in stream_kernel
+    if constexpr (PACKED) {   // several short rows per CTA, as in stream_kernel
       const int width = blockDim.x / rows_per_cta;
       const int sub = threadIdx.x / width;
       a = item * rows_per_cta + sub;
@@ -726,6 +727,21 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
 #define CB200_GATHER(U, S) stream_kernel<VecOp, U, S, cb200_grad_parts>
 #define CB200_ELEMENT(U, S) element_kernel<ElemOp, U, S>
 
+  if (rows_per_cta > 1) {
+    // short rows: one access per thread (unroll is 1 here), several rows per CTA
+    if (grad_parts) {
+      if constexpr (std::is_same<T, float>::value) {
+        return stream_hint ? go(stream_kernel<VecOp, 1, true, cb200_grad_parts, true>, *grad_parts)
+                           : go(stream_kernel<VecOp, 1, false, cb200_grad_parts, true>, *grad_parts);
+      }
+    } else if (vec) {
+      return stream_hint ? go(stream_kernel<VecOp, 1, true, DenseGrads, true>, DenseGrads{})
+                         : go(stream_kernel<VecOp, 1, false, DenseGrads, true>, DenseGrads{});
+    } else {
+      return stream_hint ? go(element_kernel<ElemOp, 1, true, true>)
+                         : go(element_kernel<ElemOp, 1, false, true>);
+    }
+  }
   if (grad_parts) {
     // only instantiated for fp32 storage (checked above)
     if constexpr (std::is_same<T, float>::value) {

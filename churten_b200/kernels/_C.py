@@ -299,7 +299,7 @@ class _Call:
             self.guard.__exit__(*exc)
         return False
 
-    def finish(self, status: int, params: torch.Tensor) -> torch.Tensor:
+    def finish(self, status: int, params: torch.Tensor, want_result: bool = True):
         _lib.check(status, self.op)
         if self.read_back:
             slot = self.slot
@@ -309,14 +309,15 @@ class _Call:
             slot.event = torch.cuda.Event()
             slot.event.record()
         # Fresh 0-dim tensor aliasing nothing: vmap rejects a function that returns
-        # no Tensor (stubs.cpp:20-24).  Its value is unspecified.
-        return params.new_empty(())
+        # no Tensor (stubs.cpp:20-24).  Its value is unspecified.  Callers that reach the
+        # wrapper directly (the front-ends) do not want it.
+        return params.new_empty(()) if want_result else None
 
 
 def adam_step_cuda(
     params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, state_steps,
     lr, beta1, beta2, eps, weight_decay, active_mask,
-    amsgrad, maximize, decoupled_weight_decay,
+    amsgrad, maximize, decoupled_weight_decay, *, want_result=True,
 ):
     op = "torchstrap::adam_step_"
     _check_consolidated(params, op)
@@ -341,13 +342,13 @@ def adam_step_cuda(
             int(amsgrad), int(maximize), int(decoupled_weight_decay), call.bumped, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
-        return call.finish(status, params)
+        return call.finish(status, params, want_result)
 
 
 def sgd_step_cuda(
     params, grads, momentum_buffers, state_steps,
     lr, momentum, dampening, weight_decay, active_mask,
-    nesterov, maximize, *, nesterov_rows=None,
+    nesterov, maximize, *, nesterov_rows=None, want_result=True,
 ):
     op = "torchstrap::sgd_step_"
     _check_consolidated(params, op)
@@ -375,12 +376,12 @@ def sgd_step_cuda(
             call.n_rows, call.row_len, strides, int(nesterov), int(maximize), call.bumped, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
-        return call.finish(status, params)
+        return call.finish(status, params, want_result)
 
 
 def adagrad_step_cuda(
     params, grads, state_sums, state_steps,
-    lr, lr_decay, weight_decay, eps, active_mask, maximize,
+    lr, lr_decay, weight_decay, eps, active_mask, maximize, *, want_result=True,
 ):
     op = "torchstrap::adagrad_step_"
     _check_consolidated(params, op)
@@ -397,12 +398,12 @@ def adagrad_step_cuda(
             call.n_rows, call.row_len, strides, int(maximize), call.bumped, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
-        return call.finish(status, params)
+        return call.finish(status, params, want_result)
 
 
-_library.impl("adam_step_", adam_step_cuda, "CUDA")
+_library.impl("adam_step_", lambda *a: adam_step_cuda(*a), "CUDA")
 _library.impl("sgd_step_", lambda *a: sgd_step_cuda(*a), "CUDA")
-_library.impl("adagrad_step_", adagrad_step_cuda, "CUDA")
+_library.impl("adagrad_step_", lambda *a: adagrad_step_cuda(*a), "CUDA")
 
 
 def scatter_rows(dst: torch.Tensor, parts: list[tuple[torch.Tensor, int, int]]) -> None:

@@ -71,9 +71,9 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None) ->
     if grads is not None or _plain_cuda_call(params):
         if params.requires_grad and torch.is_grad_enabled():
             with torch.no_grad():  # the operator is not differentiable; nothing is recorded
-                spec.direct(*args, **flags)
+                spec.direct(*args, **flags, want_result=False)
         else:
-            spec.direct(*args, **flags)
+            spec.direct(*args, **flags, want_result=False)
     else:
         spec.op(*args, **flags)
     return state
