@@ -232,15 +232,14 @@ def _grads_argument(op: str, grads, strides):
     """`(entry point suffix, C argument)` for a dense gradient matrix or a `GradParts`."""
     if not isinstance(grads, GradParts):
         return "", grads.data_ptr()
-    if strides is not None:
-        raise RuntimeError(f"{op}: gradients are read from their parts only for dense fp32 buffers")
     return "_from_parts", ctypes.byref(grads.table)
 
 
 class _Call:
     """What every wrapper does around the C call: guard, steps, mask, scratch, hint."""
 
-    def __init__(self, op: str, params: torch.Tensor, state_steps: torch.Tensor, active_mask: torch.Tensor):
+    def __init__(self, op: str, params: torch.Tensor, state_steps: torch.Tensor, active_mask: torch.Tensor,
+                 steps_bumped: bool = False):
         self.op = op
         self.device = params.device
         self.n_rows, self.row_len = params.shape
@@ -258,7 +257,10 @@ class _Call:
         # cuda/adam.cu:277) and handed over as `to_hyper` would (consolidated.cuh:87-89).
         if state_steps.dtype is math and state_steps.is_contiguous():
             self.steps = state_steps
-            self.bumped = 0
+            self.bumped = int(steps_bumped)
+        elif steps_bumped:   # a later column range of the same step: the clocks have advanced
+            self.steps = state_steps.to(params.dtype).to(math).contiguous()
+            self.bumped = 1
         else:
             state_steps.add_(active_mask.to(state_steps.dtype))
             self.steps = state_steps.to(params.dtype).to(math).contiguous()
@@ -317,7 +319,7 @@ class _Call:
 def adam_step_cuda(
     params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, state_steps,
     lr, beta1, beta2, eps, weight_decay, active_mask,
-    amsgrad, maximize, decoupled_weight_decay, *, want_result=True,
+    amsgrad, maximize, decoupled_weight_decay, *, want_result=True, steps_bumped=False,
 ):
     op = "torchstrap::adam_step_"
     _check_consolidated(params, op)
@@ -330,7 +332,11 @@ def adam_step_cuda(
     if strides is not None and not amsgrad:
         strides = (ctypes.c_int64 * 10)(*strides, 0, 0)
     suffix, grads_c = _grads_argument(op, grads, strides)
-    with _Call(op, params, state_steps, active_mask) as call:
+    if suffix and strides is not None:
+        # the table has one (row, element) pair per buffer in the usual order; the gradient
+        # buffer's pair is ignored by the *_from_parts entry points
+        strides = (ctypes.c_int64 * (len(strides) + 2))(*strides[:2], 0, 0, *strides[2:])
+    with _Call(op, params, state_steps, active_mask, steps_bumped) as call:
         lr_c, b1_c, b2_c = _hyper(lr, params), _hyper(beta1, params), _hyper(beta2, params)
         eps_c, wd_c = _hyper(eps, params), _hyper(weight_decay, params)
         status = getattr(_cb, "cb200_adam_step" + suffix)(
@@ -348,7 +354,7 @@ def adam_step_cuda(
 def sgd_step_cuda(
     params, grads, momentum_buffers, state_steps,
     lr, momentum, dampening, weight_decay, active_mask,
-    nesterov, maximize, *, nesterov_rows=None, want_result=True,
+    nesterov, maximize, *, nesterov_rows=None, want_result=True, steps_bumped=False,
 ):
     op = "torchstrap::sgd_step_"
     _check_consolidated(params, op)
@@ -361,7 +367,11 @@ def sgd_step_cuda(
     if strides is not None and momentum_buffers is None:
         strides = (ctypes.c_int64 * 6)(*strides, 0, 0)
     suffix, grads_c = _grads_argument(op, grads, strides)
-    with _Call(op, params, state_steps, active_mask) as call:
+    if suffix and strides is not None:
+        # the table has one (row, element) pair per buffer in the usual order; the gradient
+        # buffer's pair is ignored by the *_from_parts entry points
+        strides = (ctypes.c_int64 * (len(strides) + 2))(*strides[:2], 0, 0, *strides[2:])
+    with _Call(op, params, state_steps, active_mask, steps_bumped) as call:
         lr_c, mom_c = _hyper(lr, params), _hyper(momentum, params)
         damp_c, wd_c = _hyper(dampening, params), _hyper(weight_decay, params)
         nrows_c = _mask(nesterov_rows) if nesterov_rows is not None else None
@@ -381,14 +391,18 @@ def sgd_step_cuda(
 
 def adagrad_step_cuda(
     params, grads, state_sums, state_steps,
-    lr, lr_decay, weight_decay, eps, active_mask, maximize, *, want_result=True,
+    lr, lr_decay, weight_decay, eps, active_mask, maximize, *, want_result=True, steps_bumped=False,
 ):
     op = "torchstrap::adagrad_step_"
     _check_consolidated(params, op)
     others = [("grads", grads), ("state_sums", state_sums)]
     strides = _same_layout_args(op, params, [o for o in others if isinstance(o[1], torch.Tensor)])
     suffix, grads_c = _grads_argument(op, grads, strides)
-    with _Call(op, params, state_steps, active_mask) as call:
+    if suffix and strides is not None:
+        # the table has one (row, element) pair per buffer in the usual order; the gradient
+        # buffer's pair is ignored by the *_from_parts entry points
+        strides = (ctypes.c_int64 * (len(strides) + 2))(*strides[:2], 0, 0, *strides[2:])
+    with _Call(op, params, state_steps, active_mask, steps_bumped) as call:
         lr_c, lrd_c = _hyper(lr, params), _hyper(lr_decay, params)
         wd_c, eps_c = _hyper(weight_decay, params), _hyper(eps, params)
         status = getattr(_cb, "cb200_adagrad_step" + suffix)(

@@ -47,19 +47,22 @@ def populate(spec: FusedSpec, state: State, given: dict[str, Any], buffers: tupl
     return state
 
 
-def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None) -> State:
+def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None,
+         columns: tuple[int, int] | None = None, steps_bumped: bool = False) -> State:
     """One fused launch; `defaults` holds the flags passed to `update`, over which the flags
-    stored by `init` win.  `grads`: the
-    consolidated matrix (default) or a `GradParts` for the dispatcher-free call."""
+    stored by `init` win.  `grads`: the consolidated matrix (default) or a `GradParts` for the
+    dispatcher-free call, then optionally over the column range `columns` of every buffer
+    (`steps_bumped`: an earlier range of the same step has advanced the clocks)."""
     opt = state.optimizer_state
     flags = {name: bool(opt.get(name, defaults[name])) for name in spec.flags}
+    window = (lambda t: t) if columns is None else (lambda t: t[:, columns[0]:columns[1]])
     buffers = []
     for name in spec.buffers:
         value = opt.get(name)
         if value is None and name not in spec.optional:
             raise KeyError(f"optimizer state has no {name!r}: was init() called?")
-        buffers.append(_as_2d(value) if value is not None else None)
-    params = _as_2d(state.flat_params)
+        buffers.append(window(_as_2d(value)) if value is not None else None)
+    params = window(_as_2d(state.flat_params))
     args = (
         params,
         _as_2d(state.flat_grads) if grads is None else grads,
@@ -69,11 +72,12 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None) ->
         _as_1d(state.active_mask),
     )
     if grads is not None or _plain_cuda_call(params):
+        extra = dict(want_result=False, steps_bumped=True) if steps_bumped else dict(want_result=False)
         if params.requires_grad and torch.is_grad_enabled():
             with torch.no_grad():  # the operator is not differentiable; nothing is recorded
-                spec.direct(*args, **flags, want_result=False)
+                spec.direct(*args, **flags, **extra)
         else:
-            spec.direct(*args, **flags, want_result=False)
+            spec.direct(*args, **flags, **extra)
     else:
         spec.op(*args, **flags)
     return state
@@ -88,6 +92,26 @@ def _plain_cuda_call(params: torch.Tensor) -> bool:
             and not torch.compiler.is_compiling())
 
 
+def _column_ranges(entries, width: int, limit: int):
+    """Cut the row into column ranges that hold at most `limit` gradient parts each and start
+    at a multiple of 4 columns (16 bytes of fp32, so every range keeps aligned rows).  A part
+    that straddles a cut is split between the two ranges.  Yields `(c0, c1, parts)` with the
+    parts' columns relative to `c0`."""
+    cuts = [0]
+    for i in range(limit - 1, len(entries), limit - 1):
+        cut = entries[i][1] - entries[i][1] % 4
+        if cut > cuts[-1]:
+            cuts.append(cut)
+    cuts.append(width)
+    for c0, c1 in zip(cuts, cuts[1:]):
+        inside = []
+        for tensor, offset, numel in entries:
+            lo, hi = max(offset, c0), min(offset + numel, c1)
+            if lo < hi:
+                inside.append((tensor[:, lo - offset: hi - offset], lo - c0, hi - lo))
+        yield c0, c1, inside
+
+
 def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     """The step with the gradients read in place from the per-parameter tensors `grads`
     (name -> `(N, *shape)`), leaving `state.grads` untouched.  Returns False, having done
@@ -98,17 +122,35 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     windows = state._windows
     if grads.keys() != windows.keys():
         return False     # a parameter without a gradient keeps its old one in `state.grads`
+    from churten_b200 import _lib
     from churten_b200.kernels._C import GradParts
 
-    with torch.no_grad():
-        parts = GradParts.build([(grads[name], *windows[name]) for name in windows], _as_2d(params))
-        if parts is None:
+    n = params.shape[0]
+    entries = []
+    for name, (offset, numel) in windows.items():
+        tensor = grads[name]
+        if numel == 0:
+            continue
+        if not (tensor.dim() >= 1 and tensor.shape[0] == n and tensor.numel() == n * numel
+                and tensor[0].is_contiguous()):
             return False
-        for name in spec.buffers:
-            value = state.optimizer_state.get(name)
-            if value is not None and not value.is_contiguous():
-                return False
-        step(spec, state, spec.flag_defaults, grads=parts)
+        entries.append((tensor.reshape(n, numel), offset, numel))    # a view: rows are dense
+    entries.sort(key=lambda e: e[1])
+    for name in spec.buffers:
+        value = state.optimizer_state.get(name)
+        if value is not None and not value.is_contiguous():
+            return False
+    with torch.no_grad():
+        params2d = _as_2d(params)
+        if len(entries) <= _lib.MAX_GRAD_PARTS:
+            ranges = [(None, GradParts.build(entries, params2d))]
+        else:   # more parameter tensors than one table holds: one launch pair per column range
+            ranges = [((c0, c1), GradParts.build(inside, params2d[:, c0:c1]))
+                      for c0, c1, inside in _column_ranges(entries, params2d.shape[1], _lib.MAX_GRAD_PARTS)]
+        if any(parts is None for _, parts in ranges):
+            return False
+        for i, (columns, parts) in enumerate(ranges):
+            step(spec, state, spec.flag_defaults, grads=parts, columns=columns, steps_bumped=i > 0)
     return True
 
 

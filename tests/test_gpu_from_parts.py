@@ -193,3 +193,38 @@ def test_c_abi_checks_the_table(cuda):
     moved = (p != 0)
     assert moved[:, :6].all() and moved[:, 8:14].all() and not moved[:, 6:8].any() and not moved[:, 14:].any()
     assert torch.equal(steps, torch.ones(n, device=cuda))
+
+
+def _deep():
+    # 60 linear layers: 120 parameter tensors, more than one gradient-parts table holds (96),
+    # with odd sizes so that the column cuts fall inside parts
+    sizes = [5] + [3 + (i * 7) % 11 for i in range(60)]
+    layers = []
+    for a, b in zip(sizes, sizes[1:]):
+        layers += [Linear(a, b), ReLU()]
+    return Sequential(*layers[:-1])
+
+
+@pytest.mark.parametrize("opt_name,hypers", [CASES[1], CASES[2]], ids=["Adam", "SGD"])
+def test_more_parameter_tensors_than_one_table_holds(cuda, opt_name, hypers):
+    from churten_b200.kernels import _C
+
+    cls, (scattered, in_place) = _pair(cuda, _deep, opt_name, hypers, n=4)
+    assert len(scattered.param_meta) == 120
+    gen = torch.Generator(device=cuda).manual_seed(5)
+    untouched = in_place.grads.clone()
+    for step in range(3):
+        mask = torch.tensor([True, step != 1, False, True], device=cuda)
+        for state in (scattered, in_place):
+            state.active_mask.copy_(mask)
+        grads = _grads_like(scattered, gen)
+        cls.apply_gradient(scattered, grads)
+        before = _C.launch_count()
+        cls.apply_gradient(in_place, grads, materialize=False)
+        assert _C.launch_count() - before == 4            # two column ranges: two prologue + step pairs
+    assert_bits_equal("params", in_place.params, scattered.params)
+    for key, value in scattered.optimizer_state.tensors().items():
+        assert_bits_equal(key, in_place.optimizer_state[key], value)
+    assert torch.equal(in_place.grads, untouched)
+    # the clocks advanced once per step, not once per column range
+    assert scattered.optimizer_state["state_steps"].tolist() == [3.0, 2.0, 0.0, 3.0]
