@@ -29,6 +29,8 @@ struct AdagradOp {
   // 128 x 1, 3.8 TB/s (3.8e11 elements/s) against 3.3 for 128 x 2.
   static constexpr int kThreads = 128;
   static constexpr int kUnroll = sizeof(T) == 2 ? 1 : 2;
+  // resident CTAs of 512 threads the register allocation must allow (launch bound)
+  static constexpr int kMinCtas512 = 1;
   using Row = AdagradRow;
   using Hyper = AdagradHyper<Math>;
 

@@ -30,6 +30,8 @@ struct AdamOp {
   // smaller CTAs: bf16 5.2 against 5.1 TB/s, fp64 6.7 against 6.3 TB/s.
   static constexpr int kThreads = sizeof(T) == 4 ? 256 : 128;
   static constexpr int kUnroll = 1;
+  // resident CTAs of 512 threads the register allocation must allow (launch bound)
+  static constexpr int kMinCtas512 = (sizeof(T) == 4 && !AMSGRAD) ? 3 : 1;
   using Row = AdamRowT<Math>;
   using Hyper = AdamHyper<Math>;
 

@@ -89,6 +89,8 @@ struct StaticAdamOp {
   static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;
   static constexpr int kThreads = 256;  // measured best on B200: as cb200_adam_step
   static constexpr int kUnroll = 1;
+  // resident CTAs of 512 threads the register allocation must allow (launch bound)
+  static constexpr int kMinCtas512 = 1;
   using Row = AdamRow;
   using Hyper = StaticAdamHyper;
 

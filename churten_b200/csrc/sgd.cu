@@ -27,6 +27,8 @@ struct SgdOp {
   static constexpr unsigned kWriteMask = HAS_BUF ? 0x5u : 0x1u;
   static constexpr int kThreads = 256;  // measured best on B200: 6.5-6.9 TB/s with a momentum buffer
   static constexpr int kUnroll = 1;
+  // resident CTAs of 512 threads the register allocation must allow (launch bound)
+  static constexpr int kMinCtas512 = 1;
   using Row = SgdRowT<Math>;
   using Hyper = SgdHyper<Math>;
 

@@ -409,7 +409,7 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 // A 16-byte access holds kVec = 4 fp32, 8 fp16/bf16 or 2 fp64 elements.
 // ---------------------------------------------------------------------------
 template <class Op, int UNROLL, bool STREAM, class Grads, bool PACKED = false>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, UNROLL == 1 ? Op::kMinCtas512 : 1)
 stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
               int flags, int rows_per_cta, Grads grads) {
   constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;

@@ -96,12 +96,18 @@ def _column_ranges(entries, width: int, limit: int):
     """Cut the row into column ranges that hold at most `limit` gradient parts each and start
     at a multiple of 4 columns (16 bytes of fp32, so every range keeps aligned rows).  A part
     that straddles a cut is split between the two ranges.  Yields `(c0, c1, parts)` with the
-    parts' columns relative to `c0`."""
-    cuts = [0]
-    for i in range(limit - 1, len(entries), limit - 1):
-        cut = entries[i][1] - entries[i][1] % 4
-        if cut > cuts[-1]:
-            cuts.append(cut)
+    parts' columns relative to `c0`.  (With parts of one or two columns and a `limit` below 8
+    an aligned cut may not exist where it is needed; the range then exceeds the limit and the
+    caller, finding no table for it, scatters instead.)"""
+    cuts, count = [0], 0
+    for i, (_, offset, _) in enumerate(entries):
+        if count == limit:
+            cut = offset - offset % 4
+            if cut > cuts[-1]:
+                cuts.append(cut)
+                # parts that reach past the cut are in the new range too
+                count = sum(1 for _, o, n in entries[:i] if o + n > cut)
+        count += 1
     cuts.append(width)
     for c0, c1 in zip(cuts, cuts[1:]):
         inside = []
