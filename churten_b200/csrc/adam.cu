@@ -31,7 +31,7 @@ struct AdamOp {
   static constexpr int kThreads = sizeof(T) == 4 ? 256 : 128;
   static constexpr int kUnroll = 1;
   // resident CTAs of 512 threads the register allocation must allow (launch bound)
-  static constexpr int kMinCtas512 = (sizeof(T) == 4 && !AMSGRAD) ? 3 : 1;
+  static constexpr int kMinCtas512 = 1;
   using Row = AdamRowT<Math>;
   using Hyper = AdamHyper<Math>;
 
