@@ -423,7 +423,7 @@ _library.impl("adagrad_step_", lambda *a: adagrad_step_cuda(*a), "CUDA")
 def scatter_rows(dst: torch.Tensor, parts: list[tuple[torch.Tensor, int, int]]) -> None:
     """Write dense fp32 `(N, ...)` tensors into column windows of the `(N, T)` buffer `dst`.
 
-    `parts` holds `(tensor, first_column, columns)`; one launch per 24 parts
+    `parts` holds `(tensor, first_column, columns)`; one launch per 64 parts
     (`cb200_scatter_rows`).  The caller has checked dtype, device and density.
     """
     k = len(parts)

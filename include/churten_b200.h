@@ -186,7 +186,7 @@ int cb200_adagrad_step_from_parts(int dtype, void* params, const cb200_grad_part
 
 /*
  * Scatter K per-parameter gradient tensors into the consolidated (n_rows,
- * dst_row_len) gradient buffer with one launch (per 24 parts).  Part k is an fp32
+ * dst_row_len) gradient buffer with one launch (per 64 parts).  Part k is an fp32
  * device matrix of n_rows rows x part_numels[k] columns (row stride
  * part_row_strides[k], or part_numels[k] if that table is NULL) and lands in
  * columns [part_offsets[k], part_offsets[k] + part_numels[k]) of every row.  The

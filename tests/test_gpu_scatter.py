@@ -92,7 +92,7 @@ def test_apply_gradient_is_three_launches(cuda):
     assert state.optimizer_state["state_steps"].tolist() == [1.0] * 4
 
 
-@pytest.mark.parametrize("n_parts", [1, 24, 25, 60])
+@pytest.mark.parametrize("n_parts", [1, 24, 64, 65, 150])
 def test_c_abi_many_parts_strides_and_empty_parts(cuda, n_parts):
     lib = _lib.lib()
     n = 7
