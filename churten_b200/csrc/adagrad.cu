@@ -30,7 +30,9 @@ struct AdagradOp {
   static constexpr int kThreads = 128;
   static constexpr int kUnroll = sizeof(T) == 2 ? 1 : 2;
   // resident CTAs of 512 threads the register allocation must allow (launch bound)
-  static constexpr int kMinCtas512 = 1;
+  // fp32: hold the default tile to 64 registers (68 unbounded) so that 8 CTAs of 128 threads are
+  // resident instead of 7: 6.8 against 6.4 TB/s on 256 x 4 Mi elements
+  static constexpr int kMinCtas512 = sizeof(T) == 4 ? 2 : 0;
   using Row = AdagradRow;
   using Hyper = AdagradHyper<Math>;
 

@@ -31,7 +31,10 @@ struct AdamOp {
   static constexpr int kThreads = sizeof(T) == 4 ? 256 : 128;
   static constexpr int kUnroll = 1;
   // resident CTAs of 512 threads the register allocation must allow (launch bound)
-  static constexpr int kMinCtas512 = 1;
+  // fp32 without AMSGrad: 40 registers (45 unbounded, one 4-byte spill) for 6 resident CTAs of
+  // 256 threads instead of 5: 7.84 against 7.95 ms on 1024 x 2 Mi elements; 32 registers spill
+  // too much (8.1-8.4 ms), and AMSGrad's 47-54 registers do not fit 40 without a slowdown
+  static constexpr int kMinCtas512 = (sizeof(T) == 4 && !AMSGRAD) ? 3 : 0;
   using Row = AdamRowT<Math>;
   using Hyper = AdamHyper<Math>;
 

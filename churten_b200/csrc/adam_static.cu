@@ -90,7 +90,7 @@ struct StaticAdamOp {
   static constexpr int kThreads = 256;  // measured best on B200: as cb200_adam_step
   static constexpr int kUnroll = 1;
   // resident CTAs of 512 threads the register allocation must allow (launch bound)
-  static constexpr int kMinCtas512 = 1;
+  static constexpr int kMinCtas512 = 0;  // 0: no bound beyond the thread count
   using Row = AdamRow;
   using Hyper = StaticAdamHyper;
 
