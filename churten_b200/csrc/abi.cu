@@ -89,7 +89,7 @@ int device_info(int* sm_count, size_t* l2_bytes) {
 
 extern "C" {
 
-int cb200_version(void) { return 100; }
+int cb200_version(void) { return 200; }  // 0.2.0: from-parts steps, row copy, schedules
 
 const char* cb200_last_error(void) { return cb200::g_last_error.c_str(); }
 
