@@ -466,8 +466,13 @@ def run_ours(args, w, world, rank, local_rank):
 
     # ---- end to end: gradients from pinned host memory, step counters read back ----
     pin_rows = min(n_local, max(1, (1 << 30) // (t * 4)))
-    pinned = torch.empty(pin_rows, t, dtype=torch.float32).normal_(0.0, 1e-3).to(state.grads.dtype).pin_memory()
-    steps_host = torch.empty(n_local, dtype=state.optimizer_state["state_steps"].dtype).pin_memory()
+    from churten_b200 import hostmem
+
+    # pinned staging on the GPU's own NUMA node where the host allows it (matters once several
+    # GPUs pull from the host at the same time)
+    pinned = hostmem.pinned_near(device, (pin_rows, t), state.grads.dtype)
+    pinned.copy_(torch.empty(pin_rows, t, dtype=torch.float32).normal_(0.0, 1e-3))
+    steps_host = hostmem.pinned_near(device, (n_local,), state.optimizer_state["state_steps"].dtype)
     h2d = n_local * t * state.grads.element_size()
     d2h = n_local * 4
 
@@ -540,7 +545,7 @@ def run_ours(args, w, world, rank, local_rank):
                                       f"loss all-gather ({n_local * world * 4} B) on a side stream"},
             "e2e": {"value": job_elems * e2e_steps / (e2e_ms * 1e-3), "unit": "param-updates/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "pipelined_blocks": len(blocks),
+                    "pipelined_blocks": len(blocks), "host": hostmem.describe(device),
                     "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(job_launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

@@ -35,6 +35,7 @@ from typing import Any, Callable
 
 import torch
 
+from churten_b200 import hostmem
 from churten_b200._flag import DeviceFlag
 from churten_b200.state import OptimizerState, State
 
@@ -89,7 +90,8 @@ class Snapshot:
         self._mirror: dict[str, torch.Tensor] = {}
         for name, leaf in live.items():
             # a fresh buffer in any case: the mirror of a CPU state must not alias it
-            host = torch.empty(leaf.shape, dtype=leaf.dtype, pin_memory=self._cuda)
+            host = hostmem.pinned_near(self.device, leaf.shape, leaf.dtype) if self._cuda \
+                else torch.empty(leaf.shape, dtype=leaf.dtype)
             host.copy_(leaf.detach(), non_blocking=self._cuda)
             self._mirror[name] = host
         self._pinned = self._cuda
