@@ -21,7 +21,14 @@ host memory and the step counters read back inside the timed region.
 
 `--impl reference` times the reference's own CPU kernel (oracle/_ref, built from
 its sources; the plain-C restatement if that is absent) on the host cores, on a
-bounded sample of the same workload.
+bounded sample of the same workload.  `--impl reference_cuda` times the reference's
+own CUDA kernels compiled for sm_100a, on the GPU, for comparison.
+
+Other legs, each printing one JSON line of its own instead of the step benchmark:
+`--apply-gradient [--in-place-grads]` (gradient scatter + step, or the step reading
+the gradient tensors in place), `--graph` (CUDA-graph replay), `--snapshot` (best-row
+snapshot: masked row copy device <-> pinned mirror), `--lr-schedule` (one tick of
+each learning-rate policy).  `--rows`, `--row-len`, `--dtype` reshape a workload.
 """
 
 from __future__ import annotations
