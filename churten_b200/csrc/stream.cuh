@@ -7,8 +7,9 @@
 // (replica, 65536-element chunk) pair and lets blocks of frozen replicas exit,
 // src/torchstrap/kernels/csrc/cuda/consolidated.cuh:63-69, cuda/adam.cu:86-89):
 //
-//  * Launch 1, `prologue_kernel`, one 1024-thread block: for every replica row
-//    add the mask to its step counter, and for ACTIVE rows append the row index
+//  * Launch 1, `prologue_kernel`, one 1024-thread block per 1024 rows (a block finds
+//    its place in the list by counting the mask bytes before its rows; blocks never
+//    wait for one another): for every replica row add the mask to its step counter, and for ACTIVE rows append the row index
 //    to a compacted list (order preserved, ballot + prefix sum) together with a
 //    record of that row's scalars (bias corrections, 1 - dampening, the fp64
 //    corrected learning rate ...; 32 bytes, 64 for fp64 storage).  The number of
@@ -26,12 +27,18 @@
 //    bursts, a lock-stepped persistent grid cannot.  The grid is sized from the
 //    host's hint of the active-row count when it has one, else for all rows (the
 //    surplus CTAs exit at once); the kernel strides, so any grid size is correct.
+//    Rows shorter than half a CTA share a CTA (PACKED variant); the gradient buffer
+//    can be replaced by a table of per-parameter gradient tensors that the kernel
+//    gathers from (cb200_grad_parts).
 //  * Launch 2 is issued with programmatic dependent launch: its blocks become
 //    resident while the prologue runs and wait on `griddepcontrol.wait` before
 //    they read the workspace, which hides the second launch latency.
 //
 // No shared memory, no TMA and no tensor cores: the update has no reuse and no
-// contraction; it is bound by HBM bandwidth (12-36 bytes per fp32 element).
+// contraction; it is bound by HBM bandwidth (12-36 bytes per fp32 element).  Staging
+// the tiles through shared memory with cp.async.bulk + mbarrier was measured in
+// hbm_stream_probe.cu: the same 6.9-7.0 TB/s with one CTA per tile, so the plain
+// 16-byte accesses stay.
 #pragma once
 
 #include <cuda_bf16.h>
