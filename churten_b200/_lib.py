@@ -7,11 +7,13 @@ been built, importing this module raises with the command that builds it.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_double, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libchurten_b200.so"
+# CHURTEN_B200_LIB points at another build of the library (e.g. an experimental variant)
+LIB_PATH = Path(os.environ.get("CHURTEN_B200_LIB") or _PKG / "libchurten_b200.so")
 PROBE_LIB_PATH = _PKG / "libchurten_b200_probe.so"
 
 F32, F64, F16, BF16 = 0, 1, 2, 3  # enum cb200_dtype
