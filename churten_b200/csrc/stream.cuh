@@ -160,18 +160,19 @@ __device__ __forceinline__ void store1(T* p, T v) {
 // Where buffer 1 (the gradients) comes from.
 //
 // DenseGrads: the consolidated (n_rows, row_len) matrix, like every other buffer.
-// cb200_grad_parts: the K per-parameter gradient tensors themselves, each
-//   (n_rows, numel[k]) and owning the columns [offset[k], offset[k] + numel[k]) of the
+// cb200_grad_parts: the K per-parameter gradient tensors themselves (same storage type as the
+//   other buffers), each (n_rows, numel[k]) and owning the columns [offset[k], offset[k] + numel[k]) of the
 //   consolidated row, read in place: the consolidated gradient matrix is then
 //   neither written nor read (8 of the 36 bytes per element that scatter + step
 //   move).  Columns no part covers (the alignment pad) read as zero.
 // ---------------------------------------------------------------------------
 struct DenseGrads {};
 
-// One 16-byte group of a row's gradients (4 consecutive fp32 columns from `col0`,
-// a multiple of 4) gathered from the parts.
-template <bool STREAM>
+// One 16-byte group of a row's gradients (16 / sizeof(T) consecutive columns from `col0`, a
+// multiple of that count) gathered from the parts.
+template <bool STREAM, class T>
 __device__ __forceinline__ uint4 gather16(const cb200_grad_parts& gp, int64_t r, int64_t col0) {
+  constexpr int kGroup = 16 / sizeof(T);
   // p: the last part that starts at or before col0 (offsets ascend; no part is empty)
   int lo = 0, hi = gp.n_parts;
   while (lo < hi) {
@@ -185,27 +186,26 @@ __device__ __forceinline__ uint4 gather16(const cb200_grad_parts& gp, int64_t r,
   int p = lo - 1;
   if (p >= 0) {
     const int64_t j = col0 - gp.offset[p];
-    const float* src = static_cast<const float*>(gp.ptr[p]) + r * gp.row_stride[p] + j;
+    const T* src = static_cast<const T*>(gp.ptr[p]) + r * gp.row_stride[p] + j;
     // the common case: the whole group inside one part, and 16-byte aligned there
-    if (j + 4 <= gp.numel[p] && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    if (j + kGroup <= gp.numel[p] && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
       return load16<STREAM>(src);
     }
   }
-  float g[4];
+  uint4 group = make_uint4(0u, 0u, 0u, 0u);  // all-zero bits are +0 in every storage type
+  T* element = reinterpret_cast<T*>(&group);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
+  for (int k = 0; k < kGroup; ++k) {
     const int64_t col = col0 + k;
     if (p + 1 < gp.n_parts && col >= gp.offset[p + 1]) ++p;  // at most one part starts per column
-    g[k] = 0.0f;
     if (p >= 0) {
       const int64_t j = col - gp.offset[p];
       if (j < gp.numel[p]) {
-        g[k] = load1<STREAM>(static_cast<const float*>(gp.ptr[p]) + r * gp.row_stride[p] + j);
+        element[k] = load1<STREAM>(static_cast<const T*>(gp.ptr[p]) + r * gp.row_stride[p] + j);
       }
     }
   }
-  return make_uint4(__float_as_uint(g[0]), __float_as_uint(g[1]), __float_as_uint(g[2]),
-                    __float_as_uint(g[3]));
+  return group;
 }
 
 // Storage <-> math conversions.  `Pack<T>` views one 16-byte access as kVec
@@ -479,7 +479,7 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
         for (int b = 0; b < NB; ++b) {
           if constexpr (kGather) {
             if (b == 1) {
-              raw[u][b] = gather16<STREAM>(grads, r, e0 + u * lane_elems);
+              raw[u][b] = gather16<STREAM, T>(grads, r, e0 + u * lane_elems);
               continue;
             }
           }
@@ -640,9 +640,9 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
 
   const WsView ws = ws_view(workspace, n_rows);
   const bool vec = vector_layout_ok(bufs, row_len, kVec, grad_parts ? 1 : -1);
-  if (grad_parts && (!vec || !std::is_same<T, float>::value)) {
-    return fail(4, "gradients are read from their parts only for fp32 buffers with dense, "
-                   "16-byte aligned rows");
+  if (grad_parts && !vec) {
+    return fail(4, "gradients are read from their parts only for buffers with unit element "
+                   "stride and 16-byte aligned rows");
   }
 
   // The row records are built with the fusion mask of the path that reads them.
@@ -741,10 +741,8 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   if (rows_per_cta > 1) {
     // short rows: one access per thread (unroll is 1 here), several rows per CTA
     if (grad_parts) {
-      if constexpr (std::is_same<T, float>::value) {
-        return stream_hint ? go(stream_kernel<VecOp, 1, true, cb200_grad_parts, true>, *grad_parts)
-                           : go(stream_kernel<VecOp, 1, false, cb200_grad_parts, true>, *grad_parts);
-      }
+      return stream_hint ? go(stream_kernel<VecOp, 1, true, cb200_grad_parts, true>, *grad_parts)
+                         : go(stream_kernel<VecOp, 1, false, cb200_grad_parts, true>, *grad_parts);
     } else if (vec) {
       return stream_hint ? go(stream_kernel<VecOp, 1, true, DenseGrads, true>, DenseGrads{})
                          : go(stream_kernel<VecOp, 1, false, DenseGrads, true>, DenseGrads{});
@@ -754,10 +752,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
     }
   }
   if (grad_parts) {
-    // only instantiated for fp32 storage (checked above)
-    if constexpr (std::is_same<T, float>::value) {
-      CB200_PICK(CB200_GATHER, *grad_parts);
-    }
+    CB200_PICK(CB200_GATHER, *grad_parts);
   } else if (vec) {
     CB200_PICK(CB200_DENSE, DenseGrads{});
   } else {

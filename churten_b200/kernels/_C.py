@@ -201,8 +201,8 @@ class GradParts:
     """The per-parameter gradient tensors of one step, to be read in place by the step kernel
     (`cb200_*_step_from_parts`) instead of a consolidated `(N, T)` gradient matrix.
 
-    `parts` holds `(tensor, first_column, columns)`; each tensor is `(N, ...)` fp32 on the
-    parameters' device with dense rows.  `GradParts.build` returns None when the step cannot
+    `parts` holds `(tensor, first_column, columns)`; each tensor is `(N, ...)` of the parameters'
+    dtype on their device, with dense rows.  `GradParts.build` returns None when the step cannot
     read these gradients in place (the caller then scatters them and takes the plain step).
     """
 
@@ -212,13 +212,13 @@ class GradParts:
     @classmethod
     def build(cls, parts: list[tuple[torch.Tensor, int, int]], params: torch.Tensor) -> "GradParts | None":
         parts = sorted((p for p in parts if p[2] > 0), key=lambda p: p[1])
-        if not 0 < len(parts) <= _lib.MAX_GRAD_PARTS or params.dtype is not torch.float32:
+        if not 0 < len(parts) <= _lib.MAX_GRAD_PARTS or params.dtype not in _DTYPES:
             return None
         n_rows = params.shape[0]
         table = _lib.GradPartsTable()
         table.n_parts = len(parts)
         for k, (t, offset, numel) in enumerate(parts):
-            if not (t.dtype is torch.float32 and t.device == params.device and t.dim() >= 1
+            if not (t.dtype is params.dtype and t.device == params.device and t.dim() >= 1
                     and t.shape[0] == n_rows and t.numel() == n_rows * numel and t[0].is_contiguous()):
                 return None
             table.ptr[k] = t.data_ptr()

@@ -92,17 +92,18 @@ def _plain_cuda_call(params: torch.Tensor) -> bool:
             and not torch.compiler.is_compiling())
 
 
-def _column_ranges(entries, width: int, limit: int):
+def _column_ranges(entries, width: int, limit: int, align: int = 4):
     """Cut the row into column ranges that hold at most `limit` gradient parts each and start
-    at a multiple of 4 columns (16 bytes of fp32, so every range keeps aligned rows).  A part
+    at a multiple of `align` columns (16 bytes of the storage type, so every range keeps
+    aligned rows).  A part
     that straddles a cut is split between the two ranges.  Yields `(c0, c1, parts)` with the
-    parts' columns relative to `c0`.  (With parts of one or two columns and a `limit` below 8
+    parts' columns relative to `c0`.  (With parts of a few columns and a small `limit`
     an aligned cut may not exist where it is needed; the range then exceeds the limit and the
     caller, finding no table for it, scatters instead.)"""
     cuts, count = [0], 0
     for i, (_, offset, _) in enumerate(entries):
         if count == limit:
-            cut = offset - offset % 4
+            cut = offset - offset % align
             if cut > cuts[-1]:
                 cuts.append(cut)
                 # parts that reach past the cut are in the new range too
@@ -123,7 +124,7 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     (name -> `(N, *shape)`), leaving `state.grads` untouched.  Returns False, having done
     nothing, when that is not possible here: the caller then scatters and steps."""
     params = state.flat_params
-    if not params.is_cuda or params.dtype is not torch.float32 or not params.is_contiguous():
+    if not params.is_cuda or not params.is_contiguous():
         return False
     windows = state._windows
     if grads.keys() != windows.keys():
@@ -152,7 +153,8 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
             ranges = [(None, GradParts.build(entries, params2d))]
         else:   # more parameter tensors than one table holds: one launch pair per column range
             ranges = [((c0, c1), GradParts.build(inside, params2d[:, c0:c1]))
-                      for c0, c1, inside in _column_ranges(entries, params2d.shape[1], _lib.MAX_GRAD_PARTS)]
+                      for c0, c1, inside in _column_ranges(entries, params2d.shape[1], _lib.MAX_GRAD_PARTS,
+                                                           align=16 // params2d.element_size())]
         if any(parts is None for _, parts in ranges):
             return False
         for i, (columns, parts) in enumerate(ranges):

@@ -32,8 +32,8 @@ class GradientTransformation(type):
         `materialize=False` (not in the reference) is for loops that never read `state.grads`:
         the step kernel then reads the gradient tensors where they are and `state.grads` keeps
         its old contents -- 28 instead of 36 bytes moved per Adam element.  Where the kernel
-        cannot do that (CPU state, storage other than fp32, gradients whose rows are not
-        dense) the call scatters as usual.  A model with more than 96 parameter tensors is
+        cannot do that (CPU state, gradients whose rows are not dense or whose dtype is not
+        the parameters') the call scatters as usual.  A model with more than 96 parameter tensors is
         stepped in column ranges of at most 96 tensors each.
         """
         if not materialize:

@@ -139,13 +139,13 @@ int cb200_adagrad_step(int dtype, void* params, const void* grads, void* state_s
 /*
  * The three steps with the gradients read IN PLACE from the K per-parameter gradient
  * tensors autograd produced, instead of from the consolidated gradient matrix: part k
- * is an fp32 device matrix of n_rows rows x numel[k] columns (rows row_stride[k]
- * elements apart, element stride 1) and stands for the columns
+ * is a device matrix of the step's storage type, n_rows rows x numel[k] columns (rows
+ * row_stride[k] elements apart, element stride 1) and stands for the columns
  * [offset[k], offset[k] + numel[k]) of every row; offsets ascend, parts do not overlap
  * and none is empty; columns no part covers read as zero.  All other arguments as in
  * cb200_adam_step / cb200_sgd_step / cb200_adagrad_step; `strides` still has one
  * (row, element) pair per buffer in the usual order, the pair of the gradient buffer
- * being ignored.  fp32 storage with dense, 16-byte aligned rows only
+ * being ignored.  The other buffers need unit element stride and 16-byte aligned rows
  * (CB200_ERR_UNSUPPORTED otherwise: scatter and call the plain step).
  * Replaces `apply_gradient` = `_consolidated_grads.update_(grads)` + `update(state)`
  * (src/torchstrap/optimizer/grad_transform.py:28-31) for callers that do not read the

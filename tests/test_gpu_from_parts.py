@@ -128,19 +128,35 @@ def test_falls_back_to_the_scatter_when_it_must(cuda):
     assert_bits_equal("params", in_place.params, scattered.params)
     assert_bits_equal("grads", in_place.grads, scattered.grads)
 
-    # bf16 storage
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("make", [_mlp, _wide], ids=["mlp", "wide"])
+def test_other_storage_types_gather_too(cuda, dtype, make):
     from churten_b200 import optimizer as opts
+    from churten_b200.kernels import _C
     from churten_b200.state import State
 
     torch.manual_seed(0)
-    models = [_mlp().to(cuda, torch.bfloat16) for _ in range(3)]
-    a, b = State.from_models(models), State.from_models(models)
-    for state in (a, b):
-        opts.SGD.init(state, lr=0.125)
-    grads = {n: torch.randn(s, generator=gen, device=cuda).bfloat16() for n, s, _, _ in a.param_meta}
-    opts.SGD.apply_gradient(a, grads)
-    opts.SGD.apply_gradient(b, grads, materialize=False)
-    assert_bits_equal("params", b.params.float(), a.params.float())
+    models = [make().to(cuda, dtype) for _ in range(3)]
+    gen = torch.Generator(device=cuda).manual_seed(4)
+    for cls, hypers in ((opts.SGD, dict(lr=0.125, momentum=0.5)),
+                        (opts.Adam, dict(lr=2.0 ** -7, beta1=0.875, beta2=0.96875, eps=2.0 ** -20))):
+        a, b = State.from_models(models), State.from_models(models)
+        for state in (a, b):
+            cls.init(state, **hypers)
+        for step in range(3):
+            mask = torch.tensor([True, step != 1, True], device=cuda)
+            grads = {n: (torch.randn(s, generator=gen, device=cuda) * 0.1).to(dtype) for n, s, _, _ in a.param_meta}
+            for state in (a, b):
+                state.active_mask.copy_(mask)
+            cls.apply_gradient(a, grads)
+            before = _C.launch_count()
+            cls.apply_gradient(b, grads, materialize=False)
+            assert _C.launch_count() - before == 2          # gathered, not scattered
+        assert_bits_equal("params", b.params.double(), a.params.double())
+        for key, value in a.optimizer_state.tensors().items():
+            assert_bits_equal(key, b.optimizer_state[key].double(), value.double())
 
 
 def _table(entries):
@@ -183,7 +199,6 @@ def test_c_abi_checks_the_table(cuda):
     too_many = _lib.GradPartsTable()
     too_many.n_parts = _lib.MAX_GRAD_PARTS + 1
     assert call(too_many) == bad
-    assert call(_table([(g1, 0, 6), (g2, 6, 8)]), dtype=_lib.BF16) == _lib.ERR_UNSUPPORTED
     assert call(_table([(g1, 0, 6), (g2, 6, 8)]), params=p[:, 1:]) in (bad, _lib.ERR_UNSUPPORTED)
     torch.cuda.synchronize()
     assert not p.any() and not steps.any()                               # nothing ran
