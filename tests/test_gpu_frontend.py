@@ -10,7 +10,6 @@ from torch.func import grad_and_value, vmap
 from torch.nn import Linear, ReLU, Sequential
 from torch.nn.functional import binary_cross_entropy_with_logits
 
-from helpers import f32
 
 pytestmark = pytest.mark.gpu
 

@@ -17,7 +17,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import assert_bits_equal, device_pows, full
+from helpers import assert_bits_equal, device_pows
 
 pytestmark = pytest.mark.gpu
 
