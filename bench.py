@@ -529,6 +529,8 @@ def run_ours(args, w, world, rank, local_rank):
         peak, peak_kind = _peak_gbs()
         achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
         per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else ""))
+        if args.apply_gradient:
+            per_elem = None     # the captures cover the step kernel alone
         # measured on fp32 storage; other storage types move proportionally fewer / more bytes
         traffic = (per_elem * active_elems * ELEMENT_BYTES[args.dtype] / 4) if per_elem is not None else None
         line = {
@@ -579,6 +581,10 @@ def run_ours(args, w, world, rank, local_rank):
 TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {
     # profiles/adam_stream_kernel_c5shard_rows64_ncu.md: 3.3503 GB over 121,634,816 elements
     "adam": 27.54,
+    # profiles/sgd_stream_kernel_c3_rows64_ncu.md (momentum buffer): 1.4172 GB over 73,437,952 elements
+    "sgd": 19.30,
+    # profiles/adagrad_stream_kernel_c4_rows16_ncu.md: 1.2866 GB over 67,108,864 elements
+    "adagrad": 19.17,
 }
 
 
