@@ -1,0 +1,121 @@
+"""Randomised shapes, layouts, masks and hyper-parameters (hypothesis) against the C oracle's
+CUDA formulation, bit for bit: every row length from 0 up, rows packed several to a CTA or
+spanning many tiles, dense and strided buffers, any mask, per-row hyper-parameters, several
+steps in a row."""
+
+import pytest
+import torch
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+import oracle
+from helpers import assert_bits_equal, device_pows, strided_like
+
+pytestmark = pytest.mark.gpu
+
+CUDA = torch.device("cuda:0")
+FAST = settings(max_examples=120, deadline=None, derandomize=True,
+                suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+
+shapes = st.one_of(
+    st.tuples(st.integers(1, 40), st.integers(0, 130)),          # short rows: packed CTAs, ragged tails
+    st.tuples(st.integers(1, 6), st.integers(1000, 9000)),       # several tiles per row
+    st.tuples(st.integers(1025, 2300), st.integers(1, 12)),      # several prologue blocks
+)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import churten_b200.kernels  # noqa: F401
+
+    return torch.ops.torchstrap
+
+
+def _draw(seed, R, T, nbuf):
+    gen = torch.Generator().manual_seed(seed)
+    bufs = [torch.randn(R, T, generator=gen) for _ in range(nbuf)]
+    mask = torch.rand(R, generator=gen) < torch.rand(1, generator=gen)
+    steps = torch.randint(0, 40, (R,), generator=gen).float()
+    lr = torch.exp(torch.empty(R).uniform_(-9.0, -3.0, generator=gen))
+    return gen, bufs, mask, steps, lr
+
+
+def _to_device(bufs, strided):
+    dev = [b.to(CUDA) for b in bufs]
+    return [strided_like(d) for d in dev] if strided else dev
+
+
+@FAST
+@given(shape=shapes, seed=st.integers(0, 10_000), strided=st.booleans(), has_buf=st.booleans(),
+       nesterov=st.booleans(), maximize=st.booleans())
+def test_sgd(ops, shape, seed, strided, has_buf, nesterov, maximize):
+    R, T = shape
+    gen, bufs, mask, steps, lr = _draw(seed, R, T, 3)
+    mom = torch.tensor([0.0, 0.5, 0.9])[torch.randint(0, 3, (R,), generator=gen)] if has_buf else torch.zeros(R)
+    nesterov = nesterov and has_buf
+    if nesterov:
+        mom = mom.clamp_min(0.5)
+    damp = torch.zeros(R) if nesterov else torch.rand(R, generator=gen) * 0.5
+    wd = torch.tensor([0.0, 1e-3])[torch.randint(0, 2, (R,), generator=gen)]
+    dev = _to_device(bufs, strided)
+    dsteps = steps.to(CUDA)
+    side = [x.to(CUDA) for x in (lr, mom, damp, wd)]
+    for _ in range(2):
+        g = torch.randn(R, T, generator=gen)
+        oracle.sgd_step(oracle.CUDA_FORM, bufs[0], g, bufs[2] if has_buf else None, steps, lr, mom, damp, wd,
+                        mask, nesterov, maximize)
+        ops.sgd_step_(dev[0], g.to(CUDA), dev[2] if has_buf else None, dsteps, *side, mask.to(CUDA),
+                      nesterov=nesterov, maximize=maximize)
+    assert_bits_equal("params", dev[0], bufs[0])
+    if has_buf:
+        assert_bits_equal("momentum_buffers", dev[2], bufs[2])
+    assert torch.equal(dsteps.cpu(), steps)
+
+
+@FAST
+@given(shape=shapes, seed=st.integers(0, 10_000), strided=st.booleans(), maximize=st.booleans())
+def test_adagrad(ops, shape, seed, strided, maximize):
+    R, T = shape
+    gen, bufs, mask, steps, lr = _draw(seed, R, T, 3)
+    bufs[2].abs_()
+    decay = torch.tensor([0.0, 1e-4, 1e-2])[torch.randint(0, 3, (R,), generator=gen)]
+    wd = torch.tensor([0.0, 1e-2])[torch.randint(0, 2, (R,), generator=gen)]
+    eps = torch.full((R,), 1e-10)
+    dev = _to_device(bufs, strided)
+    dsteps = steps.to(CUDA)
+    side = [x.to(CUDA) for x in (lr, decay, wd, eps)]
+    for _ in range(2):
+        g = torch.randn(R, T, generator=gen)
+        oracle.adagrad_step(oracle.CUDA_FORM, bufs[0], g, bufs[2], steps, lr, decay, wd, eps, mask, maximize)
+        ops.adagrad_step_(dev[0], g.to(CUDA), dev[2], dsteps, *side, mask.to(CUDA), maximize=maximize)
+    assert_bits_equal("params", dev[0], bufs[0])
+    assert_bits_equal("state_sums", dev[2], bufs[2])
+    assert torch.equal(dsteps.cpu(), steps)
+
+
+@FAST
+@given(shape=shapes, seed=st.integers(0, 10_000), strided=st.booleans(), amsgrad=st.booleans(),
+       adamw=st.booleans(), maximize=st.booleans())
+def test_adam(ops, shape, seed, strided, amsgrad, adamw, maximize):
+    R, T = shape
+    gen, bufs, mask, steps, lr = _draw(seed, R, T, 5)
+    bufs[3].abs_()
+    bufs[4].abs_()
+    b1 = torch.tensor([0.9, 0.95, 0.8])[torch.randint(0, 3, (R,), generator=gen)]
+    b2 = torch.tensor([0.999, 0.99, 0.9999])[torch.randint(0, 3, (R,), generator=gen)]
+    eps = torch.full((R,), 1e-8)
+    wd = torch.tensor([0.0, 1e-2])[torch.randint(0, 2, (R,), generator=gen)]
+    dev = _to_device(bufs, strided)
+    dsteps = steps.to(CUDA)
+    side = [x.to(CUDA) for x in (lr, b1, b2, eps, wd)]
+    for _ in range(2):
+        g = torch.randn(R, T, generator=gen)
+        pows = device_pows(b1, b2, steps + mask.float())
+        oracle.adam_step(oracle.CUDA_FORM, bufs[0], g, bufs[2], bufs[3], bufs[4] if amsgrad else None, steps,
+                         lr, b1, b2, eps, wd, mask, amsgrad, maximize, adamw, pow_override=pows)
+        ops.adam_step_(dev[0], g.to(CUDA), dev[2], dev[3], dev[4] if amsgrad else None, dsteps, *side,
+                       mask.to(CUDA), amsgrad=amsgrad, maximize=maximize, decoupled_weight_decay=adamw)
+    for name, a, b in zip(("params", "-", "exp_avgs", "exp_avg_sqs", "max_exp_avg_sqs"), dev, bufs):
+        if name != "-" and (name != "max_exp_avg_sqs" or amsgrad):
+            assert_bits_equal(name, a, b)
+    assert torch.equal(dsteps.cpu(), steps)
