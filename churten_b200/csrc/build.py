@@ -120,16 +120,49 @@ def build_hbm_probe(force: bool = False) -> bool:
     return True
 
 
+TORCH_BINDING = PKG / "libchurten_b200_torch.so"
+
+
+def build_torch_binding(force: bool = False) -> bool:
+    """The C++ `TORCH_LIBRARY_IMPL` binding over the C ABI (torch_binding.cpp): for the
+    reference's own extension mechanism; the Python package uses the ctypes binding."""
+    import sysconfig
+
+    import torch
+
+    src = CSRC / "torch_binding.cpp"
+    if not force and not _stale(TORCH_BINDING, [src, CSRC.parent.parent / "include" / "churten_b200.h", LIB]):
+        return False
+    torch_dir = Path(torch.__file__).resolve().parent
+    cuda_home = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-D_GLIBCXX_USE_CXX11_ABI=1",
+           f"-I{torch_dir / 'include'}", f"-I{torch_dir / 'include' / 'torch' / 'csrc' / 'api' / 'include'}",
+           f"-I{sysconfig.get_paths()['include']}", f"-I{cuda_home / 'include'}",
+           str(src), "-o", str(TORCH_BINDING),
+           f"-L{PKG}", "-lchurten_b200", "-Wl,-rpath,$ORIGIN",
+           f"-L{torch_dir / 'lib'}", f"-Wl,-rpath,{torch_dir / 'lib'}",
+           "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+           f"-L{cuda_home / 'lib64'}", "-lcudart"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"g++ failed on {src.name}:\n{res.stdout}\n{res.stderr}")
+    return True
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/spill info")
     ap.add_argument("--probe", action="store_true", help="also build churten_b200/hbm_stream_probe")
+    ap.add_argument("--torch-binding", action="store_true",
+                    help="also build churten_b200/libchurten_b200_torch.so (C++ TORCH_LIBRARY_IMPL binding)")
     args = ap.parse_args()
     if args.probe:
         print(f"{HBM_PROBE.name}: {'rebuilt' if build_hbm_probe(args.force) else 'up to date'}")
     for name, rebuilt in build(args.force, args.verbose).items():
         print(f"{name}: {'rebuilt' if rebuilt else 'up to date'}")
+    if args.torch_binding:
+        print(f"{TORCH_BINDING.name}: {'rebuilt' if build_torch_binding(args.force) else 'up to date'}")
 
 
 if __name__ == "__main__":

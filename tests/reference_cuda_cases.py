@@ -1,10 +1,11 @@
 """Seeded cases shared by the two sides of tests/test_gpu_reference_cuda.py.
 
-Run as a script (`python tests/reference_cuda_cases.py <ref_cuda.so> <out.pt>`) this
-file loads the reference's own CUDA kernels (its cuda/*.cu compiled unmodified for
-sm_100a), runs every case through `torch.ops.torchstrap.*` and saves the resulting
-buffers.  It must be a process of its own: that library defines the `torchstrap`
-operators and their CUDA kernels, and so does the package under test.
+Run as a script (`python tests/reference_cuda_cases.py <out.pt> <library.so> [...]`) this
+file loads the given operator libraries in order -- the reference's own CUDA kernels (its
+cuda/*.cu compiled unmodified for sm_100a), or the reference's CPU-only extension followed
+by this package's C++ binding -- runs every case through `torch.ops.torchstrap.*` and saves
+the resulting buffers.  It must be a process of its own: those libraries define the
+`torchstrap` operators and their CUDA kernels, and so does the package under test.
 """
 
 import itertools
@@ -85,8 +86,9 @@ def run(case: dict, d: dict) -> dict:
 
 
 if __name__ == "__main__":
-    library, out_path = sys.argv[1:3]
-    torch.ops.load_library(library)
+    out_path, libraries = sys.argv[1], sys.argv[2:]
+    for library in libraries:
+        torch.ops.load_library(library)
     device = torch.device("cuda:0")
     results = [run(case, inputs(i, case, device)) for i, case in enumerate(cases())]
     torch.cuda.synchronize()

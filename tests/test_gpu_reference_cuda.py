@@ -27,7 +27,7 @@ def reference_results(tmp_path_factory):
     if not LIBRARY.exists():
         pytest.skip("the reference's CUDA kernels have not been built (make -C oracle ref_cuda)")
     out = tmp_path_factory.mktemp("refcuda") / "results.pt"
-    done = subprocess.run([sys.executable, rc.__file__, str(LIBRARY), str(out)],
+    done = subprocess.run([sys.executable, rc.__file__, str(out), str(LIBRARY)],
                           capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stderr[-2000:]
     return torch.load(out)
@@ -45,3 +45,27 @@ def test_every_case_matches_the_reference_kernels(cuda, reference_results):
             assert_bits_equal(f"case {index} {case} {name}", got[name], want[name])
         # the masks did freeze and thaw rows
         assert 0 < float(got["steps"].sum()) < rc.STEPS * case["n"]
+
+
+def test_cpp_binding_matches_the_python_binding(cuda, tmp_path):
+    """`churten_b200/csrc/torch_binding.cpp` (TORCH_LIBRARY_IMPL over the C ABI, the form a
+    maintainer of the reference would compile into its extension) registered on top of the
+    reference's own CPU-only extension: the same cases, the same bits as the ctypes binding."""
+    import churten_b200.kernels  # noqa: F401
+
+    root = Path(__file__).resolve().parents[1]
+    schemas = root / "oracle" / "_ref" / "torchstrap_ref_cpu.so"
+    binding = root / "churten_b200" / "libchurten_b200_torch.so"
+    if not (schemas.exists() and binding.exists()):
+        pytest.skip("needs oracle/_ref and `python -m churten_b200.csrc.build --torch-binding`")
+    out = tmp_path / "cpp.pt"
+    done = subprocess.run([sys.executable, rc.__file__, str(out), str(schemas), str(binding)],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    results = torch.load(out)
+    all_cases = rc.cases()
+    assert len(results) == len(all_cases)
+    for index, (case, want) in enumerate(zip(all_cases, results)):
+        got = rc.run(case, rc.inputs(index, case, cuda))
+        for name in want:
+            assert_bits_equal(f"case {index} {case} {name}", got[name], want[name])
