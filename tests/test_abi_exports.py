@@ -92,3 +92,24 @@ def test_cpu_tensors_have_no_kernel_from_this_package():
     assert torch._C._dispatch_has_kernel_for_dispatch_key("torchstrap::adam_step_", "CUDA")
     src = Path(C.__file__).read_text()
     assert '"CPU"' not in src
+
+
+def test_header_and_library_serve_a_plain_c_program(tmp_path):
+    """tests/c_abi/consumer.c is compiled as C11 against include/churten_b200.h, linked with the
+    library and run: the boundary is a C ABI, not a C++ one."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    exe = tmp_path / "consumer"
+    source = ROOT / "tests" / "c_abi" / "consumer.c"
+    build = subprocess.run(
+        [gcc, "-std=c11", "-Wall", "-Wextra", "-pedantic", "-Werror", f"-I{ROOT / 'include'}", str(source),
+         "-o", str(exe), f"-L{_lib.LIB_PATH.parent}", "-lchurten_b200", f"-Wl,-rpath,{_lib.LIB_PATH.parent}"],
+        capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
+    assert run.stdout.startswith("ok ")
