@@ -230,3 +230,29 @@ def test_side_inputs_on_another_device_are_refused(cuda):
                        amsgrad=False, maximize=False, decoupled_weight_decay=True)
     torch.cuda.synchronize()
     assert torch.equal(bufs[0], before) and steps.abs().sum() == 0
+
+
+def test_a_c_program_steps_through_the_abi(tmp_path):
+    """tests/c_abi/gpu_step.c: CUDA runtime + the C ABI, no PyTorch anywhere in the process."""
+    import os
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    from churten_b200 import _lib as lib_module
+
+    gcc = shutil.which("gcc")
+    cuda_home = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    if gcc is None or not (cuda_home / "include" / "cuda_runtime_api.h").exists():
+        pytest.skip("needs gcc and the CUDA runtime headers")
+    root = Path(__file__).resolve().parents[1]
+    exe = tmp_path / "gpu_step"
+    build = subprocess.run(
+        [gcc, "-std=c11", "-Wall", "-Wextra", "-Werror", f"-I{root / 'include'}", f"-I{cuda_home / 'include'}",
+         str(root / "tests" / "c_abi" / "gpu_step.c"), "-o", str(exe),
+         f"-L{lib_module.LIB_PATH.parent}", "-lchurten_b200", f"-Wl,-rpath,{lib_module.LIB_PATH.parent}",
+         f"-L{cuda_home / 'lib64'}", "-lcudart", f"-Wl,-rpath,{cuda_home / 'lib64'}", "-lm"],
+        capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and run.stdout.strip() == "ok", (run.returncode, run.stdout, run.stderr)
