@@ -119,3 +119,46 @@ def test_adam(ops, shape, seed, strided, amsgrad, adamw, maximize):
         if name != "-" and (name != "max_exp_avg_sqs" or amsgrad):
             assert_bits_equal(name, a, b)
     assert torch.equal(dsteps.cpu(), steps)
+
+
+leaf = st.tuples(st.sampled_from([torch.uint8, torch.bool, torch.bfloat16, torch.float32, torch.float64]),
+                 st.integers(0, 70),          # elements per row
+                 st.integers(0, 5),           # extra elements between rows (strided rows)
+                 st.integers(0, 3))           # elements skipped at the front (misaligned base)
+
+
+@settings(max_examples=60, deadline=None, derandomize=True,
+          suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(n=st.integers(1, 300), leaves=st.lists(leaf, min_size=1, max_size=20), seed=st.integers(0, 10_000),
+       to_host=st.booleans(), invert=st.booleans(), use_mask=st.booleans())
+def test_masked_row_copy(n, leaves, seed, to_host, invert, use_mask):
+    from churten_b200.kernels import _C
+
+    gen = torch.Generator().manual_seed(seed)
+
+    def make(dtype, width, gap, skip, pinned, fill):
+        backing = torch.empty(n * (width + gap) + skip + 8, dtype=torch.float64).uniform_(0, 1, generator=gen)
+        if fill == "random":
+            raw = (backing * 200).to(torch.uint8) if dtype in (torch.uint8, torch.bool) else backing
+            flat = (raw > 100) if dtype is torch.bool else raw.to(dtype)
+        else:
+            flat = torch.zeros(backing.shape, dtype=dtype)
+        flat = flat.pin_memory() if pinned else flat.to(CUDA)
+        return flat[skip: skip + n * (width + gap)].view(n, width + gap)[:, :width]
+
+    pairs = []
+    for dtype, width, gap, skip in leaves:
+        src = make(dtype, width, gap, skip, pinned=False, fill="random")
+        dst = make(dtype, width, gap, skip, pinned=to_host, fill="zeros")
+        pairs.append((dst, src))
+    mask = (torch.rand(n, generator=gen) < 0.5).to(CUDA) if use_mask else None
+    before = [d.clone() for d, _ in pairs]
+    _C.copy_rows_masked(pairs, mask, CUDA, invert=invert)
+    torch.cuda.synchronize()
+    # without a mask every row is copied, whatever `invert` says
+    chosen = torch.ones(n, dtype=torch.bool) if mask is None else (mask.cpu() != invert)
+    for (dst, src), old in zip(pairs, before):
+        want = old.cpu().clone()
+        want[chosen] = src.cpu()[chosen]
+        assert torch.equal(dst.cpu().view(torch.uint8) if dst.dtype is not torch.bool else dst.cpu(),
+                           want.view(torch.uint8) if want.dtype is not torch.bool else want)
