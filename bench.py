@@ -81,6 +81,8 @@ def _bytes_per_elem(w) -> int:
     """Algorithmic bytes per active element (fp32 storage figures scaled by the element size)."""
     scale = ELEMENT_BYTES[w.get("dtype", "f32")]
     if w["opt"] == "adam":
+        if w.get("moment_dtype"):      # fp32 params / grads, 2-byte moments
+            return 24 if w.get("amsgrad") else 20
         return BYTES_PER_ELEM["adam_amsgrad" if w.get("amsgrad") else "adam"] * scale // 4
     return BYTES_PER_ELEM[w["opt"]] * scale // 4
 
@@ -223,6 +225,8 @@ def build_state(w, n_rows, device, seed):
     hyper = _hyper(w, n_rows, gen, device)
     if dtype in (torch.float16, torch.bfloat16) and w["opt"] == "adam":
         hyper.update(beta1=0.875, beta2=0.96875, eps=2.0 ** -20)  # values the half types can hold
+    if w.get("moment_dtype"):
+        hyper["moment_dtype"] = {"bf16": torch.bfloat16, "f16": torch.float16}[w["moment_dtype"]]
     cls.init(state, **hyper)
     if w["frozen"] > 0:
         frozen = torch.rand(n_rows, device=device, generator=gen) < w["frozen"]
@@ -529,8 +533,8 @@ def run_ours(args, w, world, rank, local_rank):
         peak, peak_kind = _peak_gbs()
         achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
         per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else ""))
-        if args.apply_gradient:
-            per_elem = None     # the captures cover the step kernel alone
+        if args.apply_gradient or w.get("moment_dtype"):
+            per_elem = None     # the captures cover the plain step kernels alone
         # measured on fp32 storage; other storage types move proportionally fewer / more bytes
         traffic = (per_elem * active_elems * ELEMENT_BYTES[args.dtype] / 4) if per_elem is not None else None
         line = {
@@ -543,6 +547,7 @@ def run_ours(args, w, world, rank, local_rank):
             "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
                        "row_len": t, "active_rows_rank0": active_rows, "cuda_graph": bool(args.graph),
+                       "moment_dtype": w.get("moment_dtype"),
                        "apply_gradient": bool(args.apply_gradient),
                        "in_place_grads": bool(args.apply_gradient and args.in_place_grads),
                        "l2": "inputs larger than L2 (no flush needed)"
@@ -746,6 +751,8 @@ def main():
     ap.add_argument("--row-len", type=int, default=0, help="override elements per replica (T)")
     ap.add_argument("--dtype", choices=sorted(ELEMENT_BYTES), default="f32",
                     help="storage type of the (N, T) buffers (the headline metric is f32)")
+    ap.add_argument("--moment-dtype", choices=("bf16", "f16"), default=None,
+                    help="Adam with fp32 parameters and 2-byte moment buffers (an extension; not the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--apply-gradient", action="store_true",
                     help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
@@ -771,6 +778,10 @@ def main():
         w["row_len"] = args.row_len
         w.pop("shapes", None)   # one flat parameter tensor of that length
     w["dtype"] = args.dtype
+    if args.moment_dtype:
+        if w["opt"] != "adam" or args.dtype != "f32":
+            sys.exit("--moment-dtype is for Adam workloads with fp32 storage")
+        w["moment_dtype"] = args.moment_dtype
     # rows are padded to 16 bytes by the State allocator: 8 elements for the 2-byte types
     per_access = 16 // ELEMENT_BYTES[args.dtype]
     if per_access > 4:

@@ -75,6 +75,13 @@ SIGNATURES = {
         [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, _P, c_int, c_int, c_int64,
          _P, c_size_t, _P],
     ),
+    "cb200_adam_step_mixed": (
+        c_int,
+        # moment_dtype params grads exp_avgs exp_avg_sqs max_exp_avg_sqs state_steps lr beta1 beta2 eps wd mask
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+         # n_rows row_len amsgrad maximize decoupled steps_already_bumped active_rows_hint ws ws_bytes stream
+         c_int64, c_int64, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P],
+    ),
     "cb200_scatter_rows": (
         c_int,
         # dst dst_row_stride dst_row_len n_rows n_parts parts offsets numels row_strides stream

@@ -1,0 +1,50 @@
+// AdamHyper / AdamOp: the Adam optimizer as the streaming kernels see it (shared by the
+// translation units that instantiate them).
+#pragma once
+
+#include "contraction.h"
+#include "stream.cuh"
+
+namespace cb200 {
+
+template <class M>
+struct AdamHyper {
+  const M* lr;
+  const M* beta1;
+  const M* beta2;
+  const M* eps;
+  const M* weight_decay;
+};
+
+// Buffer order: params, grads, exp_avgs, exp_avg_sqs, [max_exp_avg_sqs].
+template <class T, bool AMSGRAD, bool ADAMW, int FUSE>
+struct AdamOp {
+  using Storage = T;
+  using Math = typename Pack<T>::Math;
+  static constexpr int kBufs = AMSGRAD ? 5 : 4;
+  static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;  // grads are read-only
+  // Measured best on B200.  fp32: 256 x 1, 6.9 TB/s (4 buffers), 6.7 TB/s with AMSGrad.
+  // The other storage types carry 8 (or 2) elements per access and do better with
+  // smaller CTAs: bf16 5.2 against 5.1 TB/s, fp64 6.7 against 6.3 TB/s.
+  static constexpr int kThreads = sizeof(T) == 4 ? 256 : 128;
+  static constexpr int kUnroll = 1;
+  // resident CTAs of 512 threads the register allocation must allow (launch bound)
+  // fp32 without AMSGrad: 40 registers (45 unbounded, one 4-byte spill) for 6 resident CTAs of
+  // 256 threads instead of 5: 7.84 against 7.95 ms on 1024 x 2 Mi elements; 32 registers spill
+  // too much (8.1-8.4 ms), and AMSGrad's 47-54 registers do not fit 40 without a slowdown
+  static constexpr int kMinCtas512 = (sizeof(T) == 4 && !AMSGRAD) ? 3 : 0;
+  using Row = AdamRowT<Math>;
+  using Hyper = AdamHyper<Math>;
+
+  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, Math step) {
+    return adam_row<Math>(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
+  }
+  __device__ static __forceinline__ void apply(Math (&x)[kBufs], const Row& c, int flags) {
+    Math mx = Math(0);
+    if constexpr (AMSGRAD) mx = x[4];
+    adam_elem<AMSGRAD, ADAMW, FUSE, Math>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
+    if constexpr (AMSGRAD) x[4] = mx;
+  }
+};
+
+}  // namespace cb200

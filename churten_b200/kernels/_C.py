@@ -351,6 +351,44 @@ def adam_step_cuda(
         return call.finish(status, params, want_result)
 
 
+def adam_step_mixed_cuda(
+    params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, state_steps,
+    lr, beta1, beta2, eps, weight_decay, active_mask,
+    amsgrad, maximize, decoupled_weight_decay, *, want_result=True, steps_bumped=False,
+):
+    """The Adam step with fp32 params / grads and fp16 or bf16 moment buffers
+    (`cb200_adam_step_mixed`).  Not an operator of the reference: called by the front-end when
+    the state was initialised with `moment_dtype=`; dense buffers only."""
+    op = "churten_b200::adam_step_mixed"
+    _check_consolidated(params, op)
+    moments = [exp_avgs, exp_avg_sqs] + ([max_exp_avg_sqs] if amsgrad else [])
+    if amsgrad and max_exp_avg_sqs is None:
+        raise RuntimeError("amsgrad=True requires max_exp_avg_sqs")
+    if params.dtype is not torch.float32 or grads.dtype is not torch.float32:
+        raise RuntimeError(f"{op}: params and grads must be float32")
+    moment_dtype = exp_avgs.dtype
+    if moment_dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"{op}: moment buffers must be float16 or bfloat16, got {moment_dtype}")
+    for t in (params, grads, *moments):
+        if t.shape != params.shape or t.device != params.device or not t.is_contiguous():
+            raise RuntimeError(f"{op}: every buffer must be dense, of params' shape, on params' device")
+    for t in moments:
+        if t.dtype is not moment_dtype:
+            raise RuntimeError(f"{op}: the moment buffers must share one dtype")
+    with _Call(op, params, state_steps, active_mask, steps_bumped) as call:
+        lr_c, b1_c, b2_c = _hyper(lr, params), _hyper(beta1, params), _hyper(beta2, params)
+        eps_c, wd_c = _hyper(eps, params), _hyper(weight_decay, params)
+        status = _cb.cb200_adam_step_mixed(
+            _DTYPES[moment_dtype][0], params.data_ptr(), grads.data_ptr(), exp_avgs.data_ptr(),
+            exp_avg_sqs.data_ptr(), max_exp_avg_sqs.data_ptr() if amsgrad else None,
+            call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
+            eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(), call.n_rows, call.row_len,
+            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.bumped, call.hint,
+            call.ws.data_ptr(), call.ws.numel(), call.stream,
+        )
+        return call.finish(status, params, want_result)
+
+
 def sgd_step_cuda(
     params, grads, momentum_buffers, state_steps,
     lr, momentum, dampening, weight_decay, active_mask,

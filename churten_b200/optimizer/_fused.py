@@ -28,17 +28,18 @@ class FusedSpec:
     buffers: tuple[str, ...]           # (N, T) state buffers after params and grads, in order
     optional: frozenset                # buffers that may be absent (passed as None)
     flags: tuple[str, ...]             # static flags, in the operator's keyword order
+    mixed: Callable | None = None      # the step for fp32 params with fp16 / bf16 state buffers
 
 
 def populate(spec: FusedSpec, state: State, given: dict[str, Any], buffers: tuple[str, ...],
-             extra_meta: dict[str, Any] | None = None) -> State:
+             extra_meta: dict[str, Any] | None = None, buffer_dtype: torch.dtype | None = None) -> State:
     """Fill `state.optimizer_state` from `given` (the arguments of `init` by name): the
     hyper-parameter vectors (a scalar is broadcast), zeroed buffers, the static flags."""
     for name in spec.hypers:
         state.add_optim_state(name, given[name])
     state.add_optim_state("state_steps", 0)
     for name in buffers:
-        state.add_optim_state(name, per_param=True)
+        state.add_optim_state(name, per_param=True, dtype=buffer_dtype)
     # flags are stored because `apply_gradient` calls `update(state)` without arguments
     for name in spec.flags:
         state.add_optim_meta(name, given[name])
@@ -71,7 +72,14 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None,
         *[_as_1d(opt[name]) for name in spec.hypers],
         _as_1d(state.active_mask),
     )
-    if grads is not None or _plain_cuda_call(params):
+    narrow = [b for b in buffers if b is not None and b.dtype is not params.dtype]
+    if narrow:
+        if spec.mixed is None or grads is not None or columns is not None:
+            raise RuntimeError("state buffers narrower than the parameters are served by Adam's "
+                               "mixed-precision step only, with consolidated gradients")
+        with torch.no_grad():
+            spec.mixed(*args, **flags, want_result=False)
+    elif grads is not None or _plain_cuda_call(params):
         extra = dict(want_result=False, steps_bumped=True) if steps_bumped else dict(want_result=False)
         if params.requires_grad and torch.is_grad_enabled():
             with torch.no_grad():  # the operator is not differentiable; nothing is recorded
@@ -145,8 +153,8 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     entries.sort(key=lambda e: e[1])
     for name in spec.buffers:
         value = state.optimizer_state.get(name)
-        if value is not None and not value.is_contiguous():
-            return False
+        if value is not None and (not value.is_contiguous() or value.dtype is not params.dtype):
+            return False     # (narrow moment buffers take the scatter + mixed-precision step)
     with torch.no_grad():
         params2d = _as_2d(params)
         if len(entries) <= _lib.MAX_GRAD_PARTS:

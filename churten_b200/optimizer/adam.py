@@ -16,6 +16,7 @@ __all__ = ["Adam", "adam_step_"]
 _SPEC = _fused.FusedSpec(
     op=adam_step_,
     direct=_C.adam_step_cuda,
+    mixed=_C.adam_step_mixed_cuda,
     flag_defaults=dict(amsgrad=False, maximize=False, decoupled_weight_decay=True),
     hypers=("lr", "beta1", "beta2", "eps", "weight_decay"),
     buffers=("exp_avgs", "exp_avg_sqs", "max_exp_avg_sqs"),
@@ -40,12 +41,22 @@ class Adam(metaclass=GradientTransformation):
         amsgrad: bool = False,
         maximize: bool = False,
         decoupled_weight_decay: bool = True,
+        moment_dtype: torch.dtype | None = None,
     ) -> State:
-        """Per-replica hyper-parameters, zero moments; the max buffer only with AMSGrad."""
+        """Per-replica hyper-parameters, zero moments; the max buffer only with AMSGrad.
+
+        `moment_dtype=torch.bfloat16` (or float16; not in the reference, which keeps every buffer
+        in the parameters' dtype) stores the moment buffers narrow for fp32 parameters: the same
+        fp32 arithmetic, 20 instead of 28 bytes moved per element, moments rounded on store."""
+        if moment_dtype is not None and moment_dtype is not state.param_buffer_dtype:
+            if state.param_buffer_dtype is not torch.float32 or moment_dtype not in (torch.float16, torch.bfloat16):
+                raise ValueError("moment_dtype must be float16 or bfloat16, for float32 parameters")
+        else:
+            moment_dtype = None
         given = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad,
                      maximize=maximize, decoupled_weight_decay=decoupled_weight_decay)
         buffers = ("exp_avgs", "exp_avg_sqs") + (("max_exp_avg_sqs",) if amsgrad else ())
-        return _fused.populate(_SPEC, state, given, buffers)
+        return _fused.populate(_SPEC, state, given, buffers, buffer_dtype=moment_dtype)
 
     @classmethod
     def update(

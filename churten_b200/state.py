@@ -312,9 +312,11 @@ class State:
         return _GradViews(self.grads, self.param_meta, self._windows)
 
     # -- optimizer state ------------------------------------------------------------
-    def like_tensor(self, value: Any = None, per_param: bool = False) -> torch.Tensor:
-        """None -> zeros, number -> full, tensor -> expand + clone; `(N,)` or `(N, T)`."""
-        dtype, device = self.param_buffer_dtype, self.device
+    def like_tensor(self, value: Any = None, per_param: bool = False,
+                    dtype: torch.dtype | None = None) -> torch.Tensor:
+        """None -> zeros, number -> full, tensor -> expand + clone; `(N,)` or `(N, T)`; in the
+        parameters' dtype unless `dtype` says otherwise."""
+        dtype, device = dtype or self.param_buffer_dtype, self.device
         shape = self.params.shape if per_param else self.batch_size
         if value is None:
             return torch.zeros(shape, dtype=dtype, device=device)
@@ -324,8 +326,9 @@ class State:
             return torch.full(shape, value, dtype=dtype, device=device)
         raise TypeError(f"cannot build an optimizer-state tensor from {type(value).__name__}")
 
-    def add_optim_state(self, key: str, value: Any = None, per_param: bool = False) -> None:
-        self.optimizer_state[key] = self.like_tensor(value, per_param=per_param)
+    def add_optim_state(self, key: str, value: Any = None, per_param: bool = False,
+                        dtype: torch.dtype | None = None) -> None:
+        self.optimizer_state[key] = self.like_tensor(value, per_param=per_param, dtype=dtype)
 
     def add_optim_meta(self, key: str, value: Any) -> None:
         self.optimizer_state.set_meta(key, value)

@@ -185,6 +185,27 @@ int cb200_adagrad_step_from_parts(int dtype, void* params, const cb200_grad_part
                                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The Adam step with fp32 params and grads and the moment buffers (exp_avgs, exp_avg_sqs,
+ * max_exp_avg_sqs) STORED in fp16 or bf16 (`moment_dtype` = CB200_F16 or CB200_BF16): the
+ * arithmetic of cb200_adam_step(CB200_F32, ...) unchanged, moments widened exactly on load and
+ * rounded to nearest even on store; 20 instead of 28 bytes moved per element (24 instead of 36
+ * with AMSGrad).  state_steps and the hyper-parameter vectors are fp32.  Dense buffers only
+ * (unit element stride, rows row_len elements apart, row_len % 4 == 0, params / grads 16-byte
+ * and moment buffers 8-byte aligned): CB200_ERR_UNSUPPORTED otherwise.
+ * No counterpart in the reference, which names low-precision optimizer state as a roadmap
+ * item (README.md:312-316) and keeps all buffers in the parameters' dtype
+ * (src/torchstrap/kernels/csrc/cuda/adam.cu:302-303): an opt-in with its own numerics.
+ */
+int cb200_adam_step_mixed(int moment_dtype, float* params, const float* grads, void* exp_avgs,
+                          void* exp_avg_sqs, void* max_exp_avg_sqs, float* state_steps,
+                          const float* lr, const float* beta1, const float* beta2,
+                          const float* eps, const float* weight_decay,
+                          const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                          int amsgrad, int maximize, int decoupled_weight_decay,
+                          int steps_already_bumped, int64_t active_rows_hint, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/*
  * Scatter K per-parameter gradient tensors into the consolidated (n_rows,
  * dst_row_len) gradient buffer with one launch (per 64 parts).  Part k is an fp32
  * device matrix of n_rows rows x part_numels[k] columns (row stride

@@ -88,6 +88,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_default_cpu_fuse.restype = c_uint
         L.oracle_set_storage.restype = c_int
         L.oracle_set_storage.argtypes = [c_int]
+        L.oracle_set_moment_storage.restype = c_int
+        L.oracle_set_moment_storage.argtypes = [c_int]
         L.oracle_set_threads.restype = c_int
         L.oracle_set_threads.argtypes = [c_int]
         _lib = L
@@ -167,6 +169,14 @@ STORE_F32, STORE_F16, STORE_BF16 = 0, 2, 3
 def set_storage(storage: int) -> int:
     """Emulate fp16 / bf16 buffers in the CUDA formulation (see oracle.h); returns the old setting."""
     return int(lib().oracle_set_storage(storage))
+
+
+STORE_SAME = -1
+
+
+def set_moment_storage(storage: int) -> int:
+    """Emulate fp16 / bf16 storage of Adam's moment buffers alone; returns the old setting."""
+    return int(lib().oracle_set_moment_storage(storage))
 
 
 def set_threads(n: int) -> int:

@@ -72,10 +72,26 @@ int oracle_set_storage(int storage) {
   return old;
 }
 
-static inline float st(float x) {
-  if (g_storage == ORACLE_STORE_BF16) return (float)(__bf16)x;
-  if (g_storage == ORACLE_STORE_F16) return (float)(_Float16)x;
+static inline float narrow(float x, int storage) {
+  if (storage == ORACLE_STORE_BF16) return (float)(__bf16)x;
+  if (storage == ORACLE_STORE_F16) return (float)(_Float16)x;
   return x;
+}
+
+static inline float st(float x) { return narrow(x, g_storage); }
+
+/* Storage of Adam's moment buffers alone (fp32 parameters with fp16 / bf16 optimizer state);
+ * ORACLE_STORE_SAME follows oracle_set_storage. */
+static int g_moment_storage = ORACLE_STORE_SAME;
+
+int oracle_set_moment_storage(int storage) {
+  int old = g_moment_storage;
+  g_moment_storage = storage;
+  return old;
+}
+
+static inline float stm(float x) {
+  return narrow(x, g_moment_storage == ORACLE_STORE_SAME ? g_storage : g_moment_storage);
 }
 
 int oracle_set_threads(int n) {
@@ -161,7 +177,7 @@ static inline void adam_cuda_elem(float* p, float g, float* m, float* v, float* 
   float root;
   if (amsgrad) {
     const float x = std_max(*mx, ev);
-    *mx = st(x);
+    *mx = stm(x);
     root = sqrtf(x);
   } else {
     root = sqrtf(ev);
@@ -169,8 +185,8 @@ static inline void adam_cuda_elem(float* p, float g, float* m, float* v, float* 
   const float denom = root / c->bc2_sqrt + c->eps;
   param = param - (c->step_size * em) / denom;
   *p = st(param);
-  *m = st(em);
-  *v = st(ev);
+  *m = stm(em);
+  *v = stm(ev);
 }
 
 typedef struct {

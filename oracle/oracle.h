@@ -46,8 +46,12 @@ enum { ORACLE_FORM_CUDA = 0, ORACLE_FORM_CPU = 1 };
 /* Storage types the CUDA formulation can emulate on float matrices (values that the
  * type represents exactly); fp32 math throughout, results rounded to nearest-even
  * into the storage type.  Returns the previous setting. */
-enum { ORACLE_STORE_F32 = 0, ORACLE_STORE_F16 = 2, ORACLE_STORE_BF16 = 3 };
+enum { ORACLE_STORE_SAME = -1, ORACLE_STORE_F32 = 0, ORACLE_STORE_F16 = 2, ORACLE_STORE_BF16 = 3 };
 int oracle_set_storage(int storage);
+/* Storage of Adam's moment buffers alone (CUDA form): the emulation of fp32 parameters with
+ * fp16 / bf16 optimizer state, an extension of the new library with no counterpart in the
+ * reference.  ORACLE_STORE_SAME (the default) follows oracle_set_storage. */
+int oracle_set_moment_storage(int storage);
 
 typedef struct {
   float* ptr;

@@ -1,0 +1,135 @@
+"""fp32 parameters with fp16 / bf16 moment buffers (`cb200_adam_step_mixed`, `Adam.init(...,
+moment_dtype=)`): an extension of this library (the reference keeps every buffer in the
+parameters' dtype), so the expected values come from the C oracle's CUDA formulation with
+storage rounding of the moments alone -- the fp32 Adam arithmetic, moments rounded to nearest
+even on store -- bit for bit."""
+
+import pytest
+import torch
+from torch.nn import Linear, ReLU, Sequential
+
+import oracle
+from helpers import assert_bits_equal, device_pows
+
+pytestmark = pytest.mark.gpu
+
+STORE = {torch.float16: oracle.STORE_F16, torch.bfloat16: oracle.STORE_BF16}
+
+
+@pytest.fixture(autouse=True)
+def _restore_oracle_storage():
+    yield
+    oracle.set_moment_storage(oracle.STORE_SAME)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("amsgrad,adamw,maximize", [(False, True, False), (True, False, True), (True, True, False)])
+@pytest.mark.parametrize("R,T", [(1, 4), (7, 44), (5, 1000), (3, 70004), (1500, 8)])
+def test_bit_exact_against_the_oracle_with_narrow_moments(cuda, dtype, amsgrad, adamw, maximize, R, T):
+    from churten_b200.kernels import _C
+
+    gen = torch.Generator().manual_seed(R * 1000 + T)
+    p = torch.randn(R, T, generator=gen)
+    m = torch.zeros(R, T)
+    v = torch.zeros(R, T)
+    mx = torch.zeros(R, T)
+    steps = torch.randint(0, 30, (R,), generator=gen).float()
+    mask = torch.rand(R, generator=gen) < 0.7
+    mask[0] = True
+    lr = torch.exp(torch.empty(R).uniform_(-9.0, -4.0, generator=gen))
+    b1 = torch.tensor([0.9, 0.95, 0.8])[torch.randint(0, 3, (R,), generator=gen)]
+    b2 = torch.tensor([0.999, 0.99, 0.9999])[torch.randint(0, 3, (R,), generator=gen)]
+    eps = torch.full((R,), 1e-8)
+    wd = torch.tensor([0.0, 1e-2])[torch.randint(0, 2, (R,), generator=gen)]
+    dp, dm, dv, dmx = p.to(cuda), m.to(cuda, dtype), v.to(cuda, dtype), mx.to(cuda, dtype)
+    dsteps = steps.to(cuda)
+    side = [x.to(cuda) for x in (lr, b1, b2, eps, wd)]
+    oracle.set_moment_storage(STORE[dtype])
+    for _ in range(3):
+        g = torch.randn(R, T, generator=gen)
+        pows = device_pows(b1, b2, steps + mask.float())
+        oracle.adam_step(oracle.CUDA_FORM, p, g, m, v, mx if amsgrad else None, steps, lr, b1, b2, eps, wd, mask,
+                         amsgrad, maximize, adamw, pow_override=pows)
+        _C.adam_step_mixed_cuda(dp, g.to(cuda), dm, dv, dmx if amsgrad else None, dsteps, *side, mask.to(cuda),
+                                amsgrad, maximize, adamw)
+    assert_bits_equal("params", dp, p)
+    assert_bits_equal("exp_avgs", dm.float(), m)
+    assert_bits_equal("exp_avg_sqs", dv.float(), v)
+    if amsgrad:
+        assert_bits_equal("max_exp_avg_sqs", dmx.float(), mx)
+    assert torch.equal(dsteps.cpu(), steps)
+    assert dm.dtype is dtype and float(dm.float().abs().sum()) > 0
+
+
+def test_front_end_with_narrow_moments(cuda):
+    from churten_b200.kernels import _C
+    from churten_b200.optimizer import SGD, Adam
+    from churten_b200.state import State
+
+    torch.manual_seed(0)
+    models = [Sequential(Linear(6, 9), ReLU(), Linear(9, 2)).to(cuda) for _ in range(4)]
+    narrow, full = State.from_models(models), State.from_models(models)
+    Adam.init(narrow, lr=1e-2, amsgrad=True, moment_dtype=torch.bfloat16)
+    Adam.init(full, lr=1e-2, amsgrad=True)
+    for key in ("exp_avgs", "exp_avg_sqs", "max_exp_avg_sqs"):
+        assert narrow.optimizer_state[key].dtype is torch.bfloat16 and full.optimizer_state[key].dtype is torch.float32
+    assert narrow.optimizer_state["lr"].dtype is torch.float32
+    gen = torch.Generator(device=cuda).manual_seed(1)
+    frozen = narrow.params[2].clone()
+    for state in (narrow, full):
+        state.active_mask[2] = False
+    for _ in range(5):
+        grads = {n: torch.randn(s, generator=gen, device=cuda) * 0.1 for n, s, _, _ in narrow.param_meta}
+        before = _C.launch_count()
+        Adam.apply_gradient(narrow, grads)                           # scatter + mixed step
+        assert _C.launch_count() - before == 3
+        Adam.apply_gradient(full, grads)
+        Adam.apply_gradient(narrow, grads, materialize=False)        # no gather form: scatters as usual
+        Adam.apply_gradient(full, grads, materialize=False)
+    assert torch.equal(narrow.params[2], frozen)
+    assert narrow.optimizer_state["state_steps"].tolist() == [10.0, 10.0, 0.0, 10.0]
+    # same trajectory up to the rounding of the moments
+    torch.testing.assert_close(narrow.params, full.params, rtol=0.0, atol=5e-3)
+    assert not torch.equal(narrow.params, full.params)
+    # narrow state is Adam's alone, and only for fp32 parameters
+    with pytest.raises(TypeError):
+        SGD.init(State.from_models(models), lr=0.1, moment_dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="float32 parameters"):
+        Adam.init(State.from_models([m.double() for m in models]), moment_dtype=torch.bfloat16)
+
+
+def test_argument_checks(cuda):
+    import ctypes
+
+    from churten_b200 import _lib
+    from churten_b200.kernels import _C
+
+    p, g = torch.zeros(2, 8, device=cuda), torch.zeros(2, 8, device=cuda)
+    m, v = torch.zeros(2, 8, device=cuda, dtype=torch.bfloat16), torch.zeros(2, 8, device=cuda, dtype=torch.bfloat16)
+    steps, mask = torch.zeros(2, device=cuda), torch.ones(2, dtype=torch.bool, device=cuda)
+    vec = lambda x: torch.full((2,), x, device=cuda)
+    side = (vec(1e-3), vec(0.9), vec(0.999), vec(1e-8), vec(0.0))
+    with pytest.raises(RuntimeError, match="float16 or bfloat16"):
+        _C.adam_step_mixed_cuda(p, g, m.float(), v.float(), None, steps, *side, mask, False, False, True)
+    with pytest.raises(RuntimeError, match="dense"):
+        _C.adam_step_mixed_cuda(p, g, m.t().contiguous().t(), v, None, steps, *side, mask, False, False, True)
+    with pytest.raises(RuntimeError, match="amsgrad"):
+        _C.adam_step_mixed_cuda(p, g, m, v, None, steps, *side, mask, True, False, True)
+    lib = _lib.lib()
+    ws = torch.empty(lib.cb200_workspace_bytes(2), dtype=torch.uint8, device=cuda)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(dtype=_lib.BF16, row_len=8, params=p):
+        return lib.cb200_adam_step_mixed(dtype, ptr(params), ptr(g), ptr(m), ptr(v), None, ptr(steps),
+                                         *[ptr(s) for s in side], ptr(mask), 2, row_len, 0, 0, 1, 0, -1,
+                                         ptr(ws), ws.numel(), stream)
+
+    assert call(dtype=_lib.F32) == _lib.ERR_INVALID_ARGUMENT
+    assert call(row_len=6) == _lib.ERR_UNSUPPORTED
+    assert call(params=p.view(-1)[1:9]) == _lib.ERR_UNSUPPORTED
+    torch.cuda.synchronize()
+    assert not steps.any()
+    assert call() == _lib.OK
+    torch.cuda.synchronize()
+    assert steps.tolist() == [1.0, 1.0]
