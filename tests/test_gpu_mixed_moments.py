@@ -133,3 +133,38 @@ def test_argument_checks(cuda):
     assert call() == _lib.OK
     torch.cuda.synchronize()
     assert steps.tolist() == [1.0, 1.0]
+
+
+def test_narrow_moments_with_snapshot_and_graph_replay(cuda):
+    from churten_b200.checkpoint import Snapshot
+    from churten_b200.graphs import GraphedUpdate
+    from churten_b200.optimizer import Adam
+    from churten_b200.state import State
+
+    torch.manual_seed(0)
+    models = [Sequential(Linear(6, 9), ReLU(), Linear(9, 2)).to(cuda) for _ in range(4)]
+    eager, graphed = State.from_models(models), State.from_models(models)
+    for state in (eager, graphed):
+        Adam.init(state, lr=1e-2, moment_dtype=torch.float16)
+    step = GraphedUpdate(Adam, graphed)
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    for it in range(4):
+        g = torch.randn(eager.params.shape, generator=gen, device=cuda) * 0.1
+        g[:, -1:] = 0       # the pad lane (T = 83 -> 84)
+        for state in (eager, graphed):
+            state.grads.copy_(g)
+            state.active_mask[1] = it != 2
+        Adam.update(eager)
+        step()
+    assert_bits_equal("params", graphed.params, eager.params)
+    assert_bits_equal("exp_avgs", graphed.optimizer_state["exp_avgs"].float(), eager.optimizer_state["exp_avgs"].float())
+    # the mirror keeps each leaf in its own dtype
+    snap = Snapshot(eager)
+    assert snap.mirror["optimizer_state/exp_avgs"].dtype is torch.float16
+    kept = {k: v.clone() for k, v in eager.optimizer_state.tensors().items()}
+    eager.optimizer_state["exp_avgs"].zero_()
+    eager.params.add_(1.0)
+    snap.restore_to_live(eager)
+    assert_bits_equal("params", eager.params, graphed.params)
+    for key, value in kept.items():
+        assert torch.equal(eager.optimizer_state[key], value), key
