@@ -72,11 +72,14 @@ struct Quad<__nv_bfloat16> {
 
 // GROUPS quads per thread: 1 (any row_len % 4 == 0) or 2 (row_len % 8 == 0: the two quads are
 // adjacent, so the moments travel in one 16-byte access).
-template <class TM, bool AMSGRAD, bool ADAMW, bool STREAM, int GROUPS>
+// Grads: DenseGrads (the consolidated gradient matrix) or cb200_grad_parts (the per-parameter
+// gradient tensors, gathered 16 bytes at a time as in stream_kernel).
+template <class TM, bool AMSGRAD, bool ADAMW, bool STREAM, int GROUPS, class Grads>
 __global__ void __launch_bounds__(512)
 adam_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, TM* __restrict__ exp_avgs,
                   TM* __restrict__ exp_avg_sqs, TM* __restrict__ max_exp_avg_sqs, WsView ws,
-                  int64_t row_len, int64_t tiles_per_row, int flags) {
+                  int64_t row_len, int64_t tiles_per_row, int flags, Grads parts) {
+  constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
   pdl_wait();
   const int n_active = ws.header->n_active;
   const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
@@ -88,7 +91,8 @@ adam_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, T
     const int64_t a = item / tiles_per_row;
     const int64_t e0 = (item - a * tiles_per_row) * tile_elems + static_cast<int64_t>(threadIdx.x) * 4 * GROUPS;
     if (e0 >= row_len) continue;
-    const int64_t at = static_cast<int64_t>(ws.ids[a]) * row_len + e0;
+    const int64_t r = ws.ids[a];
+    const int64_t at = r * row_len + e0;
     const AdamRowT<float> c = rows[a];
 
     uint4 p_raw[GROUPS], g_raw[GROUPS];
@@ -96,7 +100,11 @@ adam_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, T
 #pragma unroll
     for (int q = 0; q < GROUPS; ++q) {
       p_raw[q] = load16<STREAM>(params + at + 4 * q);
-      g_raw[q] = load16<STREAM>(grads + at + 4 * q);
+      if constexpr (kGather) {
+        g_raw[q] = gather16<STREAM, float>(parts, r, e0 + 4 * q);
+      } else {
+        g_raw[q] = load16<STREAM>(grads + at + 4 * q);
+      }
       x_raw[q] = make_uint2(0u, 0u);
     }
     if constexpr (GROUPS == 2) {
@@ -160,6 +168,7 @@ struct MixedArgs {
   void* workspace;
   size_t workspace_bytes;
   cudaStream_t stream;
+  const cb200_grad_parts* parts;  // NULL: gradients come from `grads`
 };
 
 template <class TM, bool AMSGRAD, bool ADAMW>
@@ -202,17 +211,19 @@ int mixed_run(const MixedArgs& a) {
   TM* v = static_cast<TM*>(a.exp_avg_sqs);
   TM* mx = static_cast<TM*>(a.max_exp_avg_sqs);
   const dim3 grid(static_cast<unsigned>(want)), block(threads);
-  auto go = [&](auto kernel) {
+  auto go = [&](auto kernel, auto source) {
     return launch_dependent(kernel, grid, block, a.stream, a.params, a.grads, m, v, mx, ws, a.row_len,
-                            tiles_per_row, a.flags);
+                            tiles_per_row, a.flags, source);
   };
-  if (groups == 2) {
-    err = stream_hint ? go(adam_mixed_kernel<TM, AMSGRAD, ADAMW, true, 2>)
-                      : go(adam_mixed_kernel<TM, AMSGRAD, ADAMW, false, 2>);
+#define CB200_MIXED(GROUPS, GRADS, SOURCE)                                                   \
+  (stream_hint ? go(adam_mixed_kernel<TM, AMSGRAD, ADAMW, true, GROUPS, GRADS>, SOURCE)      \
+               : go(adam_mixed_kernel<TM, AMSGRAD, ADAMW, false, GROUPS, GRADS>, SOURCE))
+  if (a.parts) {
+    err = groups == 2 ? CB200_MIXED(2, cb200_grad_parts, *a.parts) : CB200_MIXED(1, cb200_grad_parts, *a.parts);
   } else {
-    err = stream_hint ? go(adam_mixed_kernel<TM, AMSGRAD, ADAMW, true, 1>)
-                      : go(adam_mixed_kernel<TM, AMSGRAD, ADAMW, false, 1>);
+    err = groups == 2 ? CB200_MIXED(2, DenseGrads, DenseGrads{}) : CB200_MIXED(1, DenseGrads, DenseGrads{});
   }
+#undef CB200_MIXED
   if (err != cudaSuccess) return cuda_fail(err, "mixed-precision step launch");
   count_launches(1);
   return CB200_OK;
@@ -229,7 +240,11 @@ bool aligned(const void* p, uintptr_t to) { return reinterpret_cast<uintptr_t>(p
 }  // namespace
 }  // namespace cb200
 
-extern "C" int cb200_adam_step_mixed(int moment_dtype, float* params, const float* grads,
+namespace cb200 {
+namespace {
+
+// The body of both entry points: exactly one of `grads` and `parts` is given.
+int mixed_entry(int moment_dtype, float* params, const float* grads, const cb200_grad_parts* parts,
                                      void* exp_avgs, void* exp_avg_sqs, void* max_exp_avg_sqs,
                                      float* state_steps, const float* lr, const float* beta1,
                                      const float* beta2, const float* eps, const float* weight_decay,
@@ -237,7 +252,6 @@ extern "C" int cb200_adam_step_mixed(int moment_dtype, float* params, const floa
                                      int amsgrad, int maximize, int decoupled_weight_decay,
                                      int steps_already_bumped, int64_t active_rows_hint,
                                      void* workspace, size_t workspace_bytes, void* stream) {
-  using namespace cb200;
   if (n_rows < 0 || row_len < 0) return fail(CB200_ERR_INVALID_ARGUMENT, "n_rows and row_len must be >= 0");
   if (n_rows > 0x7fffffffLL) return fail(CB200_ERR_INVALID_ARGUMENT, "n_rows must fit in 31 bits");
   if (moment_dtype != kF16 && moment_dtype != kBF16) {
@@ -249,12 +263,17 @@ extern "C" int cb200_adam_step_mixed(int moment_dtype, float* params, const floa
                                             "must not be NULL");
   }
   const bool has_data = row_len > 0;
-  if (has_data && (!params || !grads || !exp_avgs || !exp_avg_sqs || (amsgrad && !max_exp_avg_sqs))) {
+  if (parts) {
+    if (int rc = check_grad_parts(parts, row_len)) return rc;
+  }
+  if (has_data && (!params || (!grads && !parts) || !exp_avgs || !exp_avg_sqs ||
+                   (amsgrad && !max_exp_avg_sqs))) {
     return fail(CB200_ERR_INVALID_ARGUMENT, amsgrad && !max_exp_avg_sqs
                                                 ? "amsgrad=True requires max_exp_avg_sqs"
                                                 : "params, grads and the moment buffers must not be NULL");
   }
-  if (has_data && (row_len % 4 != 0 || !aligned(params, 16) || !aligned(grads, 16) || !aligned(exp_avgs, 8) ||
+  if (has_data && (row_len % 4 != 0 || !aligned(params, 16) || (!parts && !aligned(grads, 16)) ||
+                   !aligned(exp_avgs, 8) ||
                    !aligned(exp_avg_sqs, 8) || (amsgrad && !aligned(max_exp_avg_sqs, 8)))) {
     return fail(CB200_ERR_UNSUPPORTED, "the mixed-precision step needs row_len % 4 == 0, 16-byte aligned "
                                        "params / grads and 8-byte aligned moment buffers");
@@ -279,6 +298,38 @@ extern "C" int cb200_adam_step_mixed(int moment_dtype, float* params, const floa
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
+  a.parts = parts;
   return moment_dtype == kF16 ? mixed_variant<__half>(a, amsgrad != 0, decoupled_weight_decay != 0)
                               : mixed_variant<__nv_bfloat16>(a, amsgrad != 0, decoupled_weight_decay != 0);
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" int cb200_adam_step_mixed(int moment_dtype, float* params, const float* grads,
+                                     void* exp_avgs, void* exp_avg_sqs, void* max_exp_avg_sqs,
+                                     float* state_steps, const float* lr, const float* beta1,
+                                     const float* beta2, const float* eps, const float* weight_decay,
+                                     const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                                     int amsgrad, int maximize, int decoupled_weight_decay,
+                                     int steps_already_bumped, int64_t active_rows_hint,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+  return cb200::mixed_entry(moment_dtype, params, grads, nullptr, exp_avgs, exp_avg_sqs, max_exp_avg_sqs,
+                            state_steps, lr, beta1, beta2, eps, weight_decay, active_mask, n_rows, row_len,
+                            amsgrad, maximize, decoupled_weight_decay, steps_already_bumped,
+                            active_rows_hint, workspace, workspace_bytes, stream);
+}
+
+extern "C" int cb200_adam_step_mixed_from_parts(
+    int moment_dtype, float* params, const cb200_grad_parts* grad_parts, void* exp_avgs,
+    void* exp_avg_sqs, void* max_exp_avg_sqs, float* state_steps, const float* lr, const float* beta1,
+    const float* beta2, const float* eps, const float* weight_decay, const uint8_t* active_mask,
+    int64_t n_rows, int64_t row_len, int amsgrad, int maximize, int decoupled_weight_decay,
+    int steps_already_bumped, int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
+    void* stream) {
+  if (!grad_parts) return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "grad_parts must not be NULL");
+  return cb200::mixed_entry(moment_dtype, params, nullptr, grad_parts, exp_avgs, exp_avg_sqs,
+                            max_exp_avg_sqs, state_steps, lr, beta1, beta2, eps, weight_decay, active_mask,
+                            n_rows, row_len, amsgrad, maximize, decoupled_weight_decay,
+                            steps_already_bumped, active_rows_hint, workspace, workspace_bytes, stream);
 }

@@ -364,12 +364,13 @@ def adam_step_mixed_cuda(
     moments = [exp_avgs, exp_avg_sqs] + ([max_exp_avg_sqs] if amsgrad else [])
     if amsgrad and max_exp_avg_sqs is None:
         raise RuntimeError("amsgrad=True requires max_exp_avg_sqs")
-    if params.dtype is not torch.float32 or grads.dtype is not torch.float32:
+    from_parts = isinstance(grads, GradParts)
+    if params.dtype is not torch.float32 or (not from_parts and grads.dtype is not torch.float32):
         raise RuntimeError(f"{op}: params and grads must be float32")
     moment_dtype = exp_avgs.dtype
     if moment_dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError(f"{op}: moment buffers must be float16 or bfloat16, got {moment_dtype}")
-    for t in (params, grads, *moments):
+    for t in (params, *([] if from_parts else [grads]), *moments):
         if t.shape != params.shape or t.device != params.device or not t.is_contiguous():
             raise RuntimeError(f"{op}: every buffer must be dense, of params' shape, on params' device")
     for t in moments:
@@ -378,8 +379,10 @@ def adam_step_mixed_cuda(
     with _Call(op, params, state_steps, active_mask, steps_bumped) as call:
         lr_c, b1_c, b2_c = _hyper(lr, params), _hyper(beta1, params), _hyper(beta2, params)
         eps_c, wd_c = _hyper(eps, params), _hyper(weight_decay, params)
-        status = _cb.cb200_adam_step_mixed(
-            _DTYPES[moment_dtype][0], params.data_ptr(), grads.data_ptr(), exp_avgs.data_ptr(),
+        entry = _cb.cb200_adam_step_mixed_from_parts if from_parts else _cb.cb200_adam_step_mixed
+        status = entry(
+            _DTYPES[moment_dtype][0], params.data_ptr(),
+            ctypes.byref(grads.table) if from_parts else grads.data_ptr(), exp_avgs.data_ptr(),
             exp_avg_sqs.data_ptr(), max_exp_avg_sqs.data_ptr() if amsgrad else None,
             call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
             eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(), call.n_rows, call.row_len,

@@ -74,9 +74,9 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None,
     )
     narrow = [b for b in buffers if b is not None and b.dtype is not params.dtype]
     if narrow:
-        if spec.mixed is None or grads is not None or columns is not None:
+        if spec.mixed is None or columns is not None:
             raise RuntimeError("state buffers narrower than the parameters are served by Adam's "
-                               "mixed-precision step only, with consolidated gradients")
+                               "mixed-precision step only")
         with torch.no_grad():
             spec.mixed(*args, **flags, want_result=False)
     elif grads is not None or _plain_cuda_call(params):
@@ -153,8 +153,11 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     entries.sort(key=lambda e: e[1])
     for name in spec.buffers:
         value = state.optimizer_state.get(name)
-        if value is not None and (not value.is_contiguous() or value.dtype is not params.dtype):
-            return False     # (narrow moment buffers take the scatter + mixed-precision step)
+        if value is not None and not value.is_contiguous():
+            return False
+        if value is not None and value.dtype is not params.dtype and (
+                spec.mixed is None or len(entries) > _lib.MAX_GRAD_PARTS):
+            return False     # narrow moments: one gradient-parts table, Adam only
     with torch.no_grad():
         params2d = _as_2d(params)
         if len(entries) <= _lib.MAX_GRAD_PARTS:

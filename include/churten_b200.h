@@ -204,6 +204,17 @@ int cb200_adam_step_mixed(int moment_dtype, float* params, const float* grads, v
                           int amsgrad, int maximize, int decoupled_weight_decay,
                           int steps_already_bumped, int64_t active_rows_hint, void* workspace,
                           size_t workspace_bytes, void* stream);
+/* The same with the fp32 gradients read in place from their per-parameter tensors (see
+ * cb200_adam_step_from_parts): scatter + fp32 step move 36 bytes per element, this call 20. */
+int cb200_adam_step_mixed_from_parts(int moment_dtype, float* params,
+                                     const cb200_grad_parts* grad_parts, void* exp_avgs,
+                                     void* exp_avg_sqs, void* max_exp_avg_sqs, float* state_steps,
+                                     const float* lr, const float* beta1, const float* beta2,
+                                     const float* eps, const float* weight_decay,
+                                     const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                                     int amsgrad, int maximize, int decoupled_weight_decay,
+                                     int steps_already_bumped, int64_t active_rows_hint,
+                                     void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Scatter K per-parameter gradient tensors into the consolidated (n_rows,

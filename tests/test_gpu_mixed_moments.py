@@ -84,7 +84,9 @@ def test_front_end_with_narrow_moments(cuda):
         Adam.apply_gradient(narrow, grads)                           # scatter + mixed step
         assert _C.launch_count() - before == 3
         Adam.apply_gradient(full, grads)
-        Adam.apply_gradient(narrow, grads, materialize=False)        # no gather form: scatters as usual
+        before = _C.launch_count()
+        Adam.apply_gradient(narrow, grads, materialize=False)        # gathered gradients + narrow moments
+        assert _C.launch_count() - before == 2
         Adam.apply_gradient(full, grads, materialize=False)
     assert torch.equal(narrow.params[2], frozen)
     assert narrow.optimizer_state["state_steps"].tolist() == [10.0, 10.0, 0.0, 10.0]
@@ -168,3 +170,29 @@ def test_narrow_moments_with_snapshot_and_graph_replay(cuda):
     assert_bits_equal("params", eager.params, graphed.params)
     for key, value in kept.items():
         assert torch.equal(eager.optimizer_state[key], value), key
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gathered_gradients_with_narrow_moments_equal_scatter_then_step(cuda, dtype):
+    from churten_b200.optimizer import Adam
+    from churten_b200.state import State
+
+    torch.manual_seed(0)
+    # odd sizes: 16-byte groups of gradients straddle parts; 77k columns: many tiles
+    models = [Sequential(Linear(300, 257), ReLU(), Linear(257, 3), ReLU(), Linear(3, 1)).to(cuda) for _ in range(3)]
+    scattered, gathered = State.from_models(models), State.from_models(models)
+    for state in (scattered, gathered):
+        Adam.init(state, lr=1e-2, weight_decay=1e-2, amsgrad=True, moment_dtype=dtype)
+    gen = torch.Generator(device=cuda).manual_seed(2)
+    untouched = gathered.grads.clone()
+    for step in range(3):
+        mask = torch.tensor([True, step != 1, True], device=cuda)
+        grads = {n: torch.randn(s, generator=gen, device=cuda) * 0.1 for n, s, _, _ in scattered.param_meta}
+        for state in (scattered, gathered):
+            state.active_mask.copy_(mask)
+        Adam.apply_gradient(scattered, grads)
+        Adam.apply_gradient(gathered, grads, materialize=False)
+    assert_bits_equal("params", gathered.params, scattered.params)
+    for key, value in scattered.optimizer_state.tensors().items():
+        assert_bits_equal(key, gathered.optimizer_state[key].float(), value.float())
+    assert torch.equal(gathered.grads, untouched)
