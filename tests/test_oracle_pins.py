@@ -174,3 +174,43 @@ def test_cuda_form_with_low_precision_storage_matches_torch_fixtures(index, lowp
     for name, value in want.items():
         if name != "pows":
             assert_bits_equal(f"{_ids(case)}: {name}", got[name], value)
+
+
+def test_moment_only_storage_rounds_the_moments_and_nothing_else():
+    """`oracle_set_moment_storage`: the emulation behind the mixed-precision Adam tests.  With
+    bf16 moment storage the moments are bf16 values, the parameters stay full fp32 values, the
+    first step's parameters equal the fp32 run's (the update uses the unrounded moments), and
+    the default setting changes nothing."""
+    gen = torch.Generator().manual_seed(5)
+    R, T = 3, 40
+
+    def run(moment_storage, steps_n):
+        g0 = torch.Generator().manual_seed(6)
+        p = torch.randn(R, T, generator=g0)
+        m, v = torch.zeros(R, T), torch.zeros(R, T)
+        steps = torch.zeros(R)
+        vec = lambda x: torch.full((R,), x)
+        mask = torch.tensor([True, False, True])
+        old = oracle.set_moment_storage(moment_storage)
+        try:
+            for _ in range(steps_n):
+                g = torch.randn(R, T, generator=g0)
+                oracle.adam_step(oracle.CUDA_FORM, p, g, m, v, None, steps, vec(1e-2), vec(0.9), vec(0.999),
+                                 vec(1e-8), vec(0.0), mask, False, False, True)
+        finally:
+            oracle.set_moment_storage(old)
+        return p, m, v
+
+    p32, m32, v32 = run(oracle.STORE_SAME, 1)
+    p16, m16, v16 = run(oracle.STORE_BF16, 1)
+    assert torch.equal(p16, p32)                                   # step 1 reads zero moments
+    assert torch.equal(m16, m32.bfloat16().float()) and torch.equal(v16, v32.bfloat16().float())
+    assert not torch.equal(m16, m32)
+    p32, m32, _ = run(oracle.STORE_SAME, 4)
+    p16, m16, _ = run(oracle.STORE_BF16, 4)
+    assert not torch.equal(p16, p32) and torch.allclose(p16, p32, atol=1e-3)
+    assert torch.equal(m16, m16.bfloat16().float())                # representable in bf16
+    assert not torch.equal(p16, p16.bfloat16().float())            # parameters are not rounded
+    again, _, _ = run(oracle.STORE_SAME, 4)
+    assert torch.equal(again, p32)                                 # the switch was restored
+    del gen
