@@ -88,6 +88,13 @@ SIGNATURES = {
         [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
          c_int64, c_int64, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P],
     ),
+    "cb200_sgd_step_mixed": (
+        c_int,
+        # buffer_dtype params grads momentum_buffers state_steps lr momentum dampening wd mask nesterov_rows
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+         # n_rows row_len nesterov maximize steps_already_bumped active_rows_hint ws ws_bytes stream
+         c_int64, c_int64, c_int, c_int, c_int, c_int64, _P, c_size_t, _P],
+    ),
     "cb200_scatter_rows": (
         c_int,
         # dst dst_row_stride dst_row_len n_rows n_parts parts offsets numels row_strides stream

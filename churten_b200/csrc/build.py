@@ -28,9 +28,9 @@ PROBE_LIB = PKG / "libchurten_b200_probe.so"
 HBM_PROBE = PKG / "hbm_stream_probe"
 
 LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu", "scatter.cu",
-               "rowcopy.cu", "lr_schedule.cu", "adam_mixed.cu"]
+               "rowcopy.cu", "lr_schedule.cu", "adam_mixed.cu", "sgd_mixed.cu"]
 PROBE_SOURCES = ["probe.cu"]
-HEADERS = ["rowmath.cuh", "stream.cuh", "contraction.h", "adam_op.cuh", "../../include/churten_b200.h"]
+HEADERS = ["rowmath.cuh", "stream.cuh", "contraction.h", "adam_op.cuh", "sgd_op.cuh", "narrow.cuh", "../../include/churten_b200.h"]
 
 NVCC_FLAGS = [
     "-std=c++17",

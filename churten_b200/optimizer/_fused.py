@@ -29,6 +29,7 @@ class FusedSpec:
     optional: frozenset                # buffers that may be absent (passed as None)
     flags: tuple[str, ...]             # static flags, in the operator's keyword order
     mixed: Callable | None = None      # the step for fp32 params with fp16 / bf16 state buffers
+    mixed_takes_parts: bool = False    # ... and whether it can read the gradients from their parts
 
 
 def populate(spec: FusedSpec, state: State, given: dict[str, Any], buffers: tuple[str, ...],
@@ -75,8 +76,8 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None,
     narrow = [b for b in buffers if b is not None and b.dtype is not params.dtype]
     if narrow:
         if spec.mixed is None or columns is not None:
-            raise RuntimeError("state buffers narrower than the parameters are served by Adam's "
-                               "mixed-precision step only")
+            raise RuntimeError("state buffers narrower than the parameters are served by the "
+                               "mixed-precision steps of Adam and SGD only")
         with torch.no_grad():
             spec.mixed(*args, **flags, want_result=False)
     elif grads is not None or _plain_cuda_call(params):
@@ -156,8 +157,8 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
         if value is not None and not value.is_contiguous():
             return False
         if value is not None and value.dtype is not params.dtype and (
-                spec.mixed is None or len(entries) > _lib.MAX_GRAD_PARTS):
-            return False     # narrow moments: one gradient-parts table, Adam only
+                not spec.mixed_takes_parts or len(entries) > _lib.MAX_GRAD_PARTS):
+            return False     # narrow state: one gradient-parts table, Adam only
     with torch.no_grad():
         params2d = _as_2d(params)
         if len(entries) <= _lib.MAX_GRAD_PARTS:

@@ -17,6 +17,7 @@ _SPEC = _fused.FusedSpec(
     op=adam_step_,
     direct=_C.adam_step_cuda,
     mixed=_C.adam_step_mixed_cuda,
+    mixed_takes_parts=True,
     flag_defaults=dict(amsgrad=False, maximize=False, decoupled_weight_decay=True),
     hypers=("lr", "beta1", "beta2", "eps", "weight_decay"),
     buffers=("exp_avgs", "exp_avg_sqs", "max_exp_avg_sqs"),

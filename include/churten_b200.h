@@ -217,6 +217,22 @@ int cb200_adam_step_mixed_from_parts(int moment_dtype, float* params,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * SGD with momentum, fp32 params and grads, the momentum buffer STORED in fp16 or bf16
+ * (`buffer_dtype` = CB200_F16 or CB200_BF16): the arithmetic of cb200_sgd_step(CB200_F32) with a
+ * buffer, the buffer widened exactly on load and rounded to nearest even on store; 16 instead
+ * of 20 bytes per element.  Dense buffers only, as for cb200_adam_step_mixed.  No counterpart in
+ * the reference (a roadmap item there, README.md:312-316): an opt-in with its own numerics.
+ */
+int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float* grads,
+                         void* momentum_buffers, float* state_steps, const float* lr,
+                         const float* momentum, const float* dampening,
+                         const float* weight_decay, const uint8_t* active_mask,
+                         const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len,
+                         int nesterov, int maximize, int steps_already_bumped,
+                         int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/*
  * Scatter K per-parameter gradient tensors into the consolidated (n_rows,
  * dst_row_len) gradient buffer with one launch (per 64 parts).  Part k is an fp32
  * device matrix of n_rows rows x part_numels[k] columns (row stride

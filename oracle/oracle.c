@@ -329,7 +329,7 @@ static inline void sgd_cuda_elem(float* p, float g, float* buf, float lr, float 
     } else {
       b = fmaf(one_minus_damp, g, momentum * *buf);
     }
-    *buf = st(b);
+    *buf = stm(b); /* the momentum buffer follows the optimizer-state storage switch */
     g = nesterov ? fmaf(momentum, b, g) : b;
   }
   *p = st(fmaf(-lr, g, param));

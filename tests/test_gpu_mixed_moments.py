@@ -196,3 +196,64 @@ def test_gathered_gradients_with_narrow_moments_equal_scatter_then_step(cuda, dt
     for key, value in scattered.optimizer_state.tensors().items():
         assert_bits_equal(key, gathered.optimizer_state[key].float(), value.float())
     assert torch.equal(gathered.grads, untouched)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("nesterov,maximize", [(False, False), (True, True)])
+@pytest.mark.parametrize("R,T", [(1, 4), (7, 44), (5, 1000), (3, 70004), (1500, 8)])
+def test_sgd_bit_exact_against_the_oracle_with_a_narrow_buffer(cuda, dtype, nesterov, maximize, R, T):
+    from churten_b200.kernels import _C
+
+    gen = torch.Generator().manual_seed(R * 77 + T)
+    p, buf = torch.randn(R, T, generator=gen), torch.zeros(R, T)
+    steps = torch.where(torch.rand(R, generator=gen) < 0.5, torch.zeros(R), torch.full((R,), 3.0))
+    mask = torch.rand(R, generator=gen) < 0.7
+    mask[0] = True
+    lr = torch.exp(torch.empty(R).uniform_(-7.0, -3.0, generator=gen))
+    mom = torch.tensor([0.5, 0.9, 0.0])[torch.randint(0, 2 if nesterov else 3, (R,), generator=gen)]
+    damp = torch.zeros(R) if nesterov else torch.rand(R, generator=gen) * 0.5
+    wd = torch.tensor([0.0, 1e-3])[torch.randint(0, 2, (R,), generator=gen)]
+    # rows that are past their first step start from a buffer the narrow type can hold
+    buf[steps > 0] = torch.randn(R, T, generator=gen)[steps > 0].to(dtype).float()
+    dp, dbuf, dsteps = p.to(cuda), buf.to(cuda, dtype), steps.to(cuda)
+    side = [x.to(cuda) for x in (lr, mom, damp, wd)]
+    oracle.set_moment_storage(STORE[dtype])
+    for _ in range(3):
+        g = torch.randn(R, T, generator=gen)
+        oracle.sgd_step(oracle.CUDA_FORM, p, g, buf, steps, lr, mom, damp, wd, mask, nesterov, maximize)
+        _C.sgd_step_mixed_cuda(dp, g.to(cuda), dbuf, dsteps, *side, mask.to(cuda), nesterov, maximize)
+    assert_bits_equal("params", dp, p)
+    assert_bits_equal("momentum_buffers", dbuf.float(), buf)
+    assert torch.equal(dsteps.cpu(), steps) and dbuf.dtype is dtype
+
+
+def test_sgd_front_end_with_a_narrow_buffer(cuda):
+    from churten_b200.kernels import _C
+    from churten_b200.optimizer import SGD
+    from churten_b200.state import State
+
+    torch.manual_seed(0)
+    models = [Sequential(Linear(6, 9), ReLU(), Linear(9, 2)).to(cuda) for _ in range(4)]
+    narrow, full = State.from_models(models), State.from_models(models)
+    SGD.init(narrow, lr=0.05, momentum=0.9, nesterov=True, momentum_dtype=torch.bfloat16)
+    SGD.init(full, lr=0.05, momentum=0.9, nesterov=True)
+    assert narrow.optimizer_state["momentum_buffers"].dtype is torch.bfloat16
+    gen = torch.Generator(device=cuda).manual_seed(1)
+    for state in (narrow, full):
+        state.active_mask[1] = False
+    for _ in range(5):
+        grads = {n: torch.randn(s, generator=gen, device=cuda) * 0.1 for n, s, _, _ in narrow.param_meta}
+        before = _C.launch_count()
+        SGD.apply_gradient(narrow, grads)
+        assert _C.launch_count() - before == 3
+        SGD.apply_gradient(narrow, grads, materialize=False)       # no gathered form for SGD: scatters
+        SGD.apply_gradient(full, grads)
+        SGD.apply_gradient(full, grads, materialize=False)
+    assert narrow.optimizer_state["state_steps"].tolist() == [10.0, 0.0, 10.0, 10.0]
+    torch.testing.assert_close(narrow.params, full.params, rtol=0.0, atol=5e-3)
+    assert not torch.equal(narrow.params, full.params)
+    # plain SGD has no buffer to narrow: the option is accepted and changes nothing
+    plain = State.from_models(models)
+    SGD.init(plain, lr=0.05, momentum_dtype=torch.bfloat16)
+    assert "momentum_buffers" not in plain.optimizer_state
+    SGD.apply_gradient(plain, grads)
