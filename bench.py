@@ -84,6 +84,8 @@ def _bytes_per_elem(w) -> int:
         if w.get("moment_dtype"):      # fp32 params / grads, 2-byte moments
             return 24 if w.get("amsgrad") else 20
         return BYTES_PER_ELEM["adam_amsgrad" if w.get("amsgrad") else "adam"] * scale // 4
+    if w["opt"] == "sgd" and w.get("moment_dtype"):   # fp32 params / grads, 2-byte momentum buffer
+        return 16
     return BYTES_PER_ELEM[w["opt"]] * scale // 4
 
 
@@ -226,7 +228,8 @@ def build_state(w, n_rows, device, seed):
     if dtype in (torch.float16, torch.bfloat16) and w["opt"] == "adam":
         hyper.update(beta1=0.875, beta2=0.96875, eps=2.0 ** -20)  # values the half types can hold
     if w.get("moment_dtype"):
-        hyper["moment_dtype"] = {"bf16": torch.bfloat16, "f16": torch.float16}[w["moment_dtype"]]
+        key = "moment_dtype" if w["opt"] == "adam" else "momentum_dtype"
+        hyper[key] = {"bf16": torch.bfloat16, "f16": torch.float16}[w["moment_dtype"]]
     cls.init(state, **hyper)
     if w["frozen"] > 0:
         frozen = torch.rand(n_rows, device=device, generator=gen) < w["frozen"]
@@ -752,7 +755,7 @@ def main():
     ap.add_argument("--dtype", choices=sorted(ELEMENT_BYTES), default="f32",
                     help="storage type of the (N, T) buffers (the headline metric is f32)")
     ap.add_argument("--moment-dtype", choices=("bf16", "f16"), default=None,
-                    help="Adam with fp32 parameters and 2-byte moment buffers (an extension; not the headline)")
+                    help="Adam / SGD with fp32 parameters and 2-byte state buffers (an extension; not the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--apply-gradient", action="store_true",
                     help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
@@ -779,8 +782,8 @@ def main():
         w.pop("shapes", None)   # one flat parameter tensor of that length
     w["dtype"] = args.dtype
     if args.moment_dtype:
-        if w["opt"] != "adam" or args.dtype != "f32":
-            sys.exit("--moment-dtype is for Adam workloads with fp32 storage")
+        if w["opt"] not in ("adam", "sgd") or args.dtype != "f32":
+            sys.exit("--moment-dtype is for Adam and SGD workloads with fp32 storage")
         w["moment_dtype"] = args.moment_dtype
     # rows are padded to 16 bytes by the State allocator: 8 elements for the 2-byte types
     per_access = 16 // ELEMENT_BYTES[args.dtype]
