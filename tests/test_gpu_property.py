@@ -162,3 +162,62 @@ def test_masked_row_copy(n, leaves, seed, to_host, invert, use_mask):
         want[chosen] = src.cpu()[chosen]
         assert torch.equal(dst.cpu().view(torch.uint8) if dst.dtype is not torch.bool else dst.cpu(),
                            want.view(torch.uint8) if want.dtype is not torch.bool else want)
+
+
+policy_kwargs = st.one_of(
+    st.tuples(st.just("StepLR"), st.fixed_dictionaries({"step_size": st.integers(1, 60),
+                                                        "gamma": st.floats(0.01, 0.999)})),
+    st.tuples(st.just("MultiStepLR"), st.fixed_dictionaries({
+        "milestones": st.lists(st.integers(1, 5000), min_size=1, max_size=32, unique=True),
+        "gamma": st.floats(0.05, 0.99)})),
+    st.tuples(st.just("ExponentialLR"), st.fixed_dictionaries({"gamma": st.floats(0.5, 0.99999)})),
+    st.tuples(st.just("CosineAnnealingLR"), st.fixed_dictionaries({"T_max": st.integers(1, 6000),
+                                                                   "eta_min": st.floats(0.0, 1e-3)})),
+    st.tuples(st.just("WarmRestartLR"), st.fixed_dictionaries({
+        "min_lr": st.floats(0.0, 1e-4), "max_lr": st.floats(1e-3, 0.5), "base_period": st.integers(1, 40),
+        "period_mult": st.sampled_from([1, 2, 3]), "max_restarts": st.integers(0, 64)})),
+    st.tuples(st.just("ReduceLROnPlateau"), st.fixed_dictionaries({
+        "mode": st.sampled_from(["min", "max"]), "factor": st.floats(0.05, 0.9), "patience": st.integers(0, 3),
+        "threshold": st.floats(0.0, 0.1), "threshold_mode": st.sampled_from(["rel", "abs"]),
+        "cooldown": st.integers(0, 3), "min_lr": st.floats(0.0, 1e-4)})),
+)
+
+
+@settings(max_examples=150, deadline=None, derandomize=True,
+          suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(policy=policy_kwargs, seed=st.integers(0, 10_000), far=st.booleans())
+def test_schedule_kernel_equals_tensor_expressions(policy, seed, far):
+    """One-launch schedule tick against the chain of (N,) CUDA tensor expressions, bit for bit,
+    for random policy parameters and clocks (near the start or deep into the schedule)."""
+    from types import SimpleNamespace
+
+    from churten_b200 import lr_schedule
+
+    class TensorPath(lr_schedule.LRScheduler):
+        def _launch(self, *args):
+            return False
+
+    name, kwargs = policy
+    n, ticks = 257, 5
+    gen = torch.Generator(device=CUDA).manual_seed(seed)
+    base = torch.rand(n, generator=gen, device=CUDA) * 0.1 + 1e-6
+    start = torch.randint(0, 6000 if far else 8, (n,), generator=gen, device=CUDA).float()
+    masks = [torch.rand(n, generator=gen, device=CUDA) < 0.8 for _ in range(ticks)]
+    scores = [torch.rand(n, generator=gen, device=CUDA) for _ in range(ticks)]
+    outcomes = []
+    for cls in (lr_schedule.LRScheduler, TensorPath):
+        lr = base.clone()
+        state = SimpleNamespace(optimizer_state={"lr": lr}, active_mask=torch.ones(n, dtype=torch.bool, device=CUDA))
+        sched = cls(name, **kwargs)
+        needs = getattr(lr_schedule, name).needs_score
+        rates = []
+        for tick in range(ticks):
+            state.active_mask.copy_(masks[tick])
+            sched(state, score=scores[tick] if needs else None)
+            if tick == 0:
+                sched.t_.add_(start)
+            rates.append(lr.clone())
+        outcomes.append((torch.stack(rates), sched.t_.clone()))
+    (fused, fused_t), (expr, expr_t) = outcomes
+    assert_bits_equal(f"{name} {kwargs}", fused, expr)
+    assert torch.equal(fused_t, expr_t)
