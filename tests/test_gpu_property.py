@@ -221,3 +221,64 @@ def test_schedule_kernel_equals_tensor_expressions(policy, seed, far):
     (fused, fused_t), (expr, expr_t) = outcomes
     assert_bits_equal(f"{name} {kwargs}", fused, expr)
     assert torch.equal(fused_t, expr_t)
+
+
+part = st.tuples(st.integers(1, 45),     # columns of the part
+                 st.integers(0, 3),      # uncovered columns before it (read as zero gradient)
+                 st.integers(0, 5),      # extra elements between its rows
+                 st.integers(0, 3))      # elements skipped at the front of its storage
+
+
+@settings(max_examples=100, deadline=None, derandomize=True,
+          suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(n=st.integers(1, 40), parts=st.lists(part, min_size=1, max_size=60), big=st.integers(0, 3000),
+       seed=st.integers(0, 10_000), opt=st.sampled_from(["adam", "sgd", "adagrad"]))
+def test_gathered_gradients_equal_the_dense_matrix(ops, n, parts, big, seed, opt):
+    """`*_step_from_parts` over a random tiling of the row (tiny parts, gaps, strided and
+    misaligned gradient tensors, optionally one large part) against the plain step on the
+    gradient matrix those parts add up to."""
+    from churten_b200.kernels import _C
+
+    if big:
+        parts = parts + [(big, 0, 0, 0)]
+    gen = torch.Generator().manual_seed(seed)
+    entries, column = [], 0
+    for width, gap, extra, skip in parts:
+        column += gap
+        backing = torch.randn(skip + n * (width + extra) + 4, generator=gen).to(CUDA)
+        tensor = backing[skip: skip + n * (width + extra)].view(n, width + extra)[:, :width]
+        entries.append((tensor, column, width))
+        column += width
+    T = column + (-column % 4)
+    dense = torch.zeros(n, T, device=CUDA)
+    for tensor, offset, width in entries:
+        dense[:, offset: offset + width] = tensor
+    p = torch.randn(n, T, generator=gen).to(CUDA)
+    mask = (torch.rand(n, generator=gen) < 0.8).to(CUDA)
+    vec = lambda x: torch.full((n,), x, device=CUDA)
+    table = _C.GradParts.build(entries, p)
+    if len(entries) > 96:
+        assert table is None
+        return
+    assert table is not None
+    outcomes = []
+    for grads in (dense, table):
+        q, steps = p.clone(), torch.zeros(n, device=CUDA)
+        if opt == "adam":
+            m, v = torch.zeros_like(q), torch.zeros_like(q)
+            for _ in range(2):
+                _C.adam_step_cuda(q, grads, m, v, None, steps, vec(1e-2), vec(0.9), vec(0.999), vec(1e-8),
+                                  vec(1e-2), mask, False, False, True)
+            outcomes.append((q, m, v, steps))
+        elif opt == "sgd":
+            buf = torch.zeros_like(q)
+            for _ in range(2):
+                _C.sgd_step_cuda(q, grads, buf, steps, vec(1e-2), vec(0.9), vec(0.0), vec(1e-3), mask, True, False)
+            outcomes.append((q, buf, steps))
+        else:
+            acc = torch.full_like(q, 0.1)
+            for _ in range(2):
+                _C.adagrad_step_cuda(q, grads, acc, steps, vec(1e-2), vec(1e-3), vec(1e-2), vec(1e-10), mask, False)
+            outcomes.append((q, acc, steps))
+    for a, b in zip(*outcomes):
+        assert_bits_equal(opt, b, a)
