@@ -95,6 +95,12 @@ SIGNATURES = {
          # n_rows row_len nesterov maximize steps_already_bumped active_rows_hint ws ws_bytes stream
          c_int64, c_int64, c_int, c_int, c_int, c_int64, _P, c_size_t, _P],
     ),
+    "cb200_sgd_step_mixed_from_parts": (
+        c_int,
+        # the arguments of cb200_sgd_step_mixed with `grads` replaced by a cb200_grad_parts*
+        [c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_int64, c_int64, c_int, c_int, c_int, c_int64, _P, c_size_t, _P],
+    ),
     "cb200_scatter_rows": (
         c_int,
         # dst dst_row_stride dst_row_len n_rows n_parts parts offsets numels row_strides stream

@@ -10,9 +10,13 @@
 //
 // Dense buffers only; a thread takes 4 consecutive elements (16-byte accesses to params and
 // grads, an 8-byte access to the buffer), or 8 where rows are multiples of 8 elements.
+// cb200_sgd_step_mixed_from_parts reads the gradients from the per-parameter gradient tensors
+// instead (Grads = cb200_grad_parts, gathered 16 bytes at a time as in stream_kernel).
 #include "../../include/churten_b200.h"
 #include "narrow.cuh"
 #include "sgd_op.cuh"
+
+#include <type_traits>
 
 namespace cb200 {
 namespace {
@@ -20,10 +24,11 @@ namespace {
 constexpr int kSgdMixedThreads = 128;  // as measured for the Adam kernel of the same shape
 constexpr int kSgdMixedGroups = 2;
 
-template <class TM, bool STREAM, int GROUPS>
+template <class TM, bool STREAM, int GROUPS, class Grads>
 __global__ void __launch_bounds__(512)
 sgd_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, TM* __restrict__ buffers,
-                 WsView ws, int64_t row_len, int64_t tiles_per_row, int flags) {
+                 WsView ws, int64_t row_len, int64_t tiles_per_row, int flags, Grads parts) {
+  constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
   pdl_wait();
   const int n_active = ws.header->n_active;
   const int64_t total = static_cast<int64_t>(n_active) * tiles_per_row;
@@ -35,7 +40,8 @@ sgd_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, TM
     const int64_t a = item / tiles_per_row;
     const int64_t e0 = (item - a * tiles_per_row) * tile_elems + static_cast<int64_t>(threadIdx.x) * 4 * GROUPS;
     if (e0 >= row_len) continue;
-    const int64_t at = static_cast<int64_t>(ws.ids[a]) * row_len + e0;
+    const int64_t r = ws.ids[a];
+    const int64_t at = r * row_len + e0;
     const SgdRowT<float> c = rows[a];
 
     uint4 p_raw[GROUPS], g_raw[GROUPS];
@@ -43,7 +49,11 @@ sgd_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, TM
 #pragma unroll
     for (int q = 0; q < GROUPS; ++q) {
       p_raw[q] = load16<STREAM>(params + at + 4 * q);
-      g_raw[q] = load16<STREAM>(grads + at + 4 * q);
+      if constexpr (kGather) {
+        g_raw[q] = gather16<STREAM, float>(parts, r, e0 + 4 * q);
+      } else {
+        g_raw[q] = load16<STREAM>(grads + at + 4 * q);
+      }
     }
     if constexpr (GROUPS == 2) {
       const uint4 b4 = load16<STREAM>(buffers + at);
@@ -78,6 +88,7 @@ sgd_mixed_kernel(float* __restrict__ params, const float* __restrict__ grads, TM
 struct SgdMixedArgs {
   float* params;
   const float* grads;
+  const cb200_grad_parts* parts;  // NULL: gradients come from `grads`
   void* buffers;
   float* state_steps;
   SgdHyper<float> hyper;
@@ -123,15 +134,20 @@ int sgd_mixed_run(const SgdMixedArgs& a) {
                            0.75 * static_cast<double>(l2_bytes);
   TM* buffers = static_cast<TM*>(a.buffers);
   const dim3 grid(static_cast<unsigned>(want)), block(threads);
-  auto go = [&](auto kernel) {
+  auto go = [&](auto kernel, auto source) {
     return launch_dependent(kernel, grid, block, a.stream, a.params, a.grads, buffers, ws, a.row_len,
-                            tiles_per_row, a.flags);
+                            tiles_per_row, a.flags, source);
   };
-  if (groups == 2) {
-    err = stream_hint ? go(sgd_mixed_kernel<TM, true, 2>) : go(sgd_mixed_kernel<TM, false, 2>);
+#define CB200_SGD_MIXED(GROUPS, GRADS, SOURCE)                               \
+  (stream_hint ? go(sgd_mixed_kernel<TM, true, GROUPS, GRADS>, SOURCE)       \
+               : go(sgd_mixed_kernel<TM, false, GROUPS, GRADS>, SOURCE))
+  if (a.parts) {
+    err = groups == 2 ? CB200_SGD_MIXED(2, cb200_grad_parts, *a.parts)
+                      : CB200_SGD_MIXED(1, cb200_grad_parts, *a.parts);
   } else {
-    err = stream_hint ? go(sgd_mixed_kernel<TM, true, 1>) : go(sgd_mixed_kernel<TM, false, 1>);
+    err = groups == 2 ? CB200_SGD_MIXED(2, DenseGrads, DenseGrads{}) : CB200_SGD_MIXED(1, DenseGrads, DenseGrads{});
   }
+#undef CB200_SGD_MIXED
   if (err != cudaSuccess) return cuda_fail(err, "mixed-precision step launch");
   count_launches(1);
   return CB200_OK;
@@ -139,22 +155,20 @@ int sgd_mixed_run(const SgdMixedArgs& a) {
 
 bool aligned_to(const void* p, uintptr_t to) { return reinterpret_cast<uintptr_t>(p) % to == 0; }
 
-}  // namespace
-}  // namespace cb200
-
-extern "C" int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float* grads,
-                                    void* momentum_buffers, float* state_steps, const float* lr,
-                                    const float* momentum, const float* dampening,
-                                    const float* weight_decay, const uint8_t* active_mask,
-                                    const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len,
-                                    int nesterov, int maximize, int steps_already_bumped,
-                                    int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
-                                    void* stream) {
-  using namespace cb200;
+// The body of both entry points: exactly one of `grads` and `parts` is given.
+int sgd_mixed_entry(int buffer_dtype, float* params, const float* grads, const cb200_grad_parts* parts,
+                    void* momentum_buffers, float* state_steps, const float* lr, const float* momentum,
+                    const float* dampening, const float* weight_decay, const uint8_t* active_mask,
+                    const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len, int nesterov,
+                    int maximize, int steps_already_bumped, int64_t active_rows_hint, void* workspace,
+                    size_t workspace_bytes, void* stream) {
   if (n_rows < 0 || row_len < 0) return fail(CB200_ERR_INVALID_ARGUMENT, "n_rows and row_len must be >= 0");
   if (n_rows > 0x7fffffffLL) return fail(CB200_ERR_INVALID_ARGUMENT, "n_rows must fit in 31 bits");
   if (buffer_dtype != kF16 && buffer_dtype != kBF16) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "buffer_dtype must be CB200_F16 or CB200_BF16");
+  }
+  if (parts) {
+    if (int rc = check_grad_parts(parts, row_len)) return rc;
   }
   if (n_rows == 0) return CB200_OK;
   if (!state_steps || !active_mask || !lr || !momentum || !dampening || !weight_decay) {
@@ -162,10 +176,10 @@ extern "C" int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float
                                             "must not be NULL");
   }
   const bool has_data = row_len > 0;
-  if (has_data && (!params || !grads || !momentum_buffers)) {
+  if (has_data && (!params || (!grads && !parts) || !momentum_buffers)) {
     return fail(CB200_ERR_INVALID_ARGUMENT, "params, grads and momentum_buffers must not be NULL");
   }
-  if (has_data && (row_len % 4 != 0 || !aligned_to(params, 16) || !aligned_to(grads, 16) ||
+  if (has_data && (row_len % 4 != 0 || !aligned_to(params, 16) || (!parts && !aligned_to(grads, 16)) ||
                    !aligned_to(momentum_buffers, 8))) {
     return fail(CB200_ERR_UNSUPPORTED, "the mixed-precision step needs row_len % 4 == 0, 16-byte aligned "
                                        "params / grads and an 8-byte aligned momentum buffer");
@@ -176,6 +190,7 @@ extern "C" int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float
   SgdMixedArgs a;
   a.params = params;
   a.grads = grads;
+  a.parts = parts;
   a.buffers = momentum_buffers;
   a.state_steps = state_steps;
   a.hyper = SgdHyper<float>{lr, momentum, dampening, weight_decay, nesterov_rows, nesterov};
@@ -189,4 +204,34 @@ extern "C" int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float
   a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
   return buffer_dtype == kF16 ? sgd_mixed_run<__half>(a) : sgd_mixed_run<__nv_bfloat16>(a);
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float* grads,
+                                    void* momentum_buffers, float* state_steps, const float* lr,
+                                    const float* momentum, const float* dampening,
+                                    const float* weight_decay, const uint8_t* active_mask,
+                                    const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len,
+                                    int nesterov, int maximize, int steps_already_bumped,
+                                    int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  return cb200::sgd_mixed_entry(buffer_dtype, params, grads, nullptr, momentum_buffers, state_steps, lr,
+                                momentum, dampening, weight_decay, active_mask, nesterov_rows, n_rows,
+                                row_len, nesterov, maximize, steps_already_bumped, active_rows_hint,
+                                workspace, workspace_bytes, stream);
+}
+
+extern "C" int cb200_sgd_step_mixed_from_parts(
+    int buffer_dtype, float* params, const cb200_grad_parts* grad_parts, void* momentum_buffers,
+    float* state_steps, const float* lr, const float* momentum, const float* dampening,
+    const float* weight_decay, const uint8_t* active_mask, const uint8_t* nesterov_rows, int64_t n_rows,
+    int64_t row_len, int nesterov, int maximize, int steps_already_bumped, int64_t active_rows_hint,
+    void* workspace, size_t workspace_bytes, void* stream) {
+  if (!grad_parts) return cb200::fail(CB200_ERR_INVALID_ARGUMENT, "grad_parts must not be NULL");
+  return cb200::sgd_mixed_entry(buffer_dtype, params, nullptr, grad_parts, momentum_buffers, state_steps,
+                                lr, momentum, dampening, weight_decay, active_mask, nesterov_rows, n_rows,
+                                row_len, nesterov, maximize, steps_already_bumped, active_rows_hint,
+                                workspace, workspace_bytes, stream);
 }

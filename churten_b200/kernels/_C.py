@@ -437,17 +437,19 @@ def sgd_step_mixed_cuda(
 ):
     """SGD with fp32 params / grads and an fp16 or bf16 momentum buffer (`cb200_sgd_step_mixed`).
     Not an operator of the reference: called by the front-end when the state was initialised
-    with `momentum_dtype=`; dense buffers only."""
+    with `momentum_dtype=`; dense buffers only.  `grads` may be a `GradParts` table
+    (`cb200_sgd_step_mixed_from_parts`)."""
     op = "churten_b200::sgd_step_mixed"
     _check_consolidated(params, op)
     if momentum_buffers is None:
         raise RuntimeError(f"{op}: needs a momentum buffer")
-    if params.dtype is not torch.float32 or grads.dtype is not torch.float32:
+    from_parts = isinstance(grads, GradParts)
+    if params.dtype is not torch.float32 or (not from_parts and grads.dtype is not torch.float32):
         raise RuntimeError(f"{op}: params and grads must be float32")
     buffer_dtype = momentum_buffers.dtype
     if buffer_dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError(f"{op}: the momentum buffer must be float16 or bfloat16, got {buffer_dtype}")
-    for t in (params, grads, momentum_buffers):
+    for t in (params, *([] if from_parts else [grads]), momentum_buffers):
         if t.shape != params.shape or t.device != params.device or not t.is_contiguous():
             raise RuntimeError(f"{op}: every buffer must be dense, of params' shape, on params' device")
     with _Call(op, params, state_steps, active_mask, steps_bumped) as call:
@@ -456,8 +458,10 @@ def sgd_step_mixed_cuda(
         nrows_c = _mask(nesterov_rows) if nesterov_rows is not None else None
         if nrows_c is not None and (nrows_c.device != params.device or nrows_c.numel() != call.n_rows):
             raise RuntimeError(f"{op}: nesterov_rows must be a ({call.n_rows},) vector on {params.device}")
-        status = _cb.cb200_sgd_step_mixed(
-            _DTYPES[buffer_dtype][0], params.data_ptr(), grads.data_ptr(), momentum_buffers.data_ptr(),
+        entry = _cb.cb200_sgd_step_mixed_from_parts if from_parts else _cb.cb200_sgd_step_mixed
+        status = entry(
+            _DTYPES[buffer_dtype][0], params.data_ptr(),
+            ctypes.byref(grads.table) if from_parts else grads.data_ptr(), momentum_buffers.data_ptr(),
             call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(), wd_c.data_ptr(),
             call.mask.data_ptr(), nrows_c.data_ptr() if nrows_c is not None else None,
             call.n_rows, call.row_len, int(nesterov), int(maximize), call.bumped, call.hint,

@@ -158,7 +158,7 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
             return False
         if value is not None and value.dtype is not params.dtype and (
                 not spec.mixed_takes_parts or len(entries) > _lib.MAX_GRAD_PARTS):
-            return False     # narrow state: one gradient-parts table, Adam only
+            return False     # narrow state: one gradient-parts table only
     with torch.no_grad():
         params2d = _as_2d(params)
         if len(entries) <= _lib.MAX_GRAD_PARTS:

@@ -16,6 +16,7 @@ _SPEC = _fused.FusedSpec(
     op=sgd_step_,
     direct=_C.sgd_step_cuda,
     mixed=_C.sgd_step_mixed_cuda,
+    mixed_takes_parts=True,
     flag_defaults=dict(nesterov=False, maximize=False),
     hypers=("lr", "momentum", "dampening", "weight_decay"),
     buffers=("momentum_buffers",),

@@ -232,6 +232,18 @@ int cb200_sgd_step_mixed(int buffer_dtype, float* params, const float* grads,
                          int64_t active_rows_hint, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* cb200_sgd_step_mixed with the gradients gathered from the per-parameter gradient tensors, as
+ * cb200_sgd_step_from_parts does for the plain step (fp32 gradient tensors). */
+int cb200_sgd_step_mixed_from_parts(int buffer_dtype, float* params,
+                                    const struct cb200_grad_parts* grad_parts,
+                                    void* momentum_buffers, float* state_steps, const float* lr,
+                                    const float* momentum, const float* dampening,
+                                    const float* weight_decay, const uint8_t* active_mask,
+                                    const uint8_t* nesterov_rows, int64_t n_rows, int64_t row_len,
+                                    int nesterov, int maximize, int steps_already_bumped,
+                                    int64_t active_rows_hint, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
 /*
  * Scatter K per-parameter gradient tensors into the consolidated (n_rows,
  * dst_row_len) gradient buffer with one launch (per 64 parts).  Part k is an fp32

@@ -246,7 +246,9 @@ def test_sgd_front_end_with_a_narrow_buffer(cuda):
         before = _C.launch_count()
         SGD.apply_gradient(narrow, grads)
         assert _C.launch_count() - before == 3
-        SGD.apply_gradient(narrow, grads, materialize=False)       # no gathered form for SGD: scatters
+        before = _C.launch_count()
+        SGD.apply_gradient(narrow, grads, materialize=False)       # gathered gradients + narrow buffer
+        assert _C.launch_count() - before == 2
         SGD.apply_gradient(full, grads)
         SGD.apply_gradient(full, grads, materialize=False)
     assert narrow.optimizer_state["state_steps"].tolist() == [10.0, 0.0, 10.0, 10.0]
@@ -257,3 +259,28 @@ def test_sgd_front_end_with_a_narrow_buffer(cuda):
     SGD.init(plain, lr=0.05, momentum_dtype=torch.bfloat16)
     assert "momentum_buffers" not in plain.optimizer_state
     SGD.apply_gradient(plain, grads)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_sgd_gathered_gradients_with_a_narrow_buffer_equal_scatter_then_step(cuda, dtype):
+    from churten_b200.optimizer import SGD
+    from churten_b200.state import State
+
+    torch.manual_seed(0)
+    models = [Sequential(Linear(300, 257), ReLU(), Linear(257, 3), ReLU(), Linear(3, 1)).to(cuda) for _ in range(3)]
+    scattered, gathered = State.from_models(models), State.from_models(models)
+    for state in (scattered, gathered):
+        SGD.init(state, lr=1e-2, momentum=0.9, weight_decay=1e-3, nesterov=True, momentum_dtype=dtype)
+    gen = torch.Generator(device=cuda).manual_seed(2)
+    untouched = gathered.grads.clone()
+    for step in range(3):
+        mask = torch.tensor([True, step != 1, True], device=cuda)
+        grads = {n: torch.randn(s, generator=gen, device=cuda) * 0.1 for n, s, _, _ in scattered.param_meta}
+        for state in (scattered, gathered):
+            state.active_mask.copy_(mask)
+        SGD.apply_gradient(scattered, grads)
+        SGD.apply_gradient(gathered, grads, materialize=False)
+    assert_bits_equal("params", gathered.params, scattered.params)
+    for key, value in scattered.optimizer_state.tensors().items():
+        assert_bits_equal(key, gathered.optimizer_state[key].float(), value.float())
+    assert torch.equal(gathered.grads, untouched)
