@@ -282,3 +282,74 @@ def test_gathered_gradients_equal_the_dense_matrix(ops, n, parts, big, seed, opt
             outcomes.append((q, acc, steps))
     for a, b in zip(*outcomes):
         assert_bits_equal(opt, b, a)
+
+
+STORE = {torch.float16: oracle.STORE_F16, torch.bfloat16: oracle.STORE_BF16}
+narrow_shapes = st.one_of(
+    st.tuples(st.integers(1, 40), st.integers(0, 40)),          # rows of 0..160 elements
+    st.tuples(st.integers(1, 5), st.integers(250, 2500)),       # several tiles per row
+    st.tuples(st.integers(1025, 2100), st.integers(1, 3)),      # several prologue blocks
+)
+
+
+def _narrow_at(x, dtype, shift):
+    """A dense device copy of `x` in `dtype` whose storage starts 8 * shift bytes past a 16-byte
+    boundary (shift = 1: the kernels' one-quad-per-thread form even for rows of 8k elements)."""
+    backing = torch.zeros(x.numel() + 8, dtype=dtype, device=CUDA)
+    view = backing[4 * shift: 4 * shift + x.numel()].view(x.shape)
+    view.copy_(x)
+    return view
+
+
+@settings(max_examples=80, deadline=None, derandomize=True,
+          suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(shape=narrow_shapes, seed=st.integers(0, 10_000), dtype=st.sampled_from([torch.float16, torch.bfloat16]),
+       opt=st.sampled_from(["adam", "adamw_amsgrad", "sgd", "sgd_nesterov"]), shift=st.integers(0, 1),
+       maximize=st.booleans())
+def test_narrow_state_steps_match_the_oracle(shape, seed, dtype, opt, shift, maximize):
+    """fp32 parameters with fp16 / bf16 optimizer state over random shapes, masks, alignments of
+    the narrow buffers and per-row hyper-parameters: equal to the oracle with its moment-only
+    storage rounding."""
+    from churten_b200.kernels import _C
+
+    R, T = shape[0], 4 * shape[1]
+    gen, (p,), mask, steps, lr = _draw(seed, R, T, 1)
+    wd = torch.tensor([0.0, 1e-2])[torch.randint(0, 2, (R,), generator=gen)]
+    dp, dsteps, dmask = p.to(CUDA), steps.to(CUDA), mask.to(CUDA)
+    oracle.set_moment_storage(STORE[dtype])
+    try:
+        if opt.startswith("adam"):
+            amsgrad = adamw = opt == "adamw_amsgrad"
+            b1 = torch.tensor([0.9, 0.8])[torch.randint(0, 2, (R,), generator=gen)]
+            b2 = torch.tensor([0.999, 0.99])[torch.randint(0, 2, (R,), generator=gen)]
+            eps = torch.full((R,), 1e-8)
+            state = [torch.zeros(R, T) for _ in range(3)]
+            dstate = [_narrow_at(x, dtype, shift) for x in state]
+            side = [x.to(CUDA) for x in (lr, b1, b2, eps, wd)]
+            for _ in range(2):
+                g = torch.randn(R, T, generator=gen)
+                pows = device_pows(b1, b2, steps + mask.float())
+                oracle.adam_step(oracle.CUDA_FORM, p, g, state[0], state[1], state[2] if amsgrad else None, steps,
+                                 lr, b1, b2, eps, wd, mask, amsgrad, maximize, adamw, pow_override=pows)
+                _C.adam_step_mixed_cuda(dp, g.to(CUDA), dstate[0], dstate[1], dstate[2] if amsgrad else None,
+                                        dsteps, *side, dmask, amsgrad, maximize, adamw)
+            names = ["exp_avgs", "exp_avg_sqs"] + (["max_exp_avg_sqs"] if amsgrad else [])
+        else:
+            nesterov = opt == "sgd_nesterov"
+            mom = torch.tensor([0.5, 0.9])[torch.randint(0, 2, (R,), generator=gen)]
+            damp = torch.zeros(R) if nesterov else torch.rand(R, generator=gen) * 0.5
+            state = [torch.zeros(R, T)]
+            state[0][steps > 0] = torch.randn(R, T, generator=gen)[steps > 0].to(dtype).float()
+            dstate = [_narrow_at(x, dtype, shift) for x in state]
+            side = [x.to(CUDA) for x in (lr, mom, damp, wd)]
+            for _ in range(2):
+                g = torch.randn(R, T, generator=gen)
+                oracle.sgd_step(oracle.CUDA_FORM, p, g, state[0], steps, lr, mom, damp, wd, mask, nesterov, maximize)
+                _C.sgd_step_mixed_cuda(dp, g.to(CUDA), dstate[0], dsteps, *side, dmask, nesterov, maximize)
+            names = ["momentum_buffers"]
+    finally:
+        oracle.set_moment_storage(oracle.STORE_SAME)
+    assert_bits_equal("params", dp, p)
+    for name, device_value, value in zip(names, dstate, state):
+        assert_bits_equal(name, device_value.float(), value)
+    assert torch.equal(dsteps.cpu(), steps)
