@@ -535,9 +535,10 @@ def run_ours(args, w, world, rank, local_rank):
     if rank == 0:
         peak, peak_kind = _peak_gbs()
         achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
-        per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else ""))
-        if args.apply_gradient or w.get("moment_dtype"):
-            per_elem = None     # the captures cover the plain step kernels alone
+        per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else "") +
+                                                 ("_narrow_state" if w.get("moment_dtype") else ""))
+        if args.apply_gradient:
+            per_elem = None     # the captures cover the step kernels on the gradient matrix alone
         # measured on fp32 storage; other storage types move proportionally fewer / more bytes
         traffic = (per_elem * active_elems * ELEMENT_BYTES[args.dtype] / 4) if per_elem is not None else None
         line = {
@@ -593,6 +594,8 @@ TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {
     "sgd": 19.30,
     # profiles/adagrad_stream_kernel_c4_rows16_ncu.md: 1.2866 GB over 67,108,864 elements
     "adagrad": 19.17,
+    # profiles/adam_mixed_kernel_c5shard_rows64_ncu.md (bf16 moments): 2.3793 GB over 121,634,816 elements
+    "adam_narrow_state": 19.56,
 }
 
 
