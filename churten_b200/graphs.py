@@ -18,6 +18,11 @@ Per-batch learning-rate schedules can ride in the same graph
 (`GraphedUpdate(Adam, state, schedulers=[sched])`: step, then one tick of each schedule):
 their one-launch form reads clocks, mask and rates on the device like the step does.
 
+With `grads=` (the per-parameter gradient tensors, at addresses that stay put: the targets of
+`copy_`, or the outputs of a backward pass captured in a graph of its own) the captured call is
+`Optimizer.apply_gradient(state, grads, materialize=...)` instead: by default the step that
+gathers the gradients from those tensors, with no scatter into the `(N, T)` gradient buffer.
+
 In-place changes to `state.active_mask` and to the hyper-parameter vectors between
 replays are honoured, exactly as with the eager call.  What is frozen at capture
 time: the set of buffers (rebuild the object after replacing a `State`), the
@@ -34,7 +39,8 @@ from churten_b200.state import State
 
 
 class GraphedUpdate:
-    def __init__(self, optimizer, state: State, active_rows: int | None = None, schedulers=()):
+    def __init__(self, optimizer, state: State, active_rows: int | None = None, schedulers=(),
+                 grads=None, materialize: bool = False):
         if state.device.type != "cuda":
             raise ValueError("GraphedUpdate needs a State on a CUDA device")
         self.optimizer = optimizer
@@ -43,6 +49,11 @@ class GraphedUpdate:
         for sched in self.schedulers:
             if sched._policy_class().needs_score:
                 raise ValueError("a schedule that needs the epoch score is ticked per epoch, outside the graph")
+        self.grads = grads
+        if grads is None:
+            step = lambda: optimizer.update(state)
+        else:
+            step = lambda: optimizer.apply_gradient(state, grads, materialize=materialize)
         self.graph = torch.cuda.CUDAGraph()
         mask = state.active_mask
         saved = mask.clone()
@@ -53,7 +64,7 @@ class GraphedUpdate:
             # stream's scratch and loads the kernels without touching the state or
             # advancing any clock.
             mask.fill_(False)
-            optimizer.update(state)
+            step()
             # A tick with every row frozen advances no clock but captures the schedule's
             # starting rates and rewrites the rates from clock 0; put the caller's back.
             rates = state.optimizer_state["lr"].clone() if self.schedulers else None
@@ -66,7 +77,7 @@ class GraphedUpdate:
             _C.set_capture_hint(active_rows)
             try:
                 with torch.cuda.graph(self.graph, stream=stream):
-                    optimizer.update(state)
+                    step()
                     for sched in self.schedulers:
                         sched(state)
             finally:

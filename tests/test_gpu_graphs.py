@@ -119,3 +119,41 @@ def test_schedules_that_cannot_be_captured_are_refused(cuda):
     torch.cuda.synchronize()
     O.Adam.update(state)       # the device and the state are still usable
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("opt_name,extra", [("Adam", {}), ("SGD", {}), ("Adagrad", {}),
+                                            ("Adam", dict(moment_dtype=torch.bfloat16)),
+                                            ("SGD", dict(momentum_dtype=torch.float16))])
+@pytest.mark.parametrize("materialize", [False, True])
+def test_replay_of_the_step_on_per_parameter_gradients(cuda, opt_name, extra, materialize):
+    """`GraphedUpdate(grads=...)`: the captured `apply_gradient` reads the gradient tensors at
+    their fixed addresses on every replay; equal to the eager call, 2 launches gathered and 3
+    with the scatter."""
+    import churten_b200.optimizer as O
+    from churten_b200.graphs import GraphedUpdate
+    from churten_b200.kernels import _C
+
+    opt = getattr(O, opt_name)
+    hp = {"Adam": dict(lr=1e-2, amsgrad=True), "SGD": dict(lr=1e-2, momentum=0.9, nesterov=True),
+          "Adagrad": dict(lr=1e-2, lr_decay=1e-2, initial_accumulator_value=0.1)}[opt_name]
+    eager, graphed = _state(cuda, opt, **hp, **extra), _state(cuda, opt, **hp, **extra)
+    static = {name: torch.zeros(shape, device=cuda) for name, shape, _, _ in graphed.param_meta}
+    before = _C.launch_count()
+    step = GraphedUpdate(opt, graphed, grads=static, materialize=materialize)
+    assert _C.launch_count() - before == 2 * (3 if materialize else 2)      # warm-up + capture
+    assert graphed.optimizer_state["state_steps"].abs().sum() == 0
+    gen = torch.Generator(device=cuda).manual_seed(1)
+    for it in range(5):
+        for tensor in static.values():
+            tensor.copy_(torch.randn(tensor.shape, device=cuda, generator=gen))
+        if it == 2:
+            for st in (eager, graphed):
+                st.active_mask[3] = False
+                st.optimizer_state["lr"][0] *= 0.5
+        opt.apply_gradient(eager, static, materialize=materialize)
+        step()
+    torch.cuda.synchronize()
+    assert_bits_equal("params", graphed.params, eager.params)
+    for key, value in eager.optimizer_state.tensors().items():
+        assert_bits_equal(key, graphed.optimizer_state[key].float(), value.float())
+    assert eager.optimizer_state["state_steps"].tolist() == [5.0, 5.0, 5.0, 2.0, 5.0, 5.0]
