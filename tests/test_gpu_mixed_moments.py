@@ -284,3 +284,39 @@ def test_sgd_gathered_gradients_with_a_narrow_buffer_equal_scatter_then_step(cud
     for key, value in scattered.optimizer_state.tensors().items():
         assert_bits_equal(key, gathered.optimizer_state[key].float(), value.float())
     assert torch.equal(gathered.grads, untouched)
+
+
+def test_sgd_argument_checks(cuda):
+    import ctypes
+
+    from churten_b200 import _lib
+
+    p, g = torch.zeros(2, 8, device=cuda), torch.ones(2, 8, device=cuda)
+    buf = torch.zeros(2, 8, device=cuda, dtype=torch.float16)
+    steps, mask = torch.zeros(2, device=cuda), torch.ones(2, dtype=torch.bool, device=cuda)
+    vec = lambda x: torch.full((2,), x, device=cuda)
+    side = (vec(0.5), vec(0.9), vec(0.0), vec(0.0))
+    lib = _lib.lib()
+    ws = torch.empty(lib.cb200_workspace_bytes(2), dtype=torch.uint8, device=cuda)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(entry=lib.cb200_sgd_step_mixed, dtype=_lib.F16, row_len=8, grads=ptr(g), ws_bytes=ws.numel()):
+        return entry(dtype, ptr(p), grads, ptr(buf), ptr(steps), *[ptr(s) for s in side], ptr(mask), None,
+                     2, row_len, 0, 0, 0, -1, ptr(ws), ws_bytes, stream)
+
+    assert call(dtype=_lib.F64) == _lib.ERR_INVALID_ARGUMENT
+    assert call(row_len=6) == _lib.ERR_UNSUPPORTED
+    assert call(grads=None) == _lib.ERR_INVALID_ARGUMENT
+    assert call(ws_bytes=8) == _lib.ERR_WORKSPACE
+    assert call(entry=lib.cb200_sgd_step_mixed_from_parts, grads=None) == _lib.ERR_INVALID_ARGUMENT
+    assert "grad_parts" in _lib.last_error()
+    table = _lib.GradPartsTable()
+    table.n_parts = _lib.MAX_GRAD_PARTS + 1
+    assert call(entry=lib.cb200_sgd_step_mixed_from_parts, grads=ctypes.byref(table)) != _lib.OK
+    torch.cuda.synchronize()
+    assert not steps.any() and not p.any()
+    assert call() == _lib.OK
+    torch.cuda.synchronize()
+    assert steps.tolist() == [1.0, 1.0] and torch.equal(p, torch.full_like(p, -0.5))
+    assert torch.equal(buf, torch.ones_like(buf))
