@@ -14,7 +14,6 @@ from pathlib import Path
 _PKG = Path(__file__).resolve().parent
 # CHURTEN_B200_LIB points at another build of the library (e.g. an experimental variant)
 LIB_PATH = Path(os.environ.get("CHURTEN_B200_LIB") or _PKG / "libchurten_b200.so")
-PROBE_LIB_PATH = _PKG / "libchurten_b200_probe.so"
 
 F32, F64, F16, BF16 = 0, 1, 2, 3  # enum cb200_dtype
 
@@ -126,28 +125,6 @@ SIGNATURES = {
     "cb200_launch_count": (c_int64, []),
 }
 
-PROBE_SIGNATURES = {
-    "cb200_probe_adam": (
-        c_int,
-        # dtype fuse amsgrad adamw maximize p g m v mx n lr beta1 beta2 eps wd step stream
-        [c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int64,
-         c_double, c_double, c_double, c_double, c_double, c_double, _P],
-    ),
-    "cb200_probe_sgd": (
-        c_int,
-        # dtype fuse has_buf maximize nesterov p g buf n lr momentum dampening wd step stream
-        [c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int64,
-         c_double, c_double, c_double, c_double, c_double, _P],
-    ),
-    "cb200_probe_adagrad": (
-        c_int,
-        # dtype fuse maximize p g sum n lr lr_decay wd eps step stream
-        [c_int, c_int, c_int, _P, _P, _P, c_int64, c_double, c_double, c_double, c_double, c_double, _P],
-    ),
-    "cb200_probe_powf": (c_int, [_P, _P, _P, c_int64, _P]),
-}
-
-
 # enum cb200_lr_kind
 LR_STEP, LR_MULTISTEP, LR_EXPONENTIAL, LR_COSINE, LR_WARM_RESTART, LR_PLATEAU = range(6)
 LR_MAX_MILESTONES = 32
@@ -200,7 +177,6 @@ def _open(path: Path, signatures: dict) -> ctypes.CDLL:
 
 
 _lib: ctypes.CDLL | None = None
-_probe: ctypes.CDLL | None = None
 
 
 def lib() -> ctypes.CDLL:
@@ -208,13 +184,6 @@ def lib() -> ctypes.CDLL:
     if _lib is None:
         _lib = _open(LIB_PATH, SIGNATURES)
     return _lib
-
-
-def probe_lib() -> ctypes.CDLL:
-    global _probe
-    if _probe is None:
-        _probe = _open(PROBE_LIB_PATH, PROBE_SIGNATURES)
-    return _probe
 
 
 def last_error() -> str:

@@ -190,7 +190,9 @@ class Snapshot:
         Alone (`rows=None`) the directory is built aside and swapped in, replacing a
         previous checkpoint.  A rank that holds rows `[lo, hi)` of an ensemble of
         `total_rows` replicas passes `rows=(lo, hi)`: it writes its block in place;
-        `meta.json` is written by the rank whose block starts at row 0.
+        `meta.json` is written by the rank whose block starts at row 0.  `total_rows` is
+        required with `rows`: every rank must ask for the same file size, whichever writes
+        first or last.
         """
         target = Path(root_dir_path) / (file_name or "state_dict")
         mirror = self.mirror
@@ -200,8 +202,10 @@ class Snapshot:
             if out.exists():
                 shutil.rmtree(out)
         else:
+            if total_rows is None:
+                raise ValueError("rows=(lo, hi) needs total_rows, the replica count of the whole ensemble")
             lo, hi = rows
-            total, out = int(total_rows if total_rows is not None else hi), target
+            total, out = int(total_rows), target
             if hi - lo != n_local or not (0 <= lo <= hi <= total):
                 raise ValueError(f"rows={rows} does not describe the {n_local} rows of this snapshot")
         out.mkdir(parents=True, exist_ok=True)
@@ -318,8 +322,8 @@ def _pwrite(path: Path, file_bytes: int, offset: int, data: torch.Tensor) -> Non
     """Write `data` (uint8, contiguous) at `offset` of a file of `file_bytes` bytes."""
     fd = os.open(path, os.O_RDWR | os.O_CREAT, 0o644)
     try:
-        if os.fstat(fd).st_size != file_bytes:
-            os.ftruncate(fd, file_bytes)   # every writer asks for the same size
+        if os.fstat(fd).st_size < file_bytes:
+            os.ftruncate(fd, file_bytes)   # only ever grown: another rank's rows may already be there
         view = memoryview(data.numpy())
         done = 0
         while done < len(view):            # a single write is capped near 2 GiB
@@ -365,6 +369,8 @@ class Checkpoint:
         self.verbose = verbose
         self.deferred = deferred
         self.device_stage = device_stage
+        if rows is not None and total_rows is None:
+            raise ValueError("rows=(lo, hi) needs total_rows, the replica count of the whole ensemble")
         self.rows = rows
         self.total_rows = total_rows
         self._snapshot: Snapshot | None = None

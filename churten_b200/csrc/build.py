@@ -1,4 +1,4 @@
-"""Build libchurten_b200.so (and the contraction-search probe) for sm_100a.
+"""Build libchurten_b200.so for sm_100a.
 
     python -m churten_b200.csrc.build            # build what is out of date
     python -m churten_b200.csrc.build --force    # rebuild everything
@@ -24,12 +24,9 @@ REPO = PKG.parent
 BUILD = CSRC / "build"
 
 LIB = PKG / "libchurten_b200.so"
-PROBE_LIB = PKG / "libchurten_b200_probe.so"
-HBM_PROBE = PKG / "hbm_stream_probe"
 
 LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu", "scatter.cu",
                "rowcopy.cu", "lr_schedule.cu", "adam_mixed.cu", "sgd_mixed.cu"]
-PROBE_SOURCES = ["probe.cu"]
 HEADERS = ["rowmath.cuh", "stream.cuh", "contraction.h", "adam_op.cuh", "sgd_op.cuh", "narrow.cuh", "../../include/churten_b200.h"]
 
 NVCC_FLAGS = [
@@ -103,21 +100,7 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, bool]:
     """Compile what is out of date; returns which libraries were rebuilt."""
     return {
         LIB.name: _build_one(LIB_SOURCES, LIB, force, verbose),
-        PROBE_LIB.name: _build_one(PROBE_SOURCES, PROBE_LIB, force, verbose),
     }
-
-
-def build_hbm_probe(force: bool = False) -> bool:
-    """The standalone HBM streaming microbenchmark (a measurement tool, not part of the library)."""
-    src = CSRC / "hbm_stream_probe.cu"
-    if not force and not _stale(HBM_PROBE, [src]):
-        return False
-    cmd = [_nvcc(), "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
-           "-o", str(HBM_PROBE), str(src)]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed on {src.name}:\n{res.stdout}\n{res.stderr}")
-    return True
 
 
 TORCH_BINDING = PKG / "libchurten_b200_torch.so"
@@ -153,12 +136,9 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/spill info")
-    ap.add_argument("--probe", action="store_true", help="also build churten_b200/hbm_stream_probe")
     ap.add_argument("--torch-binding", action="store_true",
                     help="also build churten_b200/libchurten_b200_torch.so (C++ TORCH_LIBRARY_IMPL binding)")
     args = ap.parse_args()
-    if args.probe:
-        print(f"{HBM_PROBE.name}: {'rebuilt' if build_hbm_probe(args.force) else 'up to date'}")
     for name, rebuilt in build(args.force, args.verbose).items():
         print(f"{name}: {'rebuilt' if rebuilt else 'up to date'}")
     if args.torch_binding:

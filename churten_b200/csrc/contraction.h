@@ -4,7 +4,7 @@
 // the compiler decided, site by site and template instantiation by template
 // instantiation, whether a product feeding a sum became one fma.  Bit-exact
 // agreement with `torch.optim.<Opt>(fused=True)` needs the same decisions.  They
-// are found empirically: `contraction_search.py` (this folder) runs every
+// are found empirically: `tests/probe/contraction_search.py` runs every
 // combination of the masks in rowmath.cuh against torch._fused_adam_ /
 // _fused_adamw_ / _fused_sgd_ / _fused_adagrad_ on the GPU, for every storage type
 // and separately for torch's 128-bit vector path and its element-wise path, and

@@ -37,7 +37,7 @@
 // No shared memory, no TMA and no tensor cores: the update has no reuse and no
 // contraction; it is bound by HBM bandwidth (12-36 bytes per fp32 element).  Staging
 // the tiles through shared memory with cp.async.bulk + mbarrier was measured in
-// hbm_stream_probe.cu: the same 6.9-7.0 TB/s with one CTA per tile, so the plain
+// a stand-alone probe of the same access pattern: the same 6.9-7.0 TB/s with one CTA per tile, so the plain
 // 16-byte accesses stay.
 #pragma once
 

@@ -46,9 +46,9 @@ def strided_like(t: torch.Tensor) -> torch.Tensor:
 
 def device_pows(beta1: torch.Tensor, beta2: torch.Tensor, steps: torch.Tensor) -> torch.Tensor:
     """(R, 2) = [beta1^step, beta2^step] computed by the GPU's powf, returned on the CPU."""
-    from churten_b200 import _lib
+    import probe as _probe   # tests/probe: the run-time-mask build of the element math
 
-    probe = _lib.probe_lib()
+    probe = _probe.lib()
     dev = torch.device("cuda")
     base = torch.stack([beta1, beta2], dim=1).to(dev, torch.float32).contiguous()
     expo = torch.stack([steps, steps], dim=1).to(dev, torch.float32).contiguous()

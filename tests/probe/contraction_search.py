@@ -2,15 +2,15 @@
 
 Run on a GPU whose torch build is the parity target:
 
-    python -m churten_b200.csrc.contraction_search [--n 1048576] [--json out.json]
+    python tests/probe/contraction_search.py [--n 1048576] [--json out.json]
 
 For Adam/AdamW, SGD and Adagrad, and separately for torch's 128-bit vector path
 (numel % 4 == 0) and its element-wise path (numel % 4 != 0), every fusion mask
-of rowmath.cuh is run through libchurten_b200_probe.so from the same inputs as
+of rowmath.cuh is run through libchurten_b200_probe.so (probe.cu, this folder) from the same inputs as
 torch._fused_adam_ / _fused_adamw_ / _fused_sgd_ / _fused_adagrad_, over a grid
 of hyper-parameters that switches each site on, and the masks whose outputs are
 bit-identical to torch on EVERY element of EVERY case are printed.  Those masks
-are the constants of contraction.h.  It also checks that the device `powf` of
+are the constants of churten_b200/csrc/contraction.h.  It also checks that the device `powf` of
 this toolkit matches torch's for the bias-correction arguments.
 
 Inputs mix unit normals with large and subnormal-range magnitudes so that a
@@ -24,9 +24,14 @@ import itertools
 import json
 import sys
 
+from pathlib import Path
+
 import torch
 
-from churten_b200 import _lib
+sys.path[:0] = [str(Path(__file__).resolve().parents[2]), str(Path(__file__).resolve().parents[1])]
+
+import probe as _probe  # noqa: E402
+from churten_b200 import _lib  # noqa: E402
 
 
 def f32(x: float) -> float:
@@ -71,7 +76,7 @@ def _hp(x: float) -> float:
 
 
 def search_adam(n: int, dev) -> dict:
-    probe = _lib.probe_lib()
+    probe = _probe.lib()
     ok = set(range(4))
     cases = 0
     log = []
@@ -111,7 +116,7 @@ def search_adam(n: int, dev) -> dict:
 
 
 def search_sgd(n: int, dev, has_buf: bool) -> dict:
-    probe = _lib.probe_lib()
+    probe = _probe.lib()
     all_masks = [f for f in range(32) if ((f >> 1) & 3) != 3]
     ok = set(all_masks)
     cases = 0
@@ -156,7 +161,7 @@ def search_sgd(n: int, dev, has_buf: bool) -> dict:
 
 
 def search_adagrad(n: int, dev) -> dict:
-    probe = _lib.probe_lib()
+    probe = _probe.lib()
     ok = set(range(8))
     cases = 0
     log = []
@@ -192,7 +197,7 @@ def search_adagrad(n: int, dev) -> dict:
 
 def check_powf(dev) -> dict:
     """powf(beta, step) of this build vs torch.pow on the same device."""
-    probe = _lib.probe_lib()
+    probe = _probe.lib()
     betas = [0.9, 0.999, 0.99, 0.95, 0.5, 0.9999, 0.8, 0.0, 1.0]
     steps = torch.arange(1, 200001, device=dev, dtype=torch.float32)
     bad = 0

@@ -163,6 +163,25 @@ def test_row_blocks_share_the_files_and_reload_under_another_split(tmp_path):
         Snapshot.from_file(tmp_path, "shared", rows=(5, 9))
 
 
+def test_a_block_write_needs_the_ensemble_size_and_never_shrinks_the_files(tmp_path):
+    whole = make_state(n=8)
+    # without total_rows each rank would size the shared files by its own upper bound
+    with pytest.raises(ValueError, match="total_rows"):
+        Snapshot(whole.rows(0, 4)).to_file(tmp_path, "shared", rows=(0, 4))
+    with pytest.raises(ValueError, match="total_rows"):
+        Checkpoint(root_dir=tmp_path, rows=(0, 4))
+    # rank 1 writes first, rank 0 rewrites afterwards: rank 1's rows must survive, also when
+    # a stale, longer file from an earlier and larger ensemble is lying there
+    Snapshot(make_state(n=12, seed=9)).to_file(tmp_path, "shared", rows=(0, 12), total_rows=12)
+    Snapshot(whole.rows(4, 8)).to_file(tmp_path, "shared", rows=(4, 8), total_rows=8)
+    Snapshot(whole.rows(0, 4)).to_file(tmp_path, "shared", rows=(0, 4), total_rows=8)
+    Snapshot(whole.rows(0, 4)).to_file(tmp_path, "shared", rows=(0, 4), total_rows=8)
+    full = Snapshot.from_file(tmp_path, "shared")
+    assert full.mirror["params"].shape[0] == 8
+    for name, leaf in leaves(whole).items():
+        assert torch.equal(full.mirror[name], leaf), name
+
+
 def test_checkpoint_follows_the_reference_scenario(tmp_path):
     state = make_state()
     said = []
