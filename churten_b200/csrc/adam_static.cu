@@ -21,19 +21,23 @@
 // Set-up.  Host code cannot use the array's name as a device address; the address
 // comes from cudaGetSymbolAddress, asked once per device with that device current.
 // The first call on a device does this, so make that first call before starting
-// any stream capture on that device.
+// any stream capture on that device.  Each combination of amsgrad / decoupled weight
+// decay / buffer layout (dense and 16-byte aligned, or strided) / working-set size
+// (above or below the cache-hint threshold) selects a kernel of its own, and the CUDA
+// runtime may load a kernel on its first launch: call once with every combination you
+// will capture before the capture starts.
 //
 // Nothing in the array has to be zero between calls: the prologue kernel rewrites
 // the active-row count and the first `count` list entries and records on every
 // call, and entries beyond the count (left over from an earlier call) are never read.
 //
-// The device math is the same code as cb200_adam_step's (rowmath.cuh, stream.cuh);
-// the two entry points give bit-identical results.
+// The kernels are the ones cb200_adam_step launches (the same template instances of
+// stream.cuh over adam_op.cuh); only where the scratch lives differs, so the two
+// entry points give bit-identical results at the same speed.
 #include <mutex>
 
 #include "../../include/churten_b200.h"
-#include "contraction.h"
-#include "stream.cuh"
+#include "adam_op.cuh"
 
 namespace cb200 {
 namespace {
@@ -71,46 +75,13 @@ int static_scratch(void** out) {
   return 0;
 }
 
-struct StaticAdamHyper {
-  const float* lr;
-  const float* beta1;
-  const float* beta2;
-  const float* eps;
-  const float* weight_decay;
-};
-
-// Same operator description as the one behind cb200_adam_step (buffer order:
-// params, grads, exp_avgs, exp_avg_sqs, [max_exp_avg_sqs]; grads are read-only).
-template <bool AMSGRAD, bool ADAMW, int FUSE>
-struct StaticAdamOp {
-  using Storage = float;
-  using Math = float;
-  static constexpr int kBufs = AMSGRAD ? 5 : 4;
-  static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;
-  static constexpr int kThreads = 256;  // measured best on B200: as cb200_adam_step
-  static constexpr int kUnroll = 1;
-  // resident CTAs of 512 threads the register allocation must allow (launch bound)
-  static constexpr int kMinCtas512 = 0;  // 0: no bound beyond the thread count
-  using Row = AdamRow;
-  using Hyper = StaticAdamHyper;
-
-  __device__ static __forceinline__ Row make_row(const Hyper& h, int r, float step) {
-    return adam_row<float>(h.lr[r], h.beta1[r], h.beta2[r], h.eps[r], h.weight_decay[r], step);
-  }
-  __device__ static __forceinline__ void apply(float (&x)[kBufs], const Row& c, int flags) {
-    float mx = 0.0f;
-    if constexpr (AMSGRAD) mx = x[4];
-    adam_elem<AMSGRAD, ADAMW, FUSE, float>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
-    if constexpr (AMSGRAD) x[4] = mx;
-  }
-};
-
 template <bool AMSGRAD, bool ADAMW>
-int static_adam(const StaticAdamHyper& hyper, float* state_steps, const uint8_t* mask,
+int static_adam(const AdamHyper<float>& hyper, float* state_steps, const uint8_t* mask,
                 void* const* ptrs, const int64_t* strides, int64_t n_rows, int64_t row_len,
                 int flags, int64_t hint, void* scratch, cudaStream_t stream) {
-  using VecOp = StaticAdamOp<AMSGRAD, ADAMW, Fuse<float>::kAdamVec>;
-  using ElemOp = StaticAdamOp<AMSGRAD, ADAMW, Fuse<float>::kAdamElem>;
+  // the very operator types behind cb200_adam_step: same kernels, same register allocation
+  using VecOp = AdamOp<float, AMSGRAD, ADAMW, Fuse<float>::kAdamVec>;
+  using ElemOp = AdamOp<float, AMSGRAD, ADAMW, Fuse<float>::kAdamElem>;
   static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs",
                                        "max_exp_avg_sqs"};
   Bufs<VecOp::kBufs> bufs;
@@ -146,7 +117,7 @@ extern "C" int cb200_adam_step_static_scratch(
   if (n_rows > 0) {
     if (int rc = static_scratch(&scratch)) return rc;
   }
-  const StaticAdamHyper hyper{lr, beta1, beta2, eps, weight_decay};
+  const AdamHyper<float> hyper{lr, beta1, beta2, eps, weight_decay};
   void* ptrs[5] = {params, const_cast<float*>(grads), exp_avgs, exp_avg_sqs, max_exp_avg_sqs};
   const int flags = maximize ? 1 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

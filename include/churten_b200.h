@@ -350,7 +350,10 @@ int cb200_lr_schedule(const cb200_lr_policy* policy, const float* base_lrs, floa
  *    (two streams, two threads) race on it.  Serialise them, or use
  *    cb200_adam_step with a workspace per stream.
  *  - The first call on a device looks up the array's device address; make that
- *    first call before any stream capture on that device.
+ *    first call before any stream capture on that device.  Each combination of
+ *    amsgrad / decoupled_weight_decay / layout (dense and 16-byte aligned, or strided
+ *    or ragged) / size class selects its own kernel, which the CUDA runtime may load
+ *    at its first launch: call once with every combination you mean to capture first.
  *  - It performs no device allocation or free, directly or through a library.
  */
 #define CB200_STATIC_SCRATCH_MAX_ROWS 16384

@@ -15,6 +15,11 @@ point `cb200_adam_step` run on a copy.  It allocates its tensors BEFORE the
 calls; nothing is allocated between them.  It also checks that a row count over
 the limit is refused with a message that names the limit.
 
+So that the entry point does not stand on the library's word alone, one test
+compares it with PyTorch's own fused AdamW kernel row by row, one watches the
+device's free memory across calls (the "allocates nothing" promise), and the
+strided layout and the empty ensemble are covered as well.
+
 This file is collected last so that a failure here cannot hide other results.
 """
 
@@ -122,3 +127,90 @@ def test_the_limit_itself_is_served(cuda):
     for x, y in zip(a, b):
         assert _bits(x, y)
     assert torch.equal(sa, sb)
+
+
+def test_static_scratch_agrees_with_torch_fused_adamw(cuda):
+    """Ground truth from outside this library: torch._fused_adamw_ on each active row."""
+    lib = _lib.lib()
+    R, T = 5, 1000
+    gen = torch.Generator(device=cuda).manual_seed(77)
+    p, g, m, v = (torch.randn(R, T, device=cuda, generator=gen) for _ in range(4))
+    v.abs_()
+    want = [x.clone() for x in (p, m, v)]
+    steps = torch.full((R,), 3.0, device=cuda)
+    lrs = [1e-3, 3e-3, 1e-2, 2e-4, 5e-3]
+    side = [torch.tensor(lrs, device=cuda)] + [torch.full((R,), x, device=cuda) for x in (0.9, 0.999, 1e-8, 1e-2)]
+    mask = torch.tensor([True, False, True, True, False], device=cuda)
+    rc = lib.cb200_adam_step_static_scratch(
+        _ptr(p), _ptr(g), _ptr(m), _ptr(v), None, _ptr(steps), *[_ptr(s) for s in side],
+        _ptr(mask), R, T, None, 0, 0, 1, -1, _stream())
+    assert rc == _lib.OK, _lib.last_error()
+    for r in range(R):
+        if not bool(mask[r]):
+            continue
+        step = torch.tensor(3.0, device=cuda)
+        torch._fused_adamw_([want[0][r]], [g[r]], [want[1][r]], [want[2][r]], [], [step],
+                            lr=float(side[0][r]), beta1=0.9, beta2=0.999, weight_decay=1e-2, eps=1e-8,
+                            amsgrad=False, maximize=False, grad_scale=None, found_inf=None)
+    torch.cuda.synchronize()
+    for got, ref, name in zip((p, m, v), want, ("params", "exp_avgs", "exp_avg_sqs")):
+        assert _bits(got, ref), f"{name} differs from torch._fused_adamw_"
+    assert steps.tolist() == [4.0, 3.0, 4.0, 4.0, 3.0]
+
+
+def test_static_scratch_takes_no_device_memory(cuda):
+    """Free device memory, as the driver reports it, is the same after two further calls as
+    after a first (warm-up) call: no allocation, from any allocator, hides in the entry point."""
+    lib = _lib.lib()
+    R, T = 64, 4096
+    bufs = [torch.rand(R, T, device=cuda) for _ in range(4)]
+    steps = torch.zeros(R, device=cuda)
+    side = [torch.full((R,), x, device=cuda) for x in (1e-3, 0.9, 0.999, 1e-8, 0.0)]
+    mask = torch.ones(R, dtype=torch.bool, device=cuda)
+
+    def call():
+        rc = lib.cb200_adam_step_static_scratch(
+            *[_ptr(b) for b in bufs], None, _ptr(steps), *[_ptr(s) for s in side], _ptr(mask),
+            R, T, None, 0, 0, 0, -1, _stream())
+        assert rc == _lib.OK, _lib.last_error()
+        torch.cuda.synchronize()
+
+    call()  # set-up: address lookup and kernel load happen here
+    free_before = torch.cuda.mem_get_info(cuda)[0]
+    reserved_before = torch.cuda.memory_reserved(cuda)
+    call()
+    call()
+    assert torch.cuda.mem_get_info(cuda)[0] == free_before
+    assert torch.cuda.memory_reserved(cuda) == reserved_before
+    assert steps.tolist() == [3.0] * R
+
+
+def test_static_scratch_serves_strided_buffers_and_an_empty_ensemble(cuda):
+    lib = _lib.lib()
+    R, T = 9, 130
+    gen = torch.Generator(device=cuda).manual_seed(5)
+    dense = [torch.randn(R, T, device=cuda, generator=gen).abs() for _ in range(4)]
+    # the same values in (T, R) allocations viewed as (R, T): element stride R, row stride 1
+    strided = [torch.empty(T, R, device=cuda).t().copy_(x) for x in dense]
+    table = (ctypes.c_int64 * 10)(*[x for t in strided for x in (t.stride(0), t.stride(1))], 0, 0)
+    sa, sb = torch.zeros(R, device=cuda), torch.zeros(R, device=cuda)
+    side = [torch.full((R,), x, device=cuda) for x in (1e-2, 0.9, 0.999, 1e-8, 1e-2)]
+    mask = torch.rand(R, device=cuda, generator=gen) < 0.7
+    ws = torch.empty(lib.cb200_workspace_bytes(R), dtype=torch.uint8, device=cuda)
+    rc = lib.cb200_adam_step_static_scratch(
+        *[_ptr(b) for b in strided], None, _ptr(sa), *[_ptr(s) for s in side], _ptr(mask),
+        R, T, table, 0, 0, 1, -1, _stream())
+    assert rc == _lib.OK, _lib.last_error()
+    rc = lib.cb200_adam_step(
+        _lib.F32, *[_ptr(b) for b in dense], None, _ptr(sb), *[_ptr(s) for s in side], _ptr(mask),
+        R, T, None, 0, 0, 1, 0, -1, _ptr(ws), ws.numel(), _stream())
+    assert rc == _lib.OK, _lib.last_error()
+    torch.cuda.synchronize()
+    for x, y in zip(strided, dense):
+        assert _bits(x.contiguous(), y)
+    assert torch.equal(sa, sb)
+    # no rows: nothing to do, nothing touched, no error
+    rc = lib.cb200_adam_step_static_scratch(
+        None, None, None, None, None, None, None, None, None, None, None, None,
+        0, T, None, 0, 0, 1, -1, _stream())
+    assert rc == _lib.OK, _lib.last_error()
