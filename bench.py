@@ -49,6 +49,8 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 FALLBACK_HBM_GBS = 6650.0
+# the reference's own cuda/*.cu compiled unmodified for sm_100a (oracle/Makefile, target ref_cuda)
+REF_CUDA_LIB = ROOT / "oracle" / "_ref" / "torchstrap_ref_cuda.so"
 
 WORKLOADS = {
     # name: optimizer, rows per GPU, row length, frozen fraction, bytes per active element
@@ -296,14 +298,12 @@ def run_reference_cuda_arm(args, w, world, rank, local_rank):
     never imports this package's kernels."""
     import torch
 
-    import oracle
-
     if rank != 0:
         return
-    if not oracle.REF_CUDA_LIB.exists():
+    if not REF_CUDA_LIB.exists():
         print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref/torchstrap_ref_cuda.so not built"}))
         return
-    torch.ops.load_library(str(oracle.REF_CUDA_LIB))
+    torch.ops.load_library(str(REF_CUDA_LIB))
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     gen = torch.Generator(device=device).manual_seed(5000)
@@ -385,6 +385,153 @@ def run_reference_arm(args, w, world, rank):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_in_child(workload: str, steps: int) -> dict:
+    """The reference's recompiled CUDA kernels on the same workload and GPU, in a process that
+    loads nothing of this package: `{"ms_per_step", "gbs", "value"}`."""
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--impl", "reference_cuda", "--steps", str(steps),
+           "--warmup", "3", "--workload", workload]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+        for text in reversed(out.stdout.strip().splitlines()):
+            if text.startswith("{"):
+                got = json.loads(text)
+                if "unavailable" in got:
+                    return {"unavailable": got["unavailable"]}
+                return {"ms_per_step": got["ms_per_step"], "gbs": got["gbs"], "value": got["value"],
+                        "steps": got["steps"], "what": "the reference's cuda/*.cu compiled unmodified for "
+                                                       "sm_100a, same workload, same GPU, own process"}
+        return {"unavailable": (out.stderr or "no output")[-300:]}
+    except Exception as exc:
+        return {"unavailable": repr(exc)}
+
+
+def parity_replay(state, opt, w, device) -> dict:
+    """One extra step of the public front-end, replayed row by row with torch's own fused CUDA
+    optimizer kernels: the first, middle and last active replica of this rank's block must come
+    out bit for bit, one frozen replica byte for byte.  fp32 storage only."""
+    import torch
+
+    if w.get("dtype", "f32") != "f32" or w.get("moment_dtype"):
+        return {"skipped": "replay covers fp32 storage with fp32 state"}
+    o = state.optimizer_state
+    mask = state.active_mask
+    active = mask.nonzero().flatten().tolist()
+    frozen = (~mask).nonzero().flatten().tolist()
+    rows = sorted({active[0], active[len(active) // 2], active[-1]}) if active else []
+    watch = rows + frozen[:1]
+    names = {"adam": ["exp_avgs", "exp_avg_sqs"] + (["max_exp_avg_sqs"] if w.get("amsgrad") else []),
+             "sgd": ["momentum_buffers"] if o.get("momentum_buffers") is not None else [],
+             "adagrad": ["state_sums"]}[w["opt"]]
+    before = {r: {"params": state.flat_params[r].clone(), "grads": state.flat_grads[r].clone(),
+                  "step": float(o["state_steps"][r]),
+                  **{k: o[k][r].clone() for k in names}} for r in watch}
+    opt.update(state)
+    torch.cuda.synchronize(device)
+    hyper = lambda key, r: float(o[key][r])
+    same = lambda a, b: bool(torch.equal(a.view(torch.int32), b.view(torch.int32)))
+    bad = []
+    for r in rows:
+        b = before[r]
+        step = torch.tensor(b["step"] + 1.0, device=device)
+        if w["opt"] == "adam":
+            fused = torch._fused_adamw_ if o.get("decoupled_weight_decay", True) else torch._fused_adam_
+            fused([b["params"]], [b["grads"]], [b["exp_avgs"]], [b["exp_avg_sqs"]],
+                  [b["max_exp_avg_sqs"]] if w.get("amsgrad") else [], [step], lr=hyper("lr", r),
+                  beta1=hyper("beta1", r), beta2=hyper("beta2", r), weight_decay=hyper("weight_decay", r),
+                  eps=hyper("eps", r), amsgrad=bool(w.get("amsgrad")), maximize=False,
+                  grad_scale=None, found_inf=None)
+        elif w["opt"] == "sgd":
+            momentum = hyper("momentum", r)
+            torch._fused_sgd_([b["params"]], [b["grads"]],
+                              [b["momentum_buffers"]] if names and momentum != 0.0 else [],
+                              weight_decay=hyper("weight_decay", r), momentum=momentum, lr=hyper("lr", r),
+                              dampening=hyper("dampening", r), nesterov=False, maximize=False,
+                              is_first_step=b["step"] == 0.0, grad_scale=None, found_inf=None)
+        else:
+            torch._fused_adagrad_([b["params"]], [b["grads"]], [b["state_sums"]], [step], lr=hyper("lr", r),
+                                  lr_decay=hyper("lr_decay", r), weight_decay=hyper("weight_decay", r),
+                                  eps=hyper("eps", r), maximize=False, grad_scale=None, found_inf=None)
+        if not same(state.flat_params[r], b["params"]):
+            bad.append(f"params[{r}]")
+        for k in names:
+            if k == "momentum_buffers" and hyper("momentum", r) == 0.0:
+                continue   # torch keeps no buffer for a replica without momentum
+            if not same(o[k][r], b[k]):
+                bad.append(f"{k}[{r}]")
+        if float(o["state_steps"][r]) != b["step"] + 1.0:
+            bad.append(f"state_steps[{r}]")
+    for r in frozen[:1]:
+        b = before[r]
+        if not same(state.flat_params[r], b["params"]) or float(o["state_steps"][r]) != b["step"] \
+                or any(not same(o[k][r], b[k]) for k in names):
+            bad.append(f"frozen[{r}]")
+    return {"rows_checked": len(watch), "active_rows": rows, "frozen_rows": frozen[:1], "ok": not bad,
+            "mismatches": bad, "against": "torch._fused_" + {"adam": "adam(w)_", "sgd": "sgd_",
+                                                              "adagrad": "adagrad_"}[w["opt"]]}
+
+
+def measure_small(name, args, device, peak):
+    """A few steps of another workload on this GPU (after the headline): median op time from
+    CUDA events, GB/s of algorithmic bytes, clocks, and the same parity replay."""
+    import torch
+
+    from churten_b200.kernels import _C
+
+    w = dict(WORKLOADS[name], dtype="f32")
+    n, t = w["rows"], w["row_len"]
+    state, opt = build_state(w, n, device, seed=sorted(WORKLOADS).index(name) + 1)
+    bpe = _bytes_per_elem(w)
+    active = int(state.active_mask.sum().item())
+    fits_l2 = n * t * bpe <= 2 * 126e6
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if fits_l2 else None
+    steps = 10 if not fits_l2 else 30
+    stream = torch.cuda.current_stream(device)
+    for _ in range(3):
+        opt.update(state)
+    torch.cuda.synchronize(device)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    launches0 = _C.launch_count()
+    with ClockSampler(device.index) as clocks:
+        for i in range(steps):
+            if flush is not None:
+                flush.zero_()
+            starts[i].record(stream)
+            opt.update(state)
+            stops[i].record(stream)
+        torch.cuda.synchronize(device)
+    launches = _C.launch_count() - launches0
+    ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+    med = statistics.median(ms)
+    gbs = active * t * bpe / (med * 1e-3) / 1e9
+    out = {"description": w["desc"], "rows": n, "row_len": t, "active_rows": active, "steps": steps,
+           "op_ms_median": med, "op_ms_p10": _percentile(ms, 0.1), "op_ms_p90": _percentile(ms, 0.9),
+           "bytes_per_element": bpe, "gbs": gbs, "frac": gbs / peak, "frac_of_nominal_8tbs": gbs / 8000.0,
+           "param_updates_per_s": active * t / (med * 1e-3), "launches_per_step": launches / steps,
+           "l2": "evicted between timed steps (256 MiB written, not timed)" if fits_l2 else "inputs larger than L2"}
+    if fits_l2:
+        # back-to-back eager steps with a warm L2: what a training loop pays per step, host included
+        reps = 300
+        for _ in range(20):
+            opt.update(state)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(reps):
+            opt.update(state)
+        e1.record(stream)
+        torch.cuda.synchronize(device)
+        out["eager_warm_us_per_step"] = e0.elapsed_time(e1) * 1e3 / reps
+        out["eager_warm_wall_us_per_step"] = (time.perf_counter() - t0) * 1e6 / reps
+    out["clocks"] = clocks.summary()
+    out["parity"] = parity_replay(state, opt, w, device)
+    del state, flush
+    torch.cuda.empty_cache()
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -523,12 +670,22 @@ def run_ours(args, w, world, rank, local_rank):
     barrier()
     e2e_ms = e0.elapsed_time(e1)
 
+    # ---- correctness of this rank's block, outside every timed region ----
+    parity = parity_replay(state, opt, w, device)
+    parity_flag = torch.tensor([1.0 if parity.get("ok", True) else 0.0, float(parity.get("rows_checked", 0))],
+                               dtype=torch.float64, device=device)
+
     # ---- max over ranks, sum of work ----
     stats = torch.tensor([total_ms, e2e_ms, statistics.mean(per_op_ms)], dtype=torch.float64, device=device)
     work = torch.tensor([active_elems, launches], dtype=torch.float64, device=device)
     if distributed:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(work, op=dist.ReduceOp.SUM)
+        rows_checked = parity_flag[1:].clone()
+        dist.all_reduce(parity_flag, op=dist.ReduceOp.MIN)
+        dist.all_reduce(rows_checked, op=dist.ReduceOp.SUM)
+        parity = dict(parity, ok=bool(parity_flag[0].item() == 1.0), rows_checked=int(rows_checked.item()),
+                      ranks=world, note="ok = every rank's replay; rows and mismatches listed are rank 0's")
     total_ms, e2e_ms, op_ms = stats.tolist()
     job_elems, job_launches = work.tolist()
 
@@ -573,9 +730,21 @@ def run_ours(args, w, world, rank, local_rank):
                          "op_ms_mean": statistics.mean(per_op_ms), "op_ms_median": statistics.median(per_op_ms),
                          "op_ms_p10": _percentile(per_op_ms, 0.1),
                          "op_ms_p90": _percentile(per_op_ms, 0.9),
-                         "traffic": traffic},
+                         "traffic": traffic,
+                         "traffic_source": "ncu capture of a 64-row case of the same kernel, scaled by elements"},
             "clocks": clock_summary,
+            "parity": parity,
         }
+        default_line = (world == 1 and args.workload == "c5_shard" and not args.rows and not args.row_len
+                        and args.dtype == "f32" and not args.moment_dtype and not args.apply_gradient
+                        and not args.graph)
+        if default_line and not args.no_extras:
+            # the other configurations and the on-box comparator, after the headline's state is freed
+            del state, block_states, pinned, gather, loss, update
+            torch.cuda.empty_cache()
+            line["workloads"] = {name: measure_small(name, args, device, peak) for name in ("c1", "c2", "c3", "c4")}
+            torch.cuda.empty_cache()
+            line["reference_cuda"] = reference_cuda_in_child(args.workload, min(args.steps, 10))
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_in_child(args)
         print(json.dumps(line), flush=True)
@@ -584,18 +753,16 @@ def run_ours(args, w, world, rank, local_rank):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) per active element of the dominant kernel, from an ncu
-# capture of a smaller case of the same kernel (profiles/); traffic grows in
-# proportion to the elements processed.
+# DRAM bytes (read + write) per active element of the dominant kernel: dram__bytes_read.sum +
+# dram__bytes_write.sum of one ncu capture of a 16- or 64-row case of the same kernel, divided by
+# the elements that launch processed.  Traffic grows in proportion to the elements, so a full
+# launch is this figure times its active elements.  A constant from a capture, not a counter of
+# the run that prints it (a run under a profiler is never a bench number).
 TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {
-    # profiles/adam_stream_kernel_c5shard_rows64_ncu.md: 3.3503 GB over 121,634,816 elements
-    "adam": 27.54,
-    # profiles/sgd_stream_kernel_c3_rows64_ncu.md (momentum buffer): 1.4172 GB over 73,437,952 elements
-    "sgd": 19.30,
-    # profiles/adagrad_stream_kernel_c4_rows16_ncu.md: 1.2866 GB over 67,108,864 elements
-    "adagrad": 19.17,
-    # profiles/adam_mixed_kernel_c5shard_rows64_ncu.md (bf16 moments): 2.3793 GB over 121,634,816 elements
-    "adam_narrow_state": 19.56,
+    "adam": 27.54,               # 3.3503 GB over 121,634,816 elements (64 rows x 2 Mi, 58 active)
+    "sgd": 19.30,                # momentum buffer: 1.4172 GB over 73,437,952 elements
+    "adagrad": 19.17,            # 1.2866 GB over 67,108,864 elements
+    "adam_narrow_state": 19.56,  # bf16 moments: 2.3793 GB over 121,634,816 elements
 }
 
 
@@ -760,6 +927,8 @@ def main():
     ap.add_argument("--moment-dtype", choices=("bf16", "f16"), default=None,
                     help="Adam / SGD with fp32 parameters and 2-byte state buffers (an extension; not the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default line only: skip the c1-c4 sub-records and the reference-CUDA comparator")
     ap.add_argument("--apply-gradient", action="store_true",
                     help="time Optimizer.apply_gradient (gradient scatter + step) instead of update")
     ap.add_argument("--in-place-grads", action="store_true",

@@ -46,7 +46,8 @@ def default_reference_root() -> str:
 
 
 def build(reference_root: str | None = "") -> dict[str, bool]:
-    """Compile liboracle.so, and the reference's CPU kernels when its checkout is there.
+    """Compile liboracle.so and, when the reference's checkout is there, its CPU kernels and
+    its CUDA kernels for sm_100a (the on-GPU comparator; nvcc cross-compiles without a GPU).
 
     `reference_root`: "" = the default location, None = do not build the reference.
     """
@@ -57,10 +58,11 @@ def build(reference_root: str | None = "") -> dict[str, bool]:
     out["liboracle.so"] = ORACLE_LIB.exists()
     if reference_root and Path(reference_root, "src/torchstrap/kernels/csrc/stubs.cpp").exists():
         subprocess.run(
-            ["make", "-s", "-j4", "-C", str(HERE), "ref", f"REFERENCE_ROOT={reference_root}"],
+            ["make", "-s", "-j4", "-C", str(HERE), "ref", "ref_cuda", f"REFERENCE_ROOT={reference_root}"],
             check=True,
         )
     out["torchstrap_ref_cpu.so"] = REF_CPU_LIB.exists()
+    out["torchstrap_ref_cuda.so"] = REF_CUDA_LIB.exists()
     return out
 
 
