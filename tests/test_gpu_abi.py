@@ -125,7 +125,9 @@ def test_returns_fresh_scalar_that_aliases_nothing(cuda):
 
 @pytest.mark.parametrize("opt", ["adam", "adam_amsgrad", "sgd", "sgd_plain", "adagrad"])
 def test_opcheck(cuda, opt):
-    """Schema, alias annotations, fake kernel (reference test_cpu_cuda_parity.py:34-51)."""
+    """All four default checks of `torch.library.opcheck` -- schema and alias annotations,
+    autograd registration, fake kernel, AOT dispatch -- as the reference runs it
+    (test/optimizer/test_cpu_cuda_parity.py:34-51)."""
     import churten_b200.kernels  # noqa: F401
 
     R, T = 3, 24
@@ -134,7 +136,7 @@ def test_opcheck(cuda, opt):
     steps, mask = torch.zeros(R, device=cuda), torch.ones(R, dtype=torch.bool, device=cuda)
     v = lambda x: full(R, x, cuda)
     ops = torch.ops.torchstrap
-    tests = ("test_schema", "test_faketensor")
+    tests = ("test_schema", "test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic")
     if opt.startswith("adam"):
         ams = opt.endswith("amsgrad")
         args = (rnd(), rnd(), rnd(), rnd().abs(), rnd().abs() if ams else None, steps, v(1e-3),
