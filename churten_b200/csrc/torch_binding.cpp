@@ -95,7 +95,7 @@ Prepared prepare(const char* op, const at::Tensor& params, at::Tensor& state_ste
 
 at::Tensor finish(int rc, const char* op, const at::Tensor& params) {
   TORCH_CHECK(rc == CB200_OK, op, ": ", cb200_last_error(), " (cb200 status ", rc, ")");
-  return at::empty({}, params.options());  // vmap rejects an operator that returns nothing
+  return at::zeros({}, params.options());  // vmap rejects an operator that returns nothing
 }
 
 const uint8_t* bytes(const at::Tensor& mask) {

@@ -148,7 +148,7 @@ def test_static_scratch_agrees_with_torch_fused_adamw(cuda):
     for r in range(R):
         if not bool(mask[r]):
             continue
-        step = torch.tensor(3.0, device=cuda)
+        step = torch.tensor(4.0, device=cuda)   # the counter after this call's bump
         torch._fused_adamw_([want[0][r]], [g[r]], [want[1][r]], [want[2][r]], [], [step],
                             lr=float(side[0][r]), beta1=0.9, beta2=0.999, weight_decay=1e-2, eps=1e-8,
                             amsgrad=False, maximize=False, grad_scale=None, found_inf=None)
