@@ -115,6 +115,13 @@ SIGNATURES = {
         # policy base_lrs clock lr active_mask lower upper best num_bad cooldown_counter score n stream
         [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P],
     ),
+    "cb200_early_stopping_tick": (
+        c_int,
+        # score active_mask misses threshold best_epoch improved all_stopped counters n_rows
+        [_P, _P, _P, _P, _P, _P, _P, _P, c_int64,
+         # epoch patience threshold_value threshold_relative lower_is_better stream
+         c_int, c_int, c_double, c_int, c_int, _P],
+    ),
     "cb200_adam_step_static_scratch": (
         c_int,
         # the arguments of cb200_adam_step without workspace and workspace_bytes

@@ -335,6 +335,29 @@ int cb200_lr_schedule(const cb200_lr_policy* policy, const float* base_lrs, floa
                       void* stream);
 
 /*
+ * One epoch of per-replica early stopping in one launch, on the device.
+ * Replaces the host-side body of `EarlyStopping.__call__`
+ * (src/torchstrap/callbacks/training.py:262-308), which copies the score and the mask to
+ * the host, decides there and writes `state.active_mask[idx] = False` back.
+ * For every ACTIVE replica r:  improved = score[r] < threshold[r]  (> when
+ * lower_is_better == 0);  misses[r] = improved ? 0 : misses[r] + 1;  threshold[r] =
+ * score[r] -/+ (improved ? margin : 0) with margin = float(threshold_value) * score[r]
+ * (threshold_relative) or float(threshold_value);  best_epoch[r] = epoch where improved;
+ * active_mask[r] = 0 once misses[r] >= patience.  Frozen replicas keep everything.
+ *  - `improved` (n_rows bytes, may be NULL) receives this epoch's improved flags: the row
+ *    selection for a best-weights snapshot.
+ *  - `*all_stopped` (one byte of device memory) becomes 1 if no replica is active after
+ *    this epoch, else 0.
+ *  - `counters`: two int32 of device memory that are zero before the first call; each
+ *    call leaves them zero.  Calls that share them must not overlap on the GPU.
+ */
+int cb200_early_stopping_tick(const float* score, uint8_t* active_mask, int32_t* misses,
+                              float* threshold, int32_t* best_epoch, uint8_t* improved,
+                              uint8_t* all_stopped, int32_t* counters, int64_t n_rows,
+                              int32_t epoch, int32_t patience, double threshold_value,
+                              int threshold_relative, int lower_is_better, void* stream);
+
+/*
  * The Adam step (fp32 storage) for callers that may not allocate device memory:
  * the arguments and results of cb200_adam_step(CB200_F32, ...) with the counter
  * bumped in the call, but no workspace is passed -- the scratch

@@ -1,12 +1,52 @@
-"""Device-resident early stopping against a replica-by-replica restatement of the
-reference's host-side rule (src/torchstrap/callbacks/training.py:262-308)."""
+"""Device-resident early stopping against the reference's own callback.
+
+`tests/golden/early_stopping.npz` holds what the reference's `EarlyStopping`
+(src/torchstrap/callbacks/training.py:262-308, loaded by path by
+tests/golden/make_freeze_golden.py) produced, epoch by epoch, on the scenarios of
+tests/freeze_cases.py: mask, miss counters, thresholds, best epochs, returned flag.
+`churten_b200.freeze.EarlyStopping` must reproduce all of it bit for bit, on the CPU
+and on the GPU.  A replica-by-replica restatement of the rule in plain Python is kept
+as a second, independent reading."""
 
 import math
+from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 
+import freeze_cases
 from churten_b200.freeze import EarlyStopping
+
+GOLDEN = np.load(Path(__file__).resolve().parent / "golden" / "early_stopping.npz")
+
+
+def _assert_matches_fixture(name, got):
+    for key, value in got.items():
+        want = torch.from_numpy(GOLDEN[f"{name}/{key}"])
+        if key == "threshold":   # bit for bit, infinities included
+            assert torch.equal(value.view(torch.int32), want.view(torch.int32)), (name, key)
+        else:
+            assert torch.equal(value, want), (name, key)
+
+
+@pytest.mark.parametrize("name", sorted(freeze_cases.SCENARIOS))
+def test_reproduces_the_reference_callback(name):
+    _assert_matches_fixture(name, freeze_cases.drive(EarlyStopping, name))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(freeze_cases.SCENARIOS))
+def test_reproduces_the_reference_callback_on_the_gpu(cuda, name):
+    _assert_matches_fixture(name, freeze_cases.drive(EarlyStopping, name, device=cuda))
+
+
+def test_the_fixture_freezes_and_finishes():
+    # the scenarios are not trivial: replicas freeze at different epochs, some runs end early
+    masks = GOLDEN["rel-lower-p3/mask"]
+    assert masks[0].all() and not masks[-1].all()
+    assert GOLDEN["abs-lower-p1/stop"].any()
+    assert not GOLDEN["abs-lower-p5-prefrozen/mask"][:, [2, 6]].any()
 
 
 class _MaskOnly:
@@ -115,3 +155,68 @@ def test_runs_on_the_device_and_the_optimizer_honours_the_mask(cuda):
     SGD.update(state)
     moved = (state.params != before).any(dim=1)
     assert moved.tolist() == [True, False, True, False, True]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode,lower,patience", [("rel", True, 2), ("abs", False, 1), ("rel", False, 4)])
+def test_one_launch_tick_equals_the_tensor_expressions_on_many_replicas(cuda, mode, lower, patience):
+    """Several CTAs (the last-ticket reduction), NaN and infinite scores, replicas frozen by
+    someone else in between; the kernel path against the `(N,)` tensor expressions that the
+    fixture pins on the CPU, and exactly one launch per epoch."""
+    from churten_b200.kernels import _C
+
+    n, epochs = 3001, 14
+    gen = torch.Generator().manual_seed(11)
+    table = torch.rand(epochs, n, generator=gen).cumsum(0).flip(0) + torch.rand(epochs, n, generator=gen)
+    table[3, 5], table[4, 17], table[0, 2] = float("nan"), float("inf"), float("-inf")
+    if not lower:
+        table = -table
+    kwargs = dict(patience=patience, threshold=1e-3, threshold_mode=mode, lower_is_better=lower, track_best=False)
+    fast, slow = EarlyStopping(**kwargs), EarlyStopping(**kwargs)
+    slow._tick_on_device = lambda *a: None      # force the tensor expressions
+    a, b = _MaskOnly(n, cuda), _MaskOnly(n, cuda)
+    for epoch in range(epochs):
+        if epoch == 6:
+            a.active_mask[100:200] = False
+            b.active_mask[100:200] = False
+        score = table[epoch].to(cuda)
+        before = _C.launch_count()
+        done_fast = fast(a, score)
+        assert _C.launch_count() - before == 1
+        done_slow = slow(b, score)
+        assert torch.equal(a.active_mask, b.active_mask), epoch
+        assert torch.equal(fast.misses_, slow.misses_), epoch
+        assert torch.equal(fast.dynamic_threshold_.view(torch.int32), slow.dynamic_threshold_.view(torch.int32)), epoch
+        assert torch.equal(fast.best_epoch_, slow.best_epoch_), epoch
+        assert bool(done_fast) == bool(done_slow), epoch
+        assert fast._counters.tolist() == [0, 0]
+    # run everyone out: the flag turns true exactly when the last replica freezes
+    worst = torch.full((n,), float("inf") if lower else float("-inf"), device=cuda)
+    flags = [bool(fast(a, worst)) for _ in range(patience)]
+    assert flags[-1] and not a.active_mask.any()
+
+
+@pytest.mark.gpu
+def test_one_launch_tick_feeds_the_best_row_snapshot(cuda):
+    from churten_b200.optimizer import SGD
+    from churten_b200.state import State
+    from torch.nn import Linear, Sequential
+
+    def run(force_tensor_path):
+        torch.manual_seed(3)
+        state = State.from_models([Sequential(Linear(4, 3)).to(cuda) for _ in range(6)])
+        SGD.init(state, lr=0.1)
+        early = EarlyStopping(patience=2, threshold=0.0, threshold_mode="abs", track_best=True)
+        if force_tensor_path:
+            early._tick_on_device = lambda *a: None
+        scores = torch.tensor([[5., 5, 5, 5, 5, 5], [4, 6, 3, 6, 2, 6], [3, 7, 4, 7, 1, 7], [2, 8, 5, 8, 0, 8]], device=cuda)
+        for row in scores:
+            state.grads.fill_(1.0)
+            SGD.update(state)
+            early(state, row)
+        early.restore_best(state)
+        torch.cuda.synchronize()
+        return state.params.clone(), state.active_mask.clone(), early.best_epoch_.clone()
+
+    for got, want in zip(run(False), run(True)):
+        assert torch.equal(got, want)
