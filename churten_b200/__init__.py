@@ -11,4 +11,4 @@ Nothing is imported eagerly: `import churten_b200` works without the CUDA librar
 `import churten_b200.kernels` (and everything that steps) does not.
 """
 
-__version__ = "0.2.0"
+__version__ = "0.3.0"

@@ -17,6 +17,8 @@ LIB_PATH = Path(os.environ.get("CHURTEN_B200_LIB") or _PKG / "libchurten_b200.so
 
 F32, F64, F16, BF16 = 0, 1, 2, 3  # enum cb200_dtype
 
+STEPS_ALREADY_BUMPED, WORKSPACE_PREPARED = 1, 2  # enum cb200_call_flags
+
 OK = 0
 ERR_INVALID_ARGUMENT = 1
 ERR_WORKSPACE = 2
@@ -29,6 +31,7 @@ SIGNATURES = {
     "cb200_version": (c_int, []),
     "cb200_last_error": (c_char_p, []),
     "cb200_workspace_bytes": (c_size_t, [c_int64]),
+    "cb200_workspace_prepare": (c_int, [_P, c_size_t, c_int64, _P]),
     "cb200_adam_step": (
         c_int,
         # dtype params grads exp_avgs exp_avg_sqs max_exp_avg_sqs state_steps

@@ -89,12 +89,31 @@ int device_info(int* sm_count, size_t* l2_bytes) {
 
 extern "C" {
 
-int cb200_version(void) { return 200; }  // 0.2.0: from-parts steps, row copy, schedules
+int cb200_version(void) { return 300; }  // 0.3.0: single-launch step, early-stopping tick
 
 const char* cb200_last_error(void) { return cb200::g_last_error.c_str(); }
 
-// Sized for the 64-byte row records of fp64 storage; the other storage types use half of it.
-size_t cb200_workspace_bytes(int64_t n_rows) { return cb200::ws_bytes(n_rows, cb200::kMaxRecordBytes); }
+// Sized for the 64-byte row records of fp64 storage (the other storage types use half of it)
+// plus the per-row ticket counters of the single-launch step.
+size_t cb200_workspace_bytes(int64_t n_rows) { return cb200::ws_bytes_with_tickets(n_rows); }
+
+int cb200_workspace_prepare(void* workspace, size_t workspace_bytes, int64_t n_rows, void* stream) {
+  using namespace cb200;
+  if (n_rows < 0) return fail(CB200_ERR_INVALID_ARGUMENT, "n_rows must be >= 0");
+  if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kWsAlign != 0) {
+    return fail(CB200_ERR_WORKSPACE, "workspace must be a 256-byte aligned device pointer");
+  }
+  if (workspace_bytes < ws_bytes_with_tickets(n_rows)) {
+    return fail(CB200_ERR_WORKSPACE, "workspace too small: need " +
+                                         std::to_string(ws_bytes_with_tickets(n_rows)) + " bytes, got " +
+                                         std::to_string(workspace_bytes));
+  }
+  if (n_rows == 0) return CB200_OK;
+  cudaError_t err = cudaMemsetAsync(static_cast<char*>(workspace) + ws_tickets_offset(n_rows), 0,
+                                    ws_ids_bytes(n_rows), static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return cuda_fail(err, "cudaMemsetAsync(ticket counters)");
+  return CB200_OK;
+}
 
 int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm) {
   if (threads != 0 && threads != -1 && threads != 128 && threads != 256 && threads != 512) {

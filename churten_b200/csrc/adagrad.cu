@@ -57,6 +57,7 @@ struct AdagradArgs {
   int64_t n_rows, row_len;
   const int64_t* strides;
   int flags, bump;
+  bool prepared;
   int64_t hint;
   void* workspace;
   size_t workspace_bytes;
@@ -76,7 +77,7 @@ int adagrad_run(const AdagradArgs& a) {
                               static_cast<const M*>(a.weight_decay), static_cast<const M*>(a.eps)};
   return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
                                  a.row_len, a.flags, a.bump, a.hint, a.workspace,
-                                 a.workspace_bytes, a.stream, a.parts);
+                                 a.workspace_bytes, a.stream, a.parts, a.prepared);
 }
 
 // The body of both entry points: exactly one of `grads` and `parts` is given.
@@ -108,7 +109,8 @@ int adagrad_entry(int dtype, void* params, const void* grads, const cb200_grad_p
   a.row_len = row_len;
   a.strides = strides;
   a.flags = maximize ? 1 : 0;
-  a.bump = steps_already_bumped ? 0 : 1;
+  a.bump = (steps_already_bumped & CB200_STEPS_ALREADY_BUMPED) ? 0 : 1;
+  a.prepared = (steps_already_bumped & CB200_WORKSPACE_PREPARED) != 0;
   a.hint = active_rows_hint;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;

@@ -20,6 +20,7 @@ struct AdamArgs {
   int64_t n_rows, row_len;
   const int64_t* strides;
   int flags, bump, amsgrad, adamw;
+  bool prepared;
   int64_t hint;
   void* workspace;
   size_t workspace_bytes;
@@ -41,7 +42,7 @@ int adam_run(const AdamArgs& a) {
                            static_cast<const M*>(a.weight_decay)};
   return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
                                  a.row_len, a.flags, a.bump, a.hint, a.workspace,
-                                 a.workspace_bytes, a.stream, a.parts);
+                                 a.workspace_bytes, a.stream, a.parts, a.prepared);
 }
 
 template <class T>
@@ -87,7 +88,8 @@ int adam_entry(int dtype, void* params, const void* grads, const cb200_grad_part
   a.row_len = row_len;
   a.strides = strides;
   a.flags = maximize ? 1 : 0;
-  a.bump = steps_already_bumped ? 0 : 1;
+  a.bump = (steps_already_bumped & CB200_STEPS_ALREADY_BUMPED) ? 0 : 1;
+  a.prepared = (steps_already_bumped & CB200_WORKSPACE_PREPARED) != 0;
   a.amsgrad = amsgrad;
   a.adamw = decoupled_weight_decay;
   a.hint = active_rows_hint;

@@ -250,7 +250,7 @@ int mixed_entry(int moment_dtype, float* params, const float* grads, const cb200
   a.row_len = row_len;
   a.hint = active_rows_hint;
   a.flags = maximize ? 1 : 0;
-  a.bump = steps_already_bumped ? 0 : 1;
+  a.bump = (steps_already_bumped & CB200_STEPS_ALREADY_BUMPED) ? 0 : 1;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);

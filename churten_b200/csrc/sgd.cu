@@ -19,6 +19,7 @@ struct SgdArgs {
   int64_t n_rows, row_len;
   const int64_t* strides;
   int nesterov, flags, bump;
+  bool prepared;
   int64_t hint;
   void* workspace;
   size_t workspace_bytes;
@@ -39,7 +40,7 @@ int sgd_run(const SgdArgs& a) {
                           a.nesterov_rows, a.nesterov};
   return run_step<VecOp, ElemOp>(hyper, static_cast<M*>(a.state_steps), a.mask, bufs, a.n_rows,
                                  a.row_len, a.flags, a.bump, a.hint, a.workspace,
-                                 a.workspace_bytes, a.stream, a.parts);
+                                 a.workspace_bytes, a.stream, a.parts, a.prepared);
 }
 
 template <class T>
@@ -82,7 +83,8 @@ int sgd_entry(int dtype, void* params, const void* grads, const cb200_grad_parts
   a.strides = strides;
   a.nesterov = nesterov;
   a.flags = maximize ? 1 : 0;
-  a.bump = steps_already_bumped ? 0 : 1;
+  a.bump = (steps_already_bumped & CB200_STEPS_ALREADY_BUMPED) ? 0 : 1;
+  a.prepared = (steps_already_bumped & CB200_WORKSPACE_PREPARED) != 0;
   a.hint = active_rows_hint;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;

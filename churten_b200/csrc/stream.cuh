@@ -97,6 +97,17 @@ inline size_t ws_bytes(int64_t n_rows, size_t record_bytes = kMaxRecordBytes) {
   return kWsAlign + ws_ids_bytes(n_rows) + static_cast<size_t>(n_rows) * record_bytes;
 }
 
+// The single-launch step (below) keeps one int32 ticket counter per row behind the records,
+// at an offset that depends on n_rows alone.  They are zero between calls.
+inline size_t ws_tickets_offset(int64_t n_rows) { return ws_bytes(n_rows, kMaxRecordBytes); }
+inline size_t ws_bytes_with_tickets(int64_t n_rows) {
+  if (n_rows < 0) n_rows = 0;
+  return ws_tickets_offset(n_rows) + ws_ids_bytes(n_rows);
+}
+// Largest step (elements per buffer) the single-launch path takes; at and above it the
+// two-launch path always runs and the header's n_active is always written.
+constexpr int64_t kSingleLaunchMaxElements = int64_t(1) << 24;
+
 struct WsView {
   WsHeader* header;
   int32_t* ids;
@@ -514,6 +525,108 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
 }
 
 // ---------------------------------------------------------------------------
+// The whole step in ONE launch, for ensembles small enough to live in L2.
+//
+// There the two launches above cost more than the update itself (8 x 264,580 fp32
+// parameters: 9 us of HBM time, ~8 us of launch + dependency).  Here CTA b owns tile
+// (b mod tiles_per_row) of row (b / tiles_per_row) of ALL rows: it tests the row's mask byte
+// (frozen: exit), thread 0 reads the row's step counter, adds the 1 and builds the row
+// record in shared memory -- the same make_row() the prologue runs, so the record is the
+// same bits -- while the other threads already have the tile's loads in flight.  After the
+// update thread 0 draws a ticket from the row's counter; the CTA that draws the row's last
+// ticket stores the advanced step counter and puts the ticket counter back to zero.  Every
+// CTA of the row has read the old step before it drew its ticket, so the single writer
+// cannot be seen too early; nothing waits or spins.  The counters must be zero when the
+// launch starts: the caller says so (CB200_WORKSPACE_PREPARED) and each launch leaves them
+// zero.  Same element functions, same tile shape, same results as the two-launch path.
+// ---------------------------------------------------------------------------
+template <class Op, int UNROLL, class Grads>
+__global__ void __launch_bounds__(512)
+single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
+                     typename Op::Math* __restrict__ state_steps,
+                     const uint8_t* __restrict__ active_mask, int32_t* __restrict__ tickets,
+                     int64_t row_len, uint32_t tiles_per_row, int flags, int bump, Grads grads) {
+  constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
+  constexpr int NB = Op::kBufs;
+  using Row = typename Op::Row;
+  using T = typename Op::Storage;
+  using M = typename Op::Math;
+  using P = Pack<T>;
+  constexpr int VEC = P::kVec;
+
+  const uint32_t r32 = blockIdx.x / tiles_per_row;
+  const uint32_t tile = blockIdx.x - r32 * tiles_per_row;
+  const int64_t r = r32;
+  if (active_mask[r] == 0) return;   // the same byte for the whole CTA
+
+  __shared__ Row row_record;
+  __shared__ M row_step;
+  if (threadIdx.x == 0) {
+    M step = state_steps[r];
+    if (bump) step = add_rn(step, M(1));
+    row_step = step;
+    row_record = Op::make_row(hyper, static_cast<int>(r), step);
+  }
+
+  const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * VEC;
+  const int64_t e0 = static_cast<int64_t>(tile) * lane_elems * UNROLL +
+                     static_cast<int64_t>(threadIdx.x) * VEC;
+  T* base[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) base[b] = static_cast<T*>(bufs.ptr[b]) + r * bufs.stride_r[b] + e0;
+
+  uint4 raw[UNROLL][NB];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    if (e0 + u * lane_elems < row_len) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        if constexpr (kGather) {
+          if (b == 1) {
+            raw[u][b] = gather16<false, T>(grads, r, e0 + u * lane_elems);
+            continue;
+          }
+        }
+        raw[u][b] = load16<false>(base[b] + u * lane_elems);
+      }
+    }
+  }
+  __syncthreads();
+  const Row c = row_record;
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    if (e0 + u * lane_elems < row_len) {
+      M x[NB][VEC];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) P::unpack(raw[u][b], x[b]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        M e[NB];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) e[b] = x[b][k];
+        Op::apply(e, c, flags);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          if ((Op::kWriteMask >> b) & 1) x[b][k] = e[b];
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        if ((Op::kWriteMask >> b) & 1) store16<false>(base[b] + u * lane_elems, P::pack(x[b]));
+      }
+    }
+  }
+  if (bump && threadIdx.x == 0) {
+    __threadfence();   // this CTA's read of the old counter is done before its ticket shows
+    const uint32_t ticket = static_cast<uint32_t>(atomicAdd(&tickets[r], 1));
+    if (ticket == tiles_per_row - 1) {
+      tickets[r] = 0;
+      state_steps[r] = row_step;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Launch 2b: element-wise kernel for any strides, alignment and row length.
 // Same work-item scheme; a tile is blockDim x UNROLL elements.
 // ---------------------------------------------------------------------------
@@ -618,7 +731,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
                     const uint8_t* active_mask, const Bufs<VecOp::kBufs>& bufs, int64_t n_rows,
                     int64_t row_len, int flags, int bump_steps, int64_t active_rows_hint,
                     void* workspace, size_t workspace_bytes, cudaStream_t stream,
-                    const cb200_grad_parts* grad_parts = nullptr) {
+                    const cb200_grad_parts* grad_parts = nullptr, bool workspace_prepared = false) {
   static_assert(VecOp::kBufs == ElemOp::kBufs, "same optimizer");
   using T = typename VecOp::Storage;
   constexpr int kVec = Pack<T>::kVec;
@@ -643,6 +756,42 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   if (grad_parts && !vec) {
     return fail(4, "gradients are read from their parts only for buffers with unit element "
                    "stride and 16-byte aligned rows");
+  }
+
+  // Small, L2-resident steps over dense buffers: everything in one launch, if the caller
+  // vouches for the ticket counters.  The tile shape is the two-launch path's.
+  {
+    const LaunchGeometry geo = geometry();
+    const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) *
+                             static_cast<double>(sizeof(T)) * VecOp::kBufs;
+    const int64_t tile = static_cast<int64_t>(VecOp::kThreads) * kVec * VecOp::kUnroll;
+    const int64_t tiles_per_row = row_len > 0 ? (row_len + tile - 1) / tile : 0;
+    const bool short_rows = (row_len + kVec - 1) / kVec * 2 <= VecOp::kThreads;  // served PACKED
+    if (workspace_prepared && vec && row_len > 0 && !short_rows && geo.threads <= 0 &&
+        geo.unroll == 0 && geo.ctas_per_sm <= 0 &&
+        workspace_bytes >= ws_bytes_with_tickets(n_rows) &&
+        n_rows * row_len < kSingleLaunchMaxElements &&
+        footprint <= 0.75 * static_cast<double>(l2_bytes) &&
+        static_cast<double>(n_rows) * static_cast<double>(tiles_per_row) <= 2147483647.0) {
+      int32_t* tickets = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) +
+                                                    ws_tickets_offset(n_rows));
+      const unsigned grid = static_cast<unsigned>(n_rows * tiles_per_row);
+      if (grad_parts) {
+        single_launch_kernel<VecOp, VecOp::kUnroll, cb200_grad_parts>
+            <<<grid, VecOp::kThreads, 0, stream>>>(bufs, hyper, state_steps, active_mask, tickets,
+                                                   row_len, static_cast<uint32_t>(tiles_per_row),
+                                                   flags, bump_steps, *grad_parts);
+      } else {
+        single_launch_kernel<VecOp, VecOp::kUnroll, DenseGrads>
+            <<<grid, VecOp::kThreads, 0, stream>>>(bufs, hyper, state_steps, active_mask, tickets,
+                                                   row_len, static_cast<uint32_t>(tiles_per_row),
+                                                   flags, bump_steps, DenseGrads{});
+      }
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e, "single-launch step");
+      count_launches(1);
+      return 0;
+    }
   }
 
   // The row records are built with the fusion mask of the path that reads them.

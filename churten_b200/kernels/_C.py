@@ -67,11 +67,14 @@ for _name, _schema in SCHEMAS.items():
 # ---------------------------------------------------------------------------
 
 class _Slot:
-    """Per (device, stream): the prologue's scratch and what is known about the mask.
+    """Per (device, stream, row count): the step's scratch and what is known about the mask.
 
     The scratch comes from torch's caching allocator so it lives in the same pool
     as the state it serves; one per stream because two steps on different streams
-    may overlap on the GPU.
+    may overlap on the GPU, and one per row count because the ticket counters of the
+    single-launch step sit at an offset that depends on it.  A fresh scratch goes through
+    `cb200_workspace_prepare` once (a memset queued on the stream); from then on every
+    call vouches for it with CB200_WORKSPACE_PREPARED.
 
     `count` is the number of active rows of the mask identified by `mask_key`, read
     back from the device WITHOUT a host sync: on the first step after the mask
@@ -95,7 +98,8 @@ class _Slot:
         return self.mask_ref is not None and self.mask_ref() is mask and self.mask_key == key
 
 
-_slots: dict[tuple[int, int], _Slot] = {}
+_slots: dict[tuple[int, int, int], _Slot] = {}
+_MAX_SLOTS = 64   # least recently used beyond this are dropped (their scratch returns to the allocator)
 
 # Grid-size hint used while a CUDA graph is being captured (no read-back is possible
 # there); None = size the grid for every row.
@@ -107,19 +111,31 @@ def set_capture_hint(active_rows: int | None) -> None:
     _capture_hint = None if active_rows is None else int(active_rows)
 
 
+# Whether calls vouch for their scratch (CB200_WORKSPACE_PREPARED), which lets the library run
+# an L2-resident step as one launch.  Off: always the two-launch path (tests compare the two).
+_single_launch = True
+
+
+def set_single_launch(enabled: bool) -> None:
+    global _single_launch
+    _single_launch = bool(enabled)
+
+
 # Below this many elements the step is launch-bound and the read-back is not worth it.
 _HINT_MIN_ELEMENTS = 1 << 24
 
 
 def _slot(device: torch.device, stream_id: int, n_rows: int) -> _Slot:
-    key = (device.index, stream_id)
-    slot = _slots.get(key)
+    key = (device.index, stream_id, n_rows)
+    slot = _slots.pop(key, None)
     if slot is None:
-        slot = _slots[key] = _Slot()
-    need = _cb.cb200_workspace_bytes(n_rows)
-    if slot.ws is None or slot.ws.numel() < need:
-        slot.ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
-        slot.mask_ref = slot.mask_key = None
+        slot = _Slot()
+        slot.ws = torch.empty(max(_cb.cb200_workspace_bytes(n_rows), 4096), dtype=torch.uint8, device=device)
+        _lib.check(_cb.cb200_workspace_prepare(slot.ws.data_ptr(), slot.ws.numel(), n_rows, stream_id),
+                   "cb200_workspace_prepare")
+        while len(_slots) >= _MAX_SLOTS:
+            del _slots[next(iter(_slots))]
+    _slots[key] = slot   # most recently used last
     return slot
 
 
@@ -274,6 +290,8 @@ class _Call:
             self.guard = torch.cuda.device(self.device)
         self.read_back = False
         self.hint = -1
+        # the scratch of `_slot` has been through cb200_workspace_prepare for this row count
+        self.flags = self.bumped | (_lib.WORKSPACE_PREPARED if _single_launch else 0)
 
     def __enter__(self):
         if self.guard is not None:
@@ -346,7 +364,7 @@ def adam_step_cuda(
             call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
             eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(),
             call.n_rows, call.row_len, strides,
-            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.bumped, call.hint,
+            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.flags, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params, want_result)
@@ -387,7 +405,7 @@ def adam_step_mixed_cuda(
             exp_avg_sqs.data_ptr(), max_exp_avg_sqs.data_ptr() if amsgrad else None,
             call.steps.data_ptr(), lr_c.data_ptr(), b1_c.data_ptr(), b2_c.data_ptr(),
             eps_c.data_ptr(), wd_c.data_ptr(), call.mask.data_ptr(), call.n_rows, call.row_len,
-            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.bumped, call.hint,
+            int(amsgrad), int(maximize), int(decoupled_weight_decay), call.flags, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params, want_result)
@@ -425,7 +443,7 @@ def sgd_step_cuda(
             call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(),
             wd_c.data_ptr(), call.mask.data_ptr(),
             nrows_c.data_ptr() if nrows_c is not None else None,
-            call.n_rows, call.row_len, strides, int(nesterov), int(maximize), call.bumped, call.hint,
+            call.n_rows, call.row_len, strides, int(nesterov), int(maximize), call.flags, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params, want_result)
@@ -465,7 +483,7 @@ def sgd_step_mixed_cuda(
             ctypes.byref(grads.table) if from_parts else grads.data_ptr(), momentum_buffers.data_ptr(),
             call.steps.data_ptr(), lr_c.data_ptr(), mom_c.data_ptr(), damp_c.data_ptr(), wd_c.data_ptr(),
             call.mask.data_ptr(), nrows_c.data_ptr() if nrows_c is not None else None,
-            call.n_rows, call.row_len, int(nesterov), int(maximize), call.bumped, call.hint,
+            call.n_rows, call.row_len, int(nesterov), int(maximize), call.flags, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params, want_result)
@@ -491,7 +509,7 @@ def adagrad_step_cuda(
             call.dtype, params.data_ptr(), grads_c, state_sums.data_ptr(),
             call.steps.data_ptr(), lr_c.data_ptr(), lrd_c.data_ptr(), wd_c.data_ptr(),
             eps_c.data_ptr(), call.mask.data_ptr(),
-            call.n_rows, call.row_len, strides, int(maximize), call.bumped, call.hint,
+            call.n_rows, call.row_len, strides, int(maximize), call.flags, call.hint,
             call.ws.data_ptr(), call.ws.numel(), call.stream,
         )
         return call.finish(status, params, want_result)

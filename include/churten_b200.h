@@ -27,14 +27,21 @@
  *    storage), and one byte per row (0 = frozen) for the mask.
  *  - `state_steps[r]` is incremented by 1 iff `active_mask[r]`, BEFORE the
  *    update math reads it, so a replica's first update sees step 1 -- unless
- *    `steps_already_bumped` is non-zero (a caller whose counter lives in another
- *    type does the increment itself and passes a converted copy).  Frozen rows
- *    are never read or written: they stay byte-identical.
+ *    `steps_already_bumped` has the bit CB200_STEPS_ALREADY_BUMPED (a caller whose
+ *    counter lives in another type does the increment itself and passes a
+ *    converted copy).  Frozen rows are never read or written: they stay
+ *    byte-identical.  `steps_already_bumped` is a set of cb200_call_flags bits.
  *  - `workspace` is device scratch of at least `cb200_workspace_bytes(n_rows)`
  *    bytes, 256-byte aligned, owned by the caller.  It holds the compacted list
- *    of active rows and one record of per-row scalars per active row.
- *    Two calls that may overlap on the GPU (different streams) need two
- *    workspaces.
+ *    of active rows and one record of per-row scalars per active row, and needs
+ *    no initial contents.  Two calls that may overlap on the GPU (different
+ *    streams) need two workspaces.
+ *  - A step is normally two kernel launches (row compaction, then the update).
+ *    With the bit CB200_WORKSPACE_PREPARED the caller vouches that this workspace
+ *    went through cb200_workspace_prepare() for this `n_rows` and has since been
+ *    used only by step calls with the same `n_rows`; the library may then run a
+ *    step whose buffers fit in L2 (dense 16-byte-aligned rows, fewer than 2^24
+ *    elements per buffer) as ONE launch, with bit-identical results.
  *  - `active_rows_hint` is the number of non-zero entries of `active_mask` if
  *    the host happens to know it, else -1.  It only sizes the grid (one CTA per
  *    tile of an active row; without it, of every row, and the CTAs of frozen rows
@@ -59,6 +66,12 @@ extern "C" {
 
 enum cb200_dtype { CB200_F32 = 0, CB200_F64 = 1, CB200_F16 = 2, CB200_BF16 = 3 };
 
+/* Bits of the `steps_already_bumped` argument of the step entry points. */
+enum cb200_call_flags {
+  CB200_STEPS_ALREADY_BUMPED = 1, /* the caller has advanced state_steps of the active rows */
+  CB200_WORKSPACE_PREPARED = 2    /* cb200_workspace_prepare() ran on this workspace for this n_rows */
+};
+
 enum cb200_status {
   CB200_OK = 0,
   CB200_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, bad flag mix */
@@ -80,6 +93,16 @@ const char* cb200_last_error(void);
  * done once per step by a prologue kernel that writes this scratch.
  */
 size_t cb200_workspace_bytes(int64_t n_rows);
+
+/*
+ * Zeroes (asynchronously, on `stream`) the per-row ticket counters that the single-launch
+ * form of a step keeps in the workspace; afterwards the caller may pass
+ * CB200_WORKSPACE_PREPARED with this workspace and this `n_rows`.  Every single-launch step
+ * leaves the counters zero again, so once is enough -- until the workspace is used with
+ * another `n_rows` or written by anyone else.  No counterpart in the reference (one launch
+ * per step there, a block-level mask test, cuda/adam.cu:232-246).
+ */
+int cb200_workspace_prepare(void* workspace, size_t workspace_bytes, int64_t n_rows, void* stream);
 
 /*
  * Fused Adam / AdamW (+AMSGrad) step over all replicas.

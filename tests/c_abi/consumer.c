@@ -13,7 +13,7 @@ int main(void) {
   policy.kind = CB200_LR_COSINE;
   policy.t_max = 10.0;
   if (cb200_version() < 200) return 2;
-  if (cb200_workspace_bytes(1024) != 256 + 4096 + 64 * 1024) return 3;
+  if (cb200_workspace_bytes(1024) != 256 + 4096 + 64 * 1024 + 4096) return 3;
   /* argument errors are reported before anything touches a device */
   if (cb200_scatter_rows(0, 0, -1, 1, 1, 0, 0, 0, 0, 0) != CB200_ERR_INVALID_ARGUMENT) return 4;
   if (strstr(cb200_last_error(), "must be >= 0") == 0) return 5;

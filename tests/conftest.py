@@ -50,3 +50,26 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture
 def cuda():
     return torch.device("cuda:0")
+
+
+# The step has two forms with identical results: one launch for ensembles that fit in L2 (most
+# test cases), two launches otherwise.  These parity suites run every case through both.
+BOTH_STEP_FORMS = {"test_gpu_aten_parity", "test_gpu_layouts", "test_gpu_masking", "test_gpu_dtypes",
+                   "test_gpu_from_parts", "test_gpu_golden_and_oracle", "test_gpu_frontend",
+                   "test_gpu_reference_cuda", "test_gpu_property"}
+
+
+def pytest_generate_tests(metafunc):
+    if metafunc.module.__name__ in BOTH_STEP_FORMS:
+        if "step_form" not in metafunc.fixturenames:
+            metafunc.fixturenames.append("step_form")
+        metafunc.parametrize("step_form", ["one_launch", "two_launches"], indirect=True)
+
+
+@pytest.fixture
+def step_form(request):
+    from churten_b200.kernels import _C
+
+    _C.set_single_launch(request.param == "one_launch")
+    yield request.param
+    _C.set_single_launch(True)

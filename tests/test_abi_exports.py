@@ -51,9 +51,15 @@ def test_version_and_workspace_bytes():
     assert lib.cb200_version() >= 100
     assert lib.cb200_workspace_bytes(0) == 256
     # header + ids rounded to 256 + 64 bytes per row (the fp64 record; fp32 uses half)
-    assert lib.cb200_workspace_bytes(1) == 256 + 256 + 64
-    assert lib.cb200_workspace_bytes(100) == 256 + 512 + 6400
-    assert lib.cb200_workspace_bytes(8192) == 256 + 8192 * 4 + 8192 * 64
+    # + one int32 ticket counter per row, rounded to 256 (the single-launch step)
+    assert lib.cb200_workspace_bytes(1) == 256 + 256 + 64 + 256
+    assert lib.cb200_workspace_bytes(100) == 256 + 512 + 6400 + 512
+    assert lib.cb200_workspace_bytes(8192) == 256 + 8192 * 4 + 8192 * 64 + 8192 * 4
+    # preparing a workspace: argument checks need no GPU
+    assert lib.cb200_workspace_prepare(None, 1 << 20, 4, None) == _lib.ERR_WORKSPACE
+    assert lib.cb200_workspace_prepare(256, 16, 4, None) == _lib.ERR_WORKSPACE
+    assert "too small" in _lib.last_error()
+    assert lib.cb200_workspace_prepare(256, 1 << 20, 0, None) == _lib.OK
 
 
 def test_argument_errors_need_no_gpu():

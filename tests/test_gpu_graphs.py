@@ -140,7 +140,8 @@ def test_replay_of_the_step_on_per_parameter_gradients(cuda, opt_name, extra, ma
     static = {name: torch.zeros(shape, device=cuda) for name, shape, _, _ in graphed.param_meta}
     before = _C.launch_count()
     step = GraphedUpdate(opt, graphed, grads=static, materialize=materialize)
-    assert _C.launch_count() - before == 2 * (3 if materialize else 2)      # warm-up + capture
+    # warm-up + capture, each: (scatter +) a step of one or two launches
+    assert _C.launch_count() - before in {2 * (k + int(materialize)) for k in (1, 2)}
     assert graphed.optimizer_state["state_steps"].abs().sum() == 0
     gen = torch.Generator(device=cuda).manual_seed(1)
     for it in range(5):
