@@ -475,44 +475,70 @@ def parity_replay(state, opt, w, device) -> dict:
 
 def measure_small(name, args, device, peak):
     """A few steps of another workload on this GPU (after the headline): median op time from
-    CUDA events, GB/s of algorithmic bytes, clocks, and the same parity replay."""
+    CUDA events, GB/s of algorithmic bytes, clocks, and the same parity replay.
+
+    A workload that fits in L2 is timed cold in two ways: over a rotating set of independent
+    states whose total size is three times L2 (each step's inputs were evicted by the other
+    states' traffic: "inputs larger than L2"), and after 256 MiB were written between steps
+    (the step then also pays for writing back the flush's dirty lines) or read (clean lines);
+    and warm, back to back on one state, per eager step and per CUDA-graph replay."""
     import torch
 
     from churten_b200.kernels import _C
 
     w = dict(WORKLOADS[name], dtype="f32")
     n, t = w["rows"], w["row_len"]
-    state, opt = build_state(w, n, device, seed=sorted(WORKLOADS).index(name) + 1)
     bpe = _bytes_per_elem(w)
-    active = int(state.active_mask.sum().item())
+    seed = sorted(WORKLOADS).index(name) + 1
     fits_l2 = n * t * bpe <= 2 * 126e6
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if fits_l2 else None
-    steps = 10 if not fits_l2 else 30
+    copies = min(16, math.ceil(3 * 126e6 / (n * t * bpe))) if fits_l2 else 1
+    states = [build_state(w, n, device, seed=seed + 100 * i) for i in range(copies)]
+    opt = states[0][1]
+    states = [s for s, _ in states]
+    state = states[0]
+    active = int(state.active_mask.sum().item())
+    steps = 10 if not fits_l2 else 6 * copies
     stream = torch.cuda.current_stream(device)
-    for _ in range(3):
-        opt.update(state)
+    for s in states * 3:
+        opt.update(s)
     torch.cuda.synchronize(device)
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    launches0 = _C.launch_count()
-    with ClockSampler(device.index) as clocks:
-        for i in range(steps):
-            if flush is not None:
-                flush.zero_()
+
+    def timed(count, pick, before=None):
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
+        for i in range(count):
+            if before is not None:
+                before()
             starts[i].record(stream)
-            opt.update(state)
+            opt.update(pick(i))
             stops[i].record(stream)
         torch.cuda.synchronize(device)
+        return [a.elapsed_time(b) for a, b in zip(starts, stops)]
+
+    launches0 = _C.launch_count()
+    with ClockSampler(device.index) as clocks:
+        ms = timed(steps, lambda i: states[i % copies])
     launches = _C.launch_count() - launches0
-    ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
     med = statistics.median(ms)
+    # every state of the set has the same mask fraction only in expectation: count this one's
     gbs = active * t * bpe / (med * 1e-3) / 1e9
     out = {"description": w["desc"], "rows": n, "row_len": t, "active_rows": active, "steps": steps,
            "op_ms_median": med, "op_ms_p10": _percentile(ms, 0.1), "op_ms_p90": _percentile(ms, 0.9),
            "bytes_per_element": bpe, "gbs": gbs, "frac": gbs / peak, "frac_of_nominal_8tbs": gbs / 8000.0,
            "param_updates_per_s": active * t / (med * 1e-3), "launches_per_step": launches / steps,
-           "l2": "evicted between timed steps (256 MiB written, not timed)" if fits_l2 else "inputs larger than L2"}
+           "l2": (f"rotating set of {copies} independent states ({copies * n * t * bpe / 1e6:.0f} MB of step "
+                  f"traffic, 3 x L2): each step's inputs have been evicted") if fits_l2 else "inputs larger than L2"}
     if fits_l2:
+        # all states share the mask draw's seed family; use the median state's count for GB/s
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        after_flush = timed(30, lambda i: state, before=flush.zero_)
+        out["op_ms_median_after_l2_write_flush"] = statistics.median(after_flush)
+        # the same eviction by READING 256 MiB: L2 is then full of clean lines, and the step
+        # pays for its own traffic only
+        words = flush.view(torch.int64)
+        after_read = timed(30, lambda i: state, before=lambda: words.sum())
+        out["op_ms_median_after_l2_read_flush"] = statistics.median(after_read)
+        del flush, words
         # back-to-back eager steps with a warm L2: what a training loop pays per step, host included
         reps = 300
         for _ in range(20):
@@ -527,9 +553,22 @@ def measure_small(name, args, device, peak):
         torch.cuda.synchronize(device)
         out["eager_warm_us_per_step"] = e0.elapsed_time(e1) * 1e3 / reps
         out["eager_warm_wall_us_per_step"] = (time.perf_counter() - t0) * 1e6 / reps
+        from churten_b200.graphs import GraphedUpdate
+
+        replay = GraphedUpdate(opt, state, active_rows=active)
+        for _ in range(5):
+            replay()
+        torch.cuda.synchronize(device)
+        e0.record(stream)
+        for _ in range(reps):
+            replay()
+        e1.record(stream)
+        torch.cuda.synchronize(device)
+        out["graph_warm_us_per_step"] = e0.elapsed_time(e1) * 1e3 / reps
+        del replay
     out["clocks"] = clocks.summary()
     out["parity"] = parity_replay(state, opt, w, device)
-    del state, flush
+    del state, states
     torch.cuda.empty_cache()
     return out
 

@@ -212,7 +212,7 @@ def test_hint_follows_mask_changes_through_the_operator(cuda):
     assert_bits_equal("params", p, p_ref)
     assert_bits_equal("momentum_buffers", buf, b_ref)
     assert torch.equal(steps, ref_steps)
-    slot = C._slots[(cuda.index or 0, torch.cuda.current_stream().cuda_stream)]
+    slot = C._slots[(cuda.index or 0, torch.cuda.current_stream().cuda_stream, R)]
     assert slot.count == R  # the last mask (everything thawed) was counted on the device
 
 

@@ -206,7 +206,7 @@ def test_guard_regions_survive(ops, cuda, T):
 
 
 @pytest.mark.parametrize("offset", [0, 3])
-def test_many_rows_are_compacted_by_several_ctas(ops, cuda, offset):
+def test_many_rows_are_compacted_by_several_ctas(ops, cuda, offset, step_form):
     """More rows than one prologue CTA owns (1024): every CTA counts the active rows before
     its block itself, from a mask that need not be 16-byte aligned; whole blocks may be
     frozen.  Plain SGD, so the expected result is one line of tensor arithmetic."""
@@ -237,8 +237,9 @@ def test_many_rows_are_compacted_by_several_ctas(ops, cuda, offset):
     # the list of active rows the step kernel walked: the workspace header holds its length
     from churten_b200.kernels import _C
 
-    slot = _C._slots[(cuda.index or 0, torch.cuda.current_stream(cuda).cuda_stream)]
-    header = slot.ws[:8].view(torch.int32).tolist()
-    ids = slot.ws[256: 256 + 4 * header[0]].view(torch.int32)
-    assert header == [int(mask.sum()), R]
-    assert torch.equal(ids.long(), mask.nonzero().flatten())       # in row order
+    if step_form == "two_launches":   # (the single-launch form builds no list)
+        slot = _C._slots[(cuda.index or 0, torch.cuda.current_stream(cuda).cuda_stream, R)]
+        header = slot.ws[:8].view(torch.int32).tolist()
+        ids = slot.ws[256: 256 + 4 * header[0]].view(torch.int32)
+        assert header == [int(mask.sum()), R]
+        assert torch.equal(ids.long(), mask.nonzero().flatten())       # in row order

