@@ -590,9 +590,13 @@ def run_ours(args, w, world, rank, local_rank):
     from churten_b200.sharded import MetricGather, ShardSpec, verify_shard_map
 
     n_local, t = w["rows"], w["row_len"]
-    spec = ShardSpec(n_local * world, world, rank)
+    spec = ShardSpec(n_local * world, world, rank, layout=args.layout)
     verify_shard_map(spec)
     state, opt = build_state(w, n_local, device, seed=5 * 1000 + rank)
+    if args.frozen_pattern == "clustered":
+        # a clustered half of the WHOLE ensemble frozen (the lower half of the replica range):
+        # what early stopping does to a sweep laid out along the replica axis
+        state.active_mask.copy_(spec.global_rows(device) >= spec.n_rows // 2)
     gather = MetricGather(spec, device)
     loss = state.grads[:, 0].contiguous()  # stands in for the per-replica loss of the step
     active_rows = int(state.active_mask.sum().item())
@@ -727,6 +731,12 @@ def run_ours(args, w, world, rank, local_rank):
                       ranks=world, note="ok = every rank's replay; rows and mismatches listed are rank 0's")
     total_ms, e2e_ms, op_ms = stats.tolist()
     job_elems, job_launches = work.tolist()
+    rows_by_rank = [active_rows]
+    if distributed:
+        mine = torch.tensor([active_rows], dtype=torch.int64, device=device)
+        everyone = torch.empty(world, dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(everyone, mine)
+        rows_by_rank = everyone.tolist()
 
     if rank == 0:
         peak, peak_kind = _peak_gbs()
@@ -755,6 +765,8 @@ def run_ours(args, w, world, rank, local_rank):
                                                   if flush_buf is None else
                                                   "working set fits in L2: 256 MiB written between timed steps, "
                                                   "flush excluded from the time"),
+                       "layout": args.layout, "frozen_pattern": args.frozen_pattern,
+                       "active_rows_by_rank": rows_by_rank, "op_ms_slowest_rank": op_ms,
                        "parallelism": f"replica-block x{world}, no collective on the step; "
                                       f"loss all-gather ({n_local * world * 4} B) on a side stream"},
             "e2e": {"value": job_elems * e2e_steps / (e2e_ms * 1e-3), "unit": "param-updates/s",
@@ -776,7 +788,7 @@ def run_ours(args, w, world, rank, local_rank):
         }
         default_line = (world == 1 and args.workload == "c5_shard" and not args.rows and not args.row_len
                         and args.dtype == "f32" and not args.moment_dtype and not args.apply_gradient
-                        and not args.graph)
+                        and not args.graph and args.frozen_pattern == "random")
         if default_line and not args.no_extras:
             # the other configurations and the on-box comparator, after the headline's state is freed
             del state, block_states, pinned, gather, loss, update
@@ -966,6 +978,11 @@ def main():
     ap.add_argument("--moment-dtype", choices=("bf16", "f16"), default=None,
                     help="Adam / SGD with fp32 parameters and 2-byte state buffers (an extension; not the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layout", choices=("contiguous", "interleaved"), default="contiguous",
+                    help="which replicas a rank owns: a contiguous block, or every world_size-th")
+    ap.add_argument("--frozen-pattern", choices=("random", "clustered"), default="random",
+                    help="random: the workload's seeded fraction on every rank; clustered: the lower "
+                         "half of the whole ensemble's replica range")
     ap.add_argument("--no-extras", action="store_true",
                     help="default line only: skip the c1-c4 sub-records and the reference-CUDA comparator")
     ap.add_argument("--apply-gradient", action="store_true",

@@ -44,6 +44,21 @@ struct AdagradOp {
   __device__ static __forceinline__ void apply(Math (&x)[kBufs], const Row& c, int flags) {
     adagrad_elem<FUSE, Math>(x[0], x[1], x[2], c, (flags & 1) != 0);
   }
+
+  // fp16 / bf16 storage: the bounded fast form of the parameter update (rowmath.cuh) -- fp32
+  // approximations instead of the fp64 divide -- with the exact fp64 chain for the elements it
+  // cannot decide.  The accumulator is always exact.
+  static constexpr bool kNarrowFast = sizeof(T) == 2;
+  using Aux = AdagradNarrowAux;
+  __device__ static __forceinline__ Aux make_aux(const Row& c) { return adagrad_narrow_aux(c); }
+  __device__ static __forceinline__ bool apply_bounds(Math (&x)[kBufs], const Row& c, const Aux& aux,
+                                                      int flags, float& lo, float& hi) {
+    adagrad_accumulate<FUSE, Math>(x[0], x[1], x[2], c, (flags & 1) != 0);   // x[1]: the decayed gradient
+    return adagrad_param_bounds(x[0], x[1], x[2], aux, lo, hi);
+  }
+  __device__ static __forceinline__ void finish_exact(Math (&x)[kBufs], const Row& c) {
+    x[0] = adagrad_param<Math>(x[0], x[1], x[2], c);
+  }
 };
 
 struct AdagradArgs {

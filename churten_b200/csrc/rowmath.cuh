@@ -171,11 +171,12 @@ __device__ __forceinline__ AdagradRow adagrad_row(double lr, double lr_decay, do
 // registers; nothing here touches memory.
 // ---------------------------------------------------------------------------
 
-// adam_math, fused_adam_utils.cuh:55-84.  `std::max(a, b)` is `(a < b) ? b : a`,
-// which keeps a NaN already stored in max_exp_avg_sq.
+// adam_math, fused_adam_utils.cuh:55-84, in two halves: the weight decay and the moments
+// (`p` leaves as the decayed parameter), then the parameter update.  `std::max(a, b)` is
+// `(a < b) ? b : a`, which keeps a NaN already stored in max_exp_avg_sq.
 template <bool AMSGRAD, bool ADAMW, int FUSE, class M>
-__device__ __forceinline__ void adam_elem(M& p, M g, M& m, M& v, M& mx, const AdamRowT<M>& c,
-                                          bool maximize) {
+__device__ __forceinline__ void adam_moments(M& p, M g, M& m, M& v, M& mx, const AdamRowT<M>& c,
+                                             bool maximize) {
   if (maximize) g = -g;
   if (c.weight_decay != M(0)) {
     if (!ADAMW) {
@@ -187,15 +188,80 @@ __device__ __forceinline__ void adam_elem(M& p, M g, M& m, M& v, M& mx, const Ad
   m = fma_rn(c.beta1, m, fma_rn(-c.beta1, g, g));
   const M gg = mul_rn(g, g);
   v = fma_rn(c.beta2, v, fma_rn(-c.beta2, gg, gg));
-  M root;
-  if (AMSGRAD) {
-    mx = (mx < v) ? v : mx;
-    root = sqrt_rn(mx);
-  } else {
-    root = sqrt_rn(v);
-  }
-  const M denom = add_rn(div_rn(root, c.bc2_sqrt), c.eps);
-  p = sub_rn(p, div_rn(mul_rn(c.step_size, m), denom));
+  if (AMSGRAD) mx = (mx < v) ? v : mx;
+}
+
+// `second` is exp_avg_sq, or max_exp_avg_sq with AMSGrad.
+template <class M>
+__device__ __forceinline__ M adam_param(M p, M m, M second, const AdamRowT<M>& c) {
+  const M denom = add_rn(div_rn(sqrt_rn(second), c.bc2_sqrt), c.eps);
+  return sub_rn(p, div_rn(mul_rn(c.step_size, m), denom));
+}
+
+template <bool AMSGRAD, bool ADAMW, int FUSE, class M>
+__device__ __forceinline__ void adam_elem(M& p, M g, M& m, M& v, M& mx, const AdamRowT<M>& c,
+                                          bool maximize) {
+  adam_moments<AMSGRAD, ADAMW, FUSE, M>(p, g, m, v, mx, c, maximize);
+  p = adam_param<M>(p, m, AMSGRAD ? mx : v, c);
+}
+
+// ---------------------------------------------------------------------------
+// 2-byte storage: the parameter update without IEEE divisions and square roots.
+//
+// With fp16 / bf16 storage the parameter that reaches memory is a 2-byte rounding of the
+// fp32 value `p - q`, q = (step_size * m) / (sqrt(second) / bc2_sqrt + eps): 16 (13) of its
+// 24 bits are dropped.  The two IEEE divisions and the square root are a third of the
+// kernel's instructions, and these kernels are bound by instruction issue.  So q is first
+// computed with the hardware approximations -- sqrt.approx, rcp.approx (relative error at
+// most 2^-23 each over the normal range), a precomputed 1 / bc2_sqrt, ordinary roundings --
+// which gives q~ with |q~ - q| <= rho |q~| + tiny:  sqrt 2^-22 against the exact chain's
+// correctly rounded one, 1 / bc2_sqrt 2^-23, the fused sum one rounding instead of two
+// (<= 3 * 2^-24), rcp 2^-23, the product 2^-24, q's own rounding 2^-24: below 2^-20.5 in all,
+// and rho = 2^-19 leaves a factor of three.  Then `lo = p - (q~ + delta)` and
+// `hi = p - (q~ - delta)` enclose the exact fp32 result, because fp32 subtraction is monotonic,
+// and so is the rounding to storage: if lo and hi round to the SAME 2-byte value, that value is
+// the exact chain's result, bit for bit.  Otherwise (a result within ~2^-19 of a rounding
+// boundary: a few elements in 10^4), or when a precondition of the error bound fails
+// (`second` below 2^-100 but not zero, an intermediate NaN or infinity, a row whose eps or
+// bias correction is out of range), the caller runs the exact chain for that element.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kNarrowRho = 1.9073486328125e-06f;       // 2^-19
+constexpr float kNarrowTiny = 7.174648137343064e-43f;    // 2^-140: what the subnormal range can add
+__device__ __forceinline__ float quiet_nan() { return __int_as_float(0x7fc00000); }
+
+// 1 / bc2_sqrt for the fast form, or NaN for a row the error bound does not cover
+// (every bound computed from a NaN is rejected by the caller's `lo <= hi` test).
+__device__ __forceinline__ float adam_narrow_aux(const AdamRowT<float>& c) {
+  const bool covered = c.eps >= 0.0f && c.eps <= 0x1p100f && c.bc2_sqrt >= 0x1p-40f && c.bc2_sqrt <= 2.0f;
+  return covered ? __frcp_rn(c.bc2_sqrt) : quiet_nan();
+}
+
+// q~: the approximation of (step_size * m) / (sqrt(second) / bc2_sqrt + eps).
+__device__ __forceinline__ float adam_fast_quotient(float m, float second, const AdamRowT<float>& c,
+                                                    float inv_bc2) {
+  const float d = __fmaf_rn(sqrt_approx(second), inv_bc2, c.eps);
+  return __fmul_rn(__fmul_rn(c.step_size, m), rcp_approx(d));
+}
+
+// Encloses adam_param(p, m, second, c) in [lo, hi]; false if `second` is outside the bound's range.
+__device__ __forceinline__ bool adam_param_bounds(float p, float m, float second,
+                                                  const AdamRowT<float>& c, float inv_bc2,
+                                                  float& lo, float& hi) {
+  const float q = adam_fast_quotient(m, second, c, inv_bc2);
+  const float delta = __fmaf_rn(fabsf(q), kNarrowRho, kNarrowTiny);
+  lo = __fsub_rn(p, __fadd_rn(q, delta));
+  hi = __fsub_rn(p, __fsub_rn(q, delta));
+  return second >= 0x1p-100f || second == 0.0f;
 }
 
 // sgd_math, cuda/sgd.cu:103-131.  With HAS_BUF the buffer is always rewritten,
@@ -230,11 +296,11 @@ __device__ __forceinline__ void sgd_elem(M& p, M g, M& buf, const SgdRowT<M>& c,
   p = (FUSE & kSgdFuseUpdate) ? fma_rn(-c.lr, g, p) : sub_rn(p, mul_rn(c.lr, g));
 }
 
-// adagrad_math, fused_adagrad_utils.cuh:25-48.  The accumulator lives in the math
-// type; the hyper-parameters are doubles, so with float math the weight decay and
-// the parameter update widen to fp64 and narrow back.
+// adagrad_math, fused_adagrad_utils.cuh:25-48, in two halves.  The accumulator lives in the
+// math type; the hyper-parameters are doubles, so with float math the weight decay and
+// the parameter update widen to fp64 and narrow back.  `g` leaves as the decayed gradient.
 template <int FUSE, class M>
-__device__ __forceinline__ void adagrad_elem(M& p, M g, M& sum, const AdagradRow& c, bool maximize) {
+__device__ __forceinline__ void adagrad_accumulate(M p, M& g, M& sum, const AdagradRow& c, bool maximize) {
   if (maximize) g = -g;
   if (c.weight_decay != 0.0) {
     const double pd = static_cast<double>(p);
@@ -244,9 +310,56 @@ __device__ __forceinline__ void adagrad_elem(M& p, M g, M& sum, const AdagradRow
     g = static_cast<M>(t);  // round to nearest for float, identity for double
   }
   sum = (FUSE & kAdagradFuseSum) ? fma_rn(g, g, sum) : add_rn(sum, mul_rn(g, g));
+}
+
+template <class M>
+__device__ __forceinline__ M adagrad_param(M p, M g, M sum, const AdagradRow& c) {
   const double denom = __dadd_rn(static_cast<double>(sqrt_rn(sum)), c.eps);
   const double delta = __ddiv_rn(__dmul_rn(c.clr, static_cast<double>(g)), denom);
-  p = static_cast<M>(__dsub_rn(static_cast<double>(p), delta));
+  return static_cast<M>(__dsub_rn(static_cast<double>(p), delta));
+}
+
+template <int FUSE, class M>
+__device__ __forceinline__ void adagrad_elem(M& p, M g, M& sum, const AdagradRow& c, bool maximize) {
+  adagrad_accumulate<FUSE, M>(p, g, sum, c, maximize);
+  p = adagrad_param<M>(p, g, sum, c);
+}
+
+// The fast form for 2-byte storage (see adam_param_bounds): the exact chain computes
+// float(double(p) - clr * g / (sqrtf(sum) + eps)) in fp64, whose own error (2^-52) is
+// nothing beside fp32's, so q = clr * g / (sqrt(sum) + eps) is approximated in fp32:
+// float(clr) 2^-24, its product with g 2^-24, sqrt.approx 2^-22, the sum 2^-24 (eps is an
+// fp32 value widened: exact), rcp.approx 2^-23, the last product 2^-24: below 2^-21 < rho.
+// The exact chain rounds the fp64 difference to fp32 (a second rounding, which can move the
+// fp32 result by one unit against a direct rounding), so delta also carries 2^-22 |p|.
+struct AdagradNarrowAux {
+  float clr;  // NaN for a row the error bound does not cover
+  float eps;
+};
+__device__ __forceinline__ AdagradNarrowAux adagrad_narrow_aux(const AdagradRow& c) {
+  const double size = fabs(c.clr);
+  const bool covered = c.eps >= 0.0 && c.eps <= 0x1p100 && size <= 0x1p100 && (size >= 0x1p-100 || c.clr == 0.0);
+  AdagradNarrowAux aux;
+  aux.clr = covered ? static_cast<float>(c.clr) : quiet_nan();
+  aux.eps = static_cast<float>(c.eps);
+  return aux;
+}
+// q~: the approximation of clr * g / (sqrt(sum) + eps); `n` returns the numerator.
+__device__ __forceinline__ float adagrad_fast_quotient(float g, float sum, const AdagradNarrowAux& aux,
+                                                       float& n) {
+  n = __fmul_rn(aux.clr, g);
+  return __fmul_rn(n, rcp_approx(__fadd_rn(sqrt_approx(sum), aux.eps)));
+}
+
+__device__ __forceinline__ bool adagrad_param_bounds(float p, float g, float sum, const AdagradNarrowAux& aux,
+                                                     float& lo, float& hi) {
+  float n;
+  const float q = adagrad_fast_quotient(g, sum, aux, n);
+  const float delta = __fmaf_rn(fabsf(q), kNarrowRho, __fmaf_rn(fabsf(p), 0x1p-22f, kNarrowTiny));
+  lo = __fsub_rn(p, __fadd_rn(q, delta));
+  hi = __fsub_rn(p, __fsub_rn(q, delta));
+  // `sum` and the numerator in the normal range (or exactly zero)
+  return (sum >= 0x1p-100f || sum == 0.0f) && (fabsf(n) >= 0x1p-126f || n == 0.0f);
 }
 
 }  // namespace cb200

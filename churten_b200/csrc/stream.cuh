@@ -276,14 +276,13 @@ struct Pack<__half> {
       out[2 * i + 1] = __high2float(h);
     }
   }
+  // two elements rounded to storage, as one 32-bit word (the first in the low half)
+  __device__ static __forceinline__ unsigned pack2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const unsigned*>(&h);
+  }
   __device__ static __forceinline__ uint4 pack(const float (&in)[8]) {
-    unsigned w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __half2 h = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
-      w[i] = *reinterpret_cast<const unsigned*>(&h);
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
+    return make_uint4(pack2(in[0], in[1]), pack2(in[2], in[3]), pack2(in[4], in[5]), pack2(in[6], in[7]));
   }
 };
 
@@ -302,16 +301,104 @@ struct Pack<__nv_bfloat16> {
       out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
+  __device__ static __forceinline__ unsigned pack2(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const unsigned*>(&h);
+  }
   __device__ static __forceinline__ uint4 pack(const float (&in)[8]) {
-    unsigned w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
-      w[i] = *reinterpret_cast<const unsigned*>(&h);
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
+    return make_uint4(pack2(in[0], in[1]), pack2(in[2], in[3]), pack2(in[4], in[5]), pack2(in[6], in[7]));
   }
 };
+
+// ---------------------------------------------------------------------------
+// One 16-byte access of every buffer through the optimizer's element function:
+// `raw` holds the loaded accesses and leaves holding what is to be stored.
+//
+// An optimizer with 2-byte storage may offer the bounded fast form of its parameter update
+// (rowmath.cuh): Op::kNarrowFast, `Aux make_aux(Row)` once per tile,
+// `bool apply_bounds(e, row, aux, flags, lo, hi)` (state buffers updated exactly, e[0] left as
+// the input of the exact parameter update, [lo, hi] enclosing its result) and
+// `finish_exact(e, row)`.  Elements are then handled in pairs, the unit of a conversion to
+// storage: where both elements' bounds round to one storage word, that word is stored;
+// otherwise the pair takes the exact chain.
+// ---------------------------------------------------------------------------
+struct NoAux {};
+template <class Op, class = void>
+struct NarrowFast {
+  static constexpr bool value = false;
+  using Aux = NoAux;
+  __device__ static __forceinline__ Aux make_aux(const typename Op::Row&) { return Aux{}; }
+};
+template <class Op>
+struct NarrowFast<Op, std::enable_if_t<Op::kNarrowFast>> {
+  static constexpr bool value = true;
+  using Aux = typename Op::Aux;
+  __device__ static __forceinline__ Aux make_aux(const typename Op::Row& c) { return Op::make_aux(c); }
+};
+
+template <class Op>
+__device__ __forceinline__ void update_access(uint4 (&raw)[Op::kBufs], const typename Op::Row& c,
+                                              const typename NarrowFast<Op>::Aux& aux, int flags) {
+  constexpr int NB = Op::kBufs;
+  using M = typename Op::Math;
+  using P = Pack<typename Op::Storage>;
+  constexpr int VEC = P::kVec;
+  M x[NB][VEC];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) P::unpack(raw[b], x[b]);
+  if constexpr (NarrowFast<Op>::value) {
+    static_assert(VEC == 8 && (Op::kWriteMask & 1u), "2-byte storage, parameters in buffer 0");
+    unsigned word[VEC / 2];
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) {
+      M e0[NB], e1[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        e0[b] = x[b][2 * j];
+        e1[b] = x[b][2 * j + 1];
+      }
+      float lo0, hi0, lo1, hi1;
+      bool covered = Op::apply_bounds(e0, c, aux, flags, lo0, hi0);
+      covered = Op::apply_bounds(e1, c, aux, flags, lo1, hi1) && covered;
+      unsigned w = P::pack2(lo0, lo1);
+      // `lo <= hi` is false for a NaN on either side: those take the exact chain too
+      if (!(covered && lo0 <= hi0 && lo1 <= hi1 && w == P::pack2(hi0, hi1))) {
+        Op::finish_exact(e0, c);
+        Op::finish_exact(e1, c);
+        w = P::pack2(e0[0], e1[0]);
+      }
+      word[j] = w;
+#pragma unroll
+      for (int b = 1; b < NB; ++b) {
+        if ((Op::kWriteMask >> b) & 1) {
+          x[b][2 * j] = e0[b];
+          x[b][2 * j + 1] = e1[b];
+        }
+      }
+    }
+    raw[0] = make_uint4(word[0], word[1], word[2], word[3]);
+#pragma unroll
+    for (int b = 1; b < NB; ++b) {
+      if ((Op::kWriteMask >> b) & 1) raw[b] = P::pack(x[b]);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      M e[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) e[b] = x[b][k];
+      Op::apply(e, c, flags);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        if ((Op::kWriteMask >> b) & 1) x[b][k] = e[b];
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      if ((Op::kWriteMask >> b) & 1) raw[b] = P::pack(x[b]);
+    }
+  }
+}
 
 // ---------------------------------------------------------------------------
 // Launch 1: the prologue.
@@ -477,6 +564,7 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
     }
     const int64_t r = ws.ids[a];
     const Row c = rows[a];
+    const typename NarrowFast<Op>::Aux aux = NarrowFast<Op>::make_aux(c);
 
     T* base[NB];
 #pragma unroll
@@ -501,23 +589,10 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       if (e0 + u * lane_elems < row_len) {
-        M x[NB][VEC];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) P::unpack(raw[u][b], x[b]);
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-          M e[NB];
-#pragma unroll
-          for (int b = 0; b < NB; ++b) e[b] = x[b][k];
-          Op::apply(e, c, flags);
-#pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            if ((Op::kWriteMask >> b) & 1) x[b][k] = e[b];
-          }
-        }
+        update_access<Op>(raw[u], c, aux, flags);
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          if ((Op::kWriteMask >> b) & 1) store16<STREAM>(base[b] + u * lane_elems, P::pack(x[b]));
+          if ((Op::kWriteMask >> b) & 1) store16<STREAM>(base[b] + u * lane_elems, raw[u][b]);
         }
       }
     }
@@ -593,26 +668,14 @@ single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
   }
   __syncthreads();
   const Row c = row_record;
+  const typename NarrowFast<Op>::Aux aux = NarrowFast<Op>::make_aux(c);
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
     if (e0 + u * lane_elems < row_len) {
-      M x[NB][VEC];
-#pragma unroll
-      for (int b = 0; b < NB; ++b) P::unpack(raw[u][b], x[b]);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        M e[NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) e[b] = x[b][k];
-        Op::apply(e, c, flags);
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          if ((Op::kWriteMask >> b) & 1) x[b][k] = e[b];
-        }
-      }
+      update_access<Op>(raw[u], c, aux, flags);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        if ((Op::kWriteMask >> b) & 1) store16<false>(base[b] + u * lane_elems, P::pack(x[b]));
+        if ((Op::kWriteMask >> b) & 1) store16<false>(base[b] + u * lane_elems, raw[u][b]);
       }
     }
   }

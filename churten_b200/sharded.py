@@ -12,6 +12,14 @@ contributes its `(N/G,)` slice to an all-gather (NCCL over NVLink on GPUs, gloo
 on CPU).  It is tiny (32 KB at N = 8192) and is issued on a side stream so it
 overlaps the step.  The reference has no multi-device code at all; this module
 is what its single-device `State` becomes on 2-8 GPUs.
+
+Contiguous blocks are the default.  Early stopping tends to freeze neighbouring
+replicas together (a sweep laid out along the replica axis: one end of the range
+diverges or converges first), and the step time of the job is that of the rank with
+the most active rows, so `ShardSpec(..., layout="interleaved")` deals the replicas
+round-robin instead: replica r lives on rank `r mod G`, and any contiguous run of
+frozen replicas is spread evenly over the ranks.  The metric gather restores replica
+order either way.
 """
 
 from __future__ import annotations
@@ -37,27 +45,69 @@ def shard_sizes(n_rows: int, world_size: int) -> list[int]:
     return [b - a for a, b in (shard_bounds(n_rows, world_size, r) for r in range(world_size))]
 
 
+LAYOUTS = ("contiguous", "interleaved")
+
+
+def interleaved_count(n_rows: int, world_size: int, rank: int) -> int:
+    """Replicas r in [0, n_rows) with r mod world_size == rank."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    if n_rows < 0:
+        raise ValueError("n_rows must be >= 0")
+    return (n_rows - rank + world_size - 1) // world_size if n_rows > rank else 0
+
+
 @dataclass
 class ShardSpec:
     n_rows: int        # replicas in the whole ensemble
     world_size: int
     rank: int
+    layout: str = "contiguous"   # or "interleaved": replica r on rank r mod world_size
+
+    def __post_init__(self):
+        if self.layout not in LAYOUTS:
+            raise ValueError(f"layout must be one of {LAYOUTS}, got {self.layout!r}")
 
     @property
     def bounds(self) -> tuple[int, int]:
+        """`[start, stop)` of this rank's block (contiguous layout only)."""
+        if self.layout != "contiguous":
+            raise ValueError("an interleaved shard is not a row range; use rows_slice / global_rows")
         return shard_bounds(self.n_rows, self.world_size, self.rank)
 
     @property
+    def rows_slice(self) -> slice:
+        """This rank's replicas as a slice of the ensemble's row axis."""
+        if self.layout == "contiguous":
+            return slice(*shard_bounds(self.n_rows, self.world_size, self.rank))
+        if not 0 <= self.rank < self.world_size:
+            raise ValueError(f"bad rank {self.rank} for world size {self.world_size}")
+        return slice(self.rank, self.n_rows, self.world_size)
+
+    @property
     def n_local(self) -> int:
-        a, b = self.bounds
-        return b - a
+        if self.layout == "contiguous":
+            a, b = self.bounds
+            return b - a
+        return interleaved_count(self.n_rows, self.world_size, self.rank)
+
+    def global_rows(self, device=None) -> torch.Tensor:
+        """`(n_local,)` int64: the ensemble-wide index of each local replica, in local order."""
+        piece = self.rows_slice
+        return torch.arange(piece.start, max(piece.start, piece.stop), piece.step or 1, dtype=torch.int64,
+                            device=device)
+
+    def sizes(self) -> list[int]:
+        """Replicas held by every rank, in rank order."""
+        if self.layout == "contiguous":
+            return shard_sizes(self.n_rows, self.world_size)
+        return [interleaved_count(self.n_rows, self.world_size, r) for r in range(self.world_size)]
 
     def local(self, full: torch.Tensor) -> torch.Tensor:
-        """This rank's rows of an `(N, ...)` tensor that every rank can see."""
-        a, b = self.bounds
+        """This rank's rows of an `(N, ...)` tensor that every rank can see (a view)."""
         if full.shape[0] != self.n_rows:
             raise ValueError(f"expected {self.n_rows} rows, got {full.shape[0]}")
-        return full[a:b]
+        return full[self.rows_slice]
 
 
 def current_spec(n_rows: int, group=None) -> ShardSpec:
@@ -75,8 +125,11 @@ def verify_shard_map(spec: ShardSpec, group=None) -> None:
     call with an error instead of a hang.
     """
     if not (dist.is_available() and dist.is_initialized()) or spec.world_size == 1:
-        if spec.bounds != (0, spec.n_rows):
+        if spec.n_local != spec.n_rows:
             raise RuntimeError("single-rank shard does not cover the ensemble")
+        return
+    if spec.layout == "interleaved":
+        _verify_interleaved(spec, group)
         return
     a, b = spec.bounds
     mine = torch.tensor([a, b, spec.n_rows], dtype=torch.int64)
@@ -95,6 +148,24 @@ def verify_shard_map(spec: ShardSpec, group=None) -> None:
         raise RuntimeError(f"shards cover {expect} of {spec.n_rows} rows: {rows}")
 
 
+def _verify_interleaved(spec: ShardSpec, group=None) -> None:
+    """Every rank reports (first replica, stride, count, N): rank k must start at k with stride
+    G, and the counts must add up to N."""
+    piece = spec.rows_slice
+    mine = torch.tensor([piece.start, piece.step, spec.n_local, spec.n_rows], dtype=torch.int64)
+    if dist.get_backend(group) == "nccl":
+        mine = mine.cuda()
+    everyone = [torch.empty_like(mine) for _ in range(spec.world_size)]
+    dist.all_gather(everyone, mine, group=group)
+    rows = [tuple(int(x) for x in t.tolist()) for t in everyone]
+    for r, (first, stride, count, n) in enumerate(rows):
+        if n != spec.n_rows or first != r or stride != spec.world_size \
+                or count != interleaved_count(spec.n_rows, spec.world_size, r):
+            raise RuntimeError(f"inconsistent interleaved shard map at rank {r}: {rows}")
+    if sum(row[2] for row in rows) != spec.n_rows:
+        raise RuntimeError(f"shards cover {sum(row[2] for row in rows)} of {spec.n_rows} rows: {rows}")
+
+
 class MetricGather:
     """All-gather of a per-replica fp32 metric: `(n_local,)` on each rank -> `(N,)` on all.
 
@@ -109,7 +180,7 @@ class MetricGather:
         self.spec = spec
         self.group = group
         self.device = torch.device(device)
-        self.sizes = shard_sizes(spec.n_rows, spec.world_size)
+        self.sizes = spec.sizes()
         self.block = max(self.sizes) if self.sizes else 0
         self._send = torch.zeros(self.block, dtype=torch.float32, device=self.device)
         self._recv = torch.zeros(spec.world_size * self.block, dtype=torch.float32, device=self.device)
@@ -133,7 +204,15 @@ class MetricGather:
                 dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
             else:
                 self._recv[: self.block].copy_(self._send)
-            if self._even:
+            world = self.spec.world_size
+            if self.spec.layout == "interleaved":
+                # rank r's j-th value is replica j * G + r: a transpose of the (G, block) receive buffer
+                if self._even:
+                    self._out.view(self.block, world).copy_(self._recv.view(world, self.block).t())
+                else:
+                    for r, n in enumerate(self.sizes):
+                        self._out[r::world].copy_(self._recv[r * self.block : r * self.block + n])
+            elif self._even:
                 self._out.copy_(self._recv[: self.spec.n_rows])
             else:
                 offset = 0
@@ -164,8 +243,11 @@ class _NullContext:
 
 
 def shard_state(state, spec: ShardSpec):
-    """This rank's block of a `State` that holds the whole ensemble (a view, no copy)."""
+    """This rank's replicas of a `State` that holds the whole ensemble (a view, no copy; with
+    the interleaved layout its rows are `world_size` rows apart, which the kernels serve)."""
     if state.batch_size[0] != spec.n_rows:
         raise ValueError(f"state has {state.batch_size[0]} replicas, spec says {spec.n_rows}")
-    a, b = spec.bounds
-    return state.rows(a, b)
+    if spec.layout == "contiguous":
+        a, b = spec.bounds
+        return state.rows(a, b)
+    return state[spec.rows_slice]

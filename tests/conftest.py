@@ -56,7 +56,7 @@ def cuda():
 # test cases), two launches otherwise.  These parity suites run every case through both.
 BOTH_STEP_FORMS = {"test_gpu_aten_parity", "test_gpu_layouts", "test_gpu_masking", "test_gpu_dtypes",
                    "test_gpu_from_parts", "test_gpu_golden_and_oracle", "test_gpu_frontend",
-                   "test_gpu_reference_cuda", "test_gpu_property"}
+                   "test_gpu_reference_cuda", "test_gpu_property", "test_gpu_narrow_fast"}
 
 
 def pytest_generate_tests(metafunc):

@@ -41,6 +41,10 @@ SIGNATURES = {
         [c_int, c_int, c_int, _P, _P, _P, c_int64, c_double, c_double, c_double, c_double, c_double, _P],
     ),
     "cb200_probe_powf": (c_int, [_P, _P, _P, c_int64, _P]),
+    # m second rel n step_size bc2_sqrt eps stream
+    "cb200_probe_adam_quotient": (c_int, [_P, _P, _P, c_int64, c_double, c_double, c_double, _P]),
+    # g sum rel n clr eps stream
+    "cb200_probe_adagrad_quotient": (c_int, [_P, _P, _P, c_int64, c_double, c_double, _P]),
 }
 
 

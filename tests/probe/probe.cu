@@ -195,10 +195,58 @@ int adagrad_dtype(int fuse, const AdagradProbe& a) {
     default: return 1;                                   \
   }
 
+// |q~ - q| / |q~| of the fast quotients behind the 2-byte-storage parameter updates, per
+// element (fp64 arithmetic on the two fp32 results); NaN where the row is not covered.
+__global__ void probe_adam_quotient_kernel(const float* m, const float* second, double* rel, int64_t n,
+                                           float step_size, float bc2_sqrt, float eps) {
+  AdamRowT<float> c{};
+  c.step_size = step_size;
+  c.bc2_sqrt = bc2_sqrt;
+  c.eps = eps;
+  const float inv = adam_narrow_aux(c);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float fast = adam_fast_quotient(m[i], second[i], c, inv);
+    const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(second[i]), bc2_sqrt), eps);
+    const float exact = __fdiv_rn(__fmul_rn(step_size, m[i]), denom);
+    rel[i] = fabs(static_cast<double>(fast) - static_cast<double>(exact)) / fabs(static_cast<double>(fast));
+  }
+}
+
+__global__ void probe_adagrad_quotient_kernel(const float* g, const float* sum, double* rel, int64_t n,
+                                              double clr, double eps) {
+  AdagradRow c{};
+  c.clr = clr;
+  c.eps = eps;
+  const AdagradNarrowAux aux = adagrad_narrow_aux(c);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float numerator;
+    const float fast = adagrad_fast_quotient(g[i], sum[i], aux, numerator);
+    const double denom = __dadd_rn(static_cast<double>(__fsqrt_rn(sum[i])), eps);
+    const double exact = __ddiv_rn(__dmul_rn(clr, static_cast<double>(g[i])), denom);
+    rel[i] = fabs(static_cast<double>(fast) - exact) / fabs(static_cast<double>(fast));
+  }
+}
+
 }  // namespace
 }  // namespace cb200
 
 extern "C" {
+
+int cb200_probe_adam_quotient(const float* m, const float* second, double* rel, int64_t n,
+                              double step_size, double bc2_sqrt, double eps, void* stream) {
+  cb200::probe_adam_quotient_kernel<<<cb200::grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      m, second, rel, n, static_cast<float>(step_size), static_cast<float>(bc2_sqrt), static_cast<float>(eps));
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+int cb200_probe_adagrad_quotient(const float* g, const float* sum, double* rel, int64_t n, double clr,
+                                 double eps, void* stream) {
+  cb200::probe_adagrad_quotient_kernel<<<cb200::grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, sum, rel, n, clr, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
 
 // dtype: storage type of p, g, m, v, mx (enum cb200_dtype); fuse: AdamFuse mask, 0..3.
 int cb200_probe_adam(int dtype, int fuse, int amsgrad, int adamw, int maximize, void* p,
