@@ -49,12 +49,13 @@ struct AdagradOp {
   // approximations instead of the fp64 divide -- with the exact fp64 chain for the elements it
   // cannot decide.  The accumulator is always exact.
   static constexpr bool kNarrowFast = sizeof(T) == 2;
-  using Aux = AdagradNarrowAux;
-  __device__ static __forceinline__ Aux make_aux(const Row& c) { return adagrad_narrow_aux(c); }
-  __device__ static __forceinline__ bool apply_bounds(Math (&x)[kBufs], const Row& c, const Aux& aux,
-                                                      int flags, float& lo, float& hi) {
-    adagrad_accumulate<FUSE, Math>(x[0], x[1], x[2], c, (flags & 1) != 0);   // x[1]: the decayed gradient
-    return adagrad_param_bounds(x[0], x[1], x[2], aux, lo, hi);
+  __device__ static __forceinline__ bool row_variant(const Row& c) { return c.weight_decay != 0.0; }
+  template <bool DECAY>
+  __device__ static __forceinline__ bool apply_bounds(Math (&x)[kBufs], const Row& c, int flags,
+                                                      float& lo, float& hi) {
+    // x[1] leaves as the decayed gradient
+    adagrad_accumulate<FUSE, Math, DECAY ? 1 : 0>(x[0], x[1], x[2], c, (flags & 1) != 0);
+    return adagrad_param_bounds(x[0], x[1], x[2], c, lo, hi);
   }
   __device__ static __forceinline__ void finish_exact(Math (&x)[kBufs], const Row& c) {
     x[0] = adagrad_param<Math>(x[0], x[1], x[2], c);

@@ -49,15 +49,15 @@ struct AdamOp {
   // fp16 / bf16 storage: the bounded fast form of the parameter update (rowmath.cuh), with the
   // exact chain for the elements it cannot decide.  The moments are always exact.
   static constexpr bool kNarrowFast = sizeof(T) == 2;
-  using Aux = float;   // 1 / bc2_sqrt, or NaN for a row outside the error bound's range
-  __device__ static __forceinline__ Aux make_aux(const Row& c) { return adam_narrow_aux(c); }
-  __device__ static __forceinline__ bool apply_bounds(Math (&x)[kBufs], const Row& c, Aux inv_bc2,
-                                                      int flags, float& lo, float& hi) {
+  __device__ static __forceinline__ bool row_variant(const Row& c) { return c.weight_decay != Math(0); }
+  template <bool DECAY>
+  __device__ static __forceinline__ bool apply_bounds(Math (&x)[kBufs], const Row& c, int flags,
+                                                      float& lo, float& hi) {
     Math mx = Math(0);
     if constexpr (AMSGRAD) mx = x[4];
-    adam_moments<AMSGRAD, ADAMW, FUSE, Math>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
+    adam_moments<AMSGRAD, ADAMW, FUSE, Math, DECAY ? 1 : 0>(x[0], x[1], x[2], x[3], mx, c, (flags & 1) != 0);
     if constexpr (AMSGRAD) x[4] = mx;
-    return adam_param_bounds(x[0], x[2], AMSGRAD ? mx : x[3], c, inv_bc2, lo, hi);
+    return adam_param_bounds(x[0], x[2], AMSGRAD ? mx : x[3], c, lo, hi);
   }
   __device__ static __forceinline__ void finish_exact(Math (&x)[kBufs], const Row& c) {
     x[0] = adam_param<Math>(x[0], x[2], x[AMSGRAD ? 4 : 3], c);

@@ -123,11 +123,12 @@ extern "C" int cb200_copy_rows_masked(int n_leaves, void* const* dst, const void
   size_t l2 = 0;
   if (int rc = device_info(&sm_count, &l2)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  for (int base = 0; base < n_leaves; base += kMaxLeaves) {
+  // one launch per kMaxLeaves non-empty leaves; `k` carries on where the last table ended
+  for (int k = 0; k < n_leaves;) {
     Leaves table;
     table.count = 0;
     int64_t tiles = 0;
-    for (int k = base; k < n_leaves && table.count < kMaxLeaves; ++k) {
+    for (; k < n_leaves && table.count < kMaxLeaves; ++k) {
       if (row_bytes[k] == 0) continue;
       const int j = table.count++;
       table.dst[j] = static_cast<char*>(dst[k]);

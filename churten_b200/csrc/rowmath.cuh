@@ -76,7 +76,7 @@ enum AdagradFuse : int {
 // ---------------------------------------------------------------------------
 template <class M>
 struct alignas(8 * sizeof(M)) AdamRowT {
-  M lr;
+  M inv_bc2;     // 1 / bc2_sqrt for the bounded fast form of 2-byte storage; NaN: row not covered
   M beta1;
   M beta2;
   M weight_decay;
@@ -101,7 +101,9 @@ struct alignas(32) AdagradRow {
   double clr;  // lr / (1 + (step - 1) * lr_decay), in fp64
   double weight_decay;
   double eps;
-  double pad;
+  // for the bounded fast form of 2-byte storage: float(clr) (NaN: row not covered) and float(eps)
+  float fast_clr;
+  float fast_eps;
 };
 
 using AdamRow = AdamRowT<float>;
@@ -122,7 +124,6 @@ template <class M>
 __device__ __forceinline__ AdamRowT<M> adam_row(M lr, M beta1, M beta2, M eps, M weight_decay,
                                                 M step) {
   AdamRowT<M> c;
-  c.lr = lr;
   c.beta1 = beta1;
   c.beta2 = beta2;
   c.weight_decay = weight_decay;
@@ -132,6 +133,9 @@ __device__ __forceinline__ AdamRowT<M> adam_row(M lr, M beta1, M beta2, M eps, M
   c.step_size = div_rn(lr, bc1);
   c.bc2_sqrt = sqrt_rn(bc2);
   c.lr_wd = mul_rn(lr, weight_decay);
+  // the rows the error bound of the fast form covers (see adam_param_bounds)
+  const bool covered = eps >= M(0) && eps <= M(0x1p100) && c.bc2_sqrt >= M(0x1p-40) && c.bc2_sqrt <= M(2);
+  c.inv_bc2 = covered ? div_rn(M(1), c.bc2_sqrt) : M(__int_as_float(0x7fc00000));
   return c;
 }
 
@@ -162,7 +166,11 @@ __device__ __forceinline__ AdagradRow adagrad_row(double lr, double lr_decay, do
   c.clr = __ddiv_rn(lr, denom);
   c.weight_decay = weight_decay;
   c.eps = eps;
-  c.pad = 0.0;
+  // the rows the error bound of the fast form covers (see adagrad_param_bounds)
+  const double size = fabs(c.clr);
+  const bool covered = eps >= 0.0 && eps <= 0x1p100 && size <= 0x1p100 && (size >= 0x1p-100 || c.clr == 0.0);
+  c.fast_clr = covered ? static_cast<float>(c.clr) : __int_as_float(0x7fc00000);
+  c.fast_eps = static_cast<float>(eps);
   return c;
 }
 
@@ -174,11 +182,12 @@ __device__ __forceinline__ AdagradRow adagrad_row(double lr, double lr_decay, do
 // adam_math, fused_adam_utils.cuh:55-84, in two halves: the weight decay and the moments
 // (`p` leaves as the decayed parameter), then the parameter update.  `std::max(a, b)` is
 // `(a < b) ? b : a`, which keeps a NaN already stored in max_exp_avg_sq.
-template <bool AMSGRAD, bool ADAMW, int FUSE, class M>
+// DECAY: 1 = the row has weight decay, 0 = it has none, -1 = look at the record.
+template <bool AMSGRAD, bool ADAMW, int FUSE, class M, int DECAY = -1>
 __device__ __forceinline__ void adam_moments(M& p, M g, M& m, M& v, M& mx, const AdamRowT<M>& c,
                                              bool maximize) {
   if (maximize) g = -g;
-  if (c.weight_decay != M(0)) {
+  if (DECAY == 1 || (DECAY == -1 && c.weight_decay != M(0))) {
     if (!ADAMW) {
       g = (FUSE & kAdamFuseL2) ? fma_rn(p, c.weight_decay, g) : add_rn(g, mul_rn(p, c.weight_decay));
     } else {
@@ -223,7 +232,8 @@ __device__ __forceinline__ void adam_elem(M& p, M g, M& m, M& v, M& mx, const Ad
 // the exact chain's result, bit for bit.  Otherwise (a result within ~2^-19 of a rounding
 // boundary: a few elements in 10^4), or when a precondition of the error bound fails
 // (`second` below 2^-100 but not zero, an intermediate NaN or infinity, a row whose eps or
-// bias correction is out of range), the caller runs the exact chain for that element.
+// bias correction is out of range: its record then carries NaN for 1 / bc2_sqrt, and a NaN
+// bound is never accepted), the caller runs the exact chain for that element.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float sqrt_approx(float x) {
   float y;
@@ -239,25 +249,16 @@ constexpr float kNarrowRho = 1.9073486328125e-06f;       // 2^-19
 constexpr float kNarrowTiny = 7.174648137343064e-43f;    // 2^-140: what the subnormal range can add
 __device__ __forceinline__ float quiet_nan() { return __int_as_float(0x7fc00000); }
 
-// 1 / bc2_sqrt for the fast form, or NaN for a row the error bound does not cover
-// (every bound computed from a NaN is rejected by the caller's `lo <= hi` test).
-__device__ __forceinline__ float adam_narrow_aux(const AdamRowT<float>& c) {
-  const bool covered = c.eps >= 0.0f && c.eps <= 0x1p100f && c.bc2_sqrt >= 0x1p-40f && c.bc2_sqrt <= 2.0f;
-  return covered ? __frcp_rn(c.bc2_sqrt) : quiet_nan();
-}
-
 // q~: the approximation of (step_size * m) / (sqrt(second) / bc2_sqrt + eps).
-__device__ __forceinline__ float adam_fast_quotient(float m, float second, const AdamRowT<float>& c,
-                                                    float inv_bc2) {
-  const float d = __fmaf_rn(sqrt_approx(second), inv_bc2, c.eps);
+__device__ __forceinline__ float adam_fast_quotient(float m, float second, const AdamRowT<float>& c) {
+  const float d = __fmaf_rn(sqrt_approx(second), c.inv_bc2, c.eps);
   return __fmul_rn(__fmul_rn(c.step_size, m), rcp_approx(d));
 }
 
 // Encloses adam_param(p, m, second, c) in [lo, hi]; false if `second` is outside the bound's range.
 __device__ __forceinline__ bool adam_param_bounds(float p, float m, float second,
-                                                  const AdamRowT<float>& c, float inv_bc2,
-                                                  float& lo, float& hi) {
-  const float q = adam_fast_quotient(m, second, c, inv_bc2);
+                                                  const AdamRowT<float>& c, float& lo, float& hi) {
+  const float q = adam_fast_quotient(m, second, c);
   const float delta = __fmaf_rn(fabsf(q), kNarrowRho, kNarrowTiny);
   lo = __fsub_rn(p, __fadd_rn(q, delta));
   hi = __fsub_rn(p, __fsub_rn(q, delta));
@@ -299,10 +300,10 @@ __device__ __forceinline__ void sgd_elem(M& p, M g, M& buf, const SgdRowT<M>& c,
 // adagrad_math, fused_adagrad_utils.cuh:25-48, in two halves.  The accumulator lives in the
 // math type; the hyper-parameters are doubles, so with float math the weight decay and
 // the parameter update widen to fp64 and narrow back.  `g` leaves as the decayed gradient.
-template <int FUSE, class M>
+template <int FUSE, class M, int DECAY = -1>
 __device__ __forceinline__ void adagrad_accumulate(M p, M& g, M& sum, const AdagradRow& c, bool maximize) {
   if (maximize) g = -g;
-  if (c.weight_decay != 0.0) {
+  if (DECAY == 1 || (DECAY == -1 && c.weight_decay != 0.0)) {
     const double pd = static_cast<double>(p);
     const double gd = static_cast<double>(g);
     const double t = (FUSE & kAdagradFuseWd) ? __fma_rn(pd, c.weight_decay, gd)
@@ -332,34 +333,23 @@ __device__ __forceinline__ void adagrad_elem(M& p, M g, M& sum, const AdagradRow
 // fp32 value widened: exact), rcp.approx 2^-23, the last product 2^-24: below 2^-21 < rho.
 // The exact chain rounds the fp64 difference to fp32 (a second rounding, which can move the
 // fp32 result by one unit against a direct rounding), so delta also carries 2^-22 |p|.
-struct AdagradNarrowAux {
-  float clr;  // NaN for a row the error bound does not cover
-  float eps;
-};
-__device__ __forceinline__ AdagradNarrowAux adagrad_narrow_aux(const AdagradRow& c) {
-  const double size = fabs(c.clr);
-  const bool covered = c.eps >= 0.0 && c.eps <= 0x1p100 && size <= 0x1p100 && (size >= 0x1p-100 || c.clr == 0.0);
-  AdagradNarrowAux aux;
-  aux.clr = covered ? static_cast<float>(c.clr) : quiet_nan();
-  aux.eps = static_cast<float>(c.eps);
-  return aux;
-}
 // q~: the approximation of clr * g / (sqrt(sum) + eps); `n` returns the numerator.
-__device__ __forceinline__ float adagrad_fast_quotient(float g, float sum, const AdagradNarrowAux& aux,
-                                                       float& n) {
-  n = __fmul_rn(aux.clr, g);
-  return __fmul_rn(n, rcp_approx(__fadd_rn(sqrt_approx(sum), aux.eps)));
+__device__ __forceinline__ float adagrad_fast_quotient(float g, float sum, const AdagradRow& c, float& r) {
+  r = rcp_approx(__fadd_rn(sqrt_approx(sum), c.fast_eps));
+  return __fmul_rn(__fmul_rn(c.fast_clr, g), r);
 }
 
-__device__ __forceinline__ bool adagrad_param_bounds(float p, float g, float sum, const AdagradNarrowAux& aux,
+// The numerator float(clr) * g may fall into the subnormal range, where its rounding error is
+// absolute (2^-150) rather than relative; times r it is at most 2^-149 |r|, which delta carries.
+__device__ __forceinline__ bool adagrad_param_bounds(float p, float g, float sum, const AdagradRow& c,
                                                      float& lo, float& hi) {
-  float n;
-  const float q = adagrad_fast_quotient(g, sum, aux, n);
-  const float delta = __fmaf_rn(fabsf(q), kNarrowRho, __fmaf_rn(fabsf(p), 0x1p-22f, kNarrowTiny));
+  float r;
+  const float q = adagrad_fast_quotient(g, sum, c, r);
+  const float slack = __fmaf_rn(fabsf(p), 0x1p-22f, __fmaf_rn(fabsf(r), 0x1p-148f, kNarrowTiny));
+  const float delta = __fmaf_rn(fabsf(q), kNarrowRho, slack);
   lo = __fsub_rn(p, __fadd_rn(q, delta));
   hi = __fsub_rn(p, __fsub_rn(q, delta));
-  // `sum` and the numerator in the normal range (or exactly zero)
-  return (sum >= 0x1p-100f || sum == 0.0f) && (fabsf(n) >= 0x1p-126f || n == 0.0f);
+  return sum >= 0x1p-100f || sum == 0.0f;
 }
 
 }  // namespace cb200

@@ -86,11 +86,12 @@ extern "C" int cb200_scatter_rows(float* dst, int64_t dst_row_stride, int64_t ds
   size_t l2 = 0;
   if (int rc = device_info(&sm_count, &l2)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  for (int base = 0; base < n_parts; base += kMaxParts) {
+  // one launch per kMaxParts non-empty parts; `k` carries on where the last table ended
+  for (int k = 0; k < n_parts;) {
     Parts table;
     table.count = 0;
     int64_t tiles = 0;
-    for (int k = base; k < n_parts && table.count < kMaxParts; ++k) {
+    for (; k < n_parts && table.count < kMaxParts; ++k) {
       if (part_numels[k] == 0) continue;
       const int j = table.count++;
       table.src[j] = parts[k];

@@ -123,6 +123,32 @@ inline WsView ws_view(void* workspace, int64_t n_rows) {
 }
 
 // ---------------------------------------------------------------------------
+// item -> (row slot, tile): a division by tiles_per_row in every CTA.  For numerators below 2^31
+// it is one multiply-high and one shift by constants the host prepares (Granlund-Montgomery:
+// with s = ceil(log2 d) >= 1 and m = ceil(2^(31 + s) / d) < 2^32, floor(n / d) ==
+// (n * m) >> (31 + s) for every n < 2^31), instead of the ~20 instructions of a 32-bit division.
+// ---------------------------------------------------------------------------
+struct FastDiv {
+  uint32_t divisor;
+  uint32_t magic;
+  uint32_t shift;   // s - 1, applied to the high word of the product
+};
+inline FastDiv fast_div(int64_t divisor) {
+  FastDiv f{1u, 0u, 0u};
+  if (divisor <= 1 || divisor > 0x7fffffffLL) return f;   // 1: no division; the kernels test for it
+  uint32_t s = 1;
+  while ((int64_t(1) << s) < divisor) ++s;
+  const uint64_t numerator = uint64_t(1) << (31 + s);
+  f.divisor = static_cast<uint32_t>(divisor);
+  f.magic = static_cast<uint32_t>((numerator + static_cast<uint64_t>(divisor) - 1) / static_cast<uint64_t>(divisor));
+  f.shift = s - 1;
+  return f;
+}
+__device__ __forceinline__ uint32_t fast_quotient(uint32_t n, const FastDiv& f) {
+  return f.divisor == 1u ? n : (__umulhi(n, f.magic) >> f.shift);
+}
+
+// ---------------------------------------------------------------------------
 // Buffer table passed by value to the kernels.
 // ---------------------------------------------------------------------------
 template <int NB>
@@ -276,6 +302,11 @@ struct Pack<__half> {
       out[2 * i + 1] = __high2float(h);
     }
   }
+  __device__ static __forceinline__ void unpack2(unsigned w, float& a, float& b) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    a = __low2float(h);
+    b = __high2float(h);
+  }
   // two elements rounded to storage, as one 32-bit word (the first in the low half)
   __device__ static __forceinline__ unsigned pack2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -301,6 +332,10 @@ struct Pack<__nv_bfloat16> {
       out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
+  __device__ static __forceinline__ void unpack2(unsigned w, float& a, float& b) {
+    a = __uint_as_float(w << 16);          // a bf16 is the upper half of an fp32
+    b = __uint_as_float(w & 0xffff0000u);
+  }
   __device__ static __forceinline__ unsigned pack2(float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const unsigned*>(&h);
@@ -315,73 +350,75 @@ struct Pack<__nv_bfloat16> {
 // `raw` holds the loaded accesses and leaves holding what is to be stored.
 //
 // An optimizer with 2-byte storage may offer the bounded fast form of its parameter update
-// (rowmath.cuh): Op::kNarrowFast, `Aux make_aux(Row)` once per tile,
-// `bool apply_bounds(e, row, aux, flags, lo, hi)` (state buffers updated exactly, e[0] left as
-// the input of the exact parameter update, [lo, hi] enclosing its result) and
-// `finish_exact(e, row)`.  Elements are then handled in pairs, the unit of a conversion to
+// (rowmath.cuh): Op::kNarrowFast, `bool row_variant(row)` (which of two copies of the loop
+// serves the row), `bool apply_bounds<VARIANT>(e, row, flags, lo, hi)` (state buffers updated
+// exactly, e[0] left as the input of the exact parameter update, [lo, hi] enclosing its
+// result) and `finish_exact(e, row)`.  Elements are then handled in pairs, the unit of a conversion to
 // storage: where both elements' bounds round to one storage word, that word is stored;
 // otherwise the pair takes the exact chain.
 // ---------------------------------------------------------------------------
-struct NoAux {};
 template <class Op, class = void>
-struct NarrowFast {
-  static constexpr bool value = false;
-  using Aux = NoAux;
-  __device__ static __forceinline__ Aux make_aux(const typename Op::Row&) { return Aux{}; }
-};
+struct NarrowFast : std::false_type {};
 template <class Op>
-struct NarrowFast<Op, std::enable_if_t<Op::kNarrowFast>> {
-  static constexpr bool value = true;
-  using Aux = typename Op::Aux;
-  __device__ static __forceinline__ Aux make_aux(const typename Op::Row& c) { return Op::make_aux(c); }
-};
+struct NarrowFast<Op, std::enable_if_t<Op::kNarrowFast>> : std::true_type {};
 
 template <class Op>
 __device__ __forceinline__ void update_access(uint4 (&raw)[Op::kBufs], const typename Op::Row& c,
-                                              const typename NarrowFast<Op>::Aux& aux, int flags) {
+                                              int flags) {
   constexpr int NB = Op::kBufs;
   using M = typename Op::Math;
   using P = Pack<typename Op::Storage>;
   constexpr int VEC = P::kVec;
-  M x[NB][VEC];
-#pragma unroll
-  for (int b = 0; b < NB; ++b) P::unpack(raw[b], x[b]);
   if constexpr (NarrowFast<Op>::value) {
     static_assert(VEC == 8 && (Op::kWriteMask & 1u), "2-byte storage, parameters in buffer 0");
-    unsigned word[VEC / 2];
+    // Two copies of the loop, chosen once per access by a property of the row (does it have
+    // weight decay?), so that the copy without it carries none of the decay's instructions:
+    // Adagrad's decay is fp64 arithmetic, which costs issue slots even when predicated off.
+    auto pairs = [&](auto variant) {
+      constexpr bool kVariant = decltype(variant)::value;
+      // pair by pair, so that only two elements of every buffer are live in fp32 at a time
+      unsigned out[NB][VEC / 2];
 #pragma unroll
-    for (int j = 0; j < VEC / 2; ++j) {
-      M e0[NB], e1[NB];
+      for (int j = 0; j < VEC / 2; ++j) {
+        M e0[NB], e1[NB];
 #pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        e0[b] = x[b][2 * j];
-        e1[b] = x[b][2 * j + 1];
-      }
-      float lo0, hi0, lo1, hi1;
-      bool covered = Op::apply_bounds(e0, c, aux, flags, lo0, hi0);
-      covered = Op::apply_bounds(e1, c, aux, flags, lo1, hi1) && covered;
-      unsigned w = P::pack2(lo0, lo1);
-      // `lo <= hi` is false for a NaN on either side: those take the exact chain too
-      if (!(covered && lo0 <= hi0 && lo1 <= hi1 && w == P::pack2(hi0, hi1))) {
-        Op::finish_exact(e0, c);
-        Op::finish_exact(e1, c);
-        w = P::pack2(e0[0], e1[0]);
-      }
-      word[j] = w;
+        for (int b = 0; b < NB; ++b) {
+          const unsigned w = j == 0 ? raw[b].x : j == 1 ? raw[b].y : j == 2 ? raw[b].z : raw[b].w;
+          P::unpack2(w, e0[b], e1[b]);
+        }
+        float lo0, hi0, lo1, hi1;
+        bool covered = Op::template apply_bounds<kVariant>(e0, c, flags, lo0, hi0);
+        covered = Op::template apply_bounds<kVariant>(e1, c, flags, lo1, hi1) && covered;
+        unsigned w = P::pack2(lo0, lo1);
+        // A NaN bound must not be accepted: two NaNs round to the same storage word.  delta >= 0,
+        // so lo <= hi whenever neither is a NaN, and a NaN on one side alone gives different
+        // words; what is left is a NaN on both sides of an element, which makes lo0 + lo1 a NaN.
+        const float both = __fadd_rn(lo0, lo1);
+        if (!(covered && both == both && w == P::pack2(hi0, hi1))) {
+          Op::finish_exact(e0, c);
+          Op::finish_exact(e1, c);
+          w = P::pack2(e0[0], e1[0]);
+        }
+        out[0][j] = w;
 #pragma unroll
-      for (int b = 1; b < NB; ++b) {
-        if ((Op::kWriteMask >> b) & 1) {
-          x[b][2 * j] = e0[b];
-          x[b][2 * j + 1] = e1[b];
+        for (int b = 1; b < NB; ++b) {
+          if ((Op::kWriteMask >> b) & 1) out[b][j] = P::pack2(e0[b], e1[b]);
         }
       }
-    }
-    raw[0] = make_uint4(word[0], word[1], word[2], word[3]);
 #pragma unroll
-    for (int b = 1; b < NB; ++b) {
-      if ((Op::kWriteMask >> b) & 1) raw[b] = P::pack(x[b]);
+      for (int b = 0; b < NB; ++b) {
+        if ((Op::kWriteMask >> b) & 1) raw[b] = make_uint4(out[b][0], out[b][1], out[b][2], out[b][3]);
+      }
+    };
+    if (Op::row_variant(c)) {
+      pairs(std::true_type{});
+    } else {
+      pairs(std::false_type{});
     }
   } else {
+    M x[NB][VEC];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) P::unpack(raw[b], x[b]);
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       M e[NB];
@@ -520,7 +557,7 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 template <class Op, int UNROLL, bool STREAM, class Grads, bool PACKED = false>
 __global__ void __launch_bounds__(512, UNROLL == Op::kUnroll ? Op::kMinCtas512 : 0)
 stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
-              int flags, int rows_per_cta, Grads grads) {
+              int flags, int rows_per_cta, FastDiv by_tiles, Grads grads) {
   constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
@@ -553,9 +590,9 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
       int64_t tile;
       if (total <= 0x7fffffffLL) {
         const uint32_t it = static_cast<uint32_t>(item);
-        const uint32_t tpr = static_cast<uint32_t>(tiles_per_row);
-        a = it / tpr;
-        tile = it - static_cast<uint32_t>(a) * tpr;
+        const uint32_t slot = fast_quotient(it, by_tiles);
+        a = slot;
+        tile = it - slot * by_tiles.divisor;
       } else {
         a = item / tiles_per_row;
         tile = item - a * tiles_per_row;
@@ -564,7 +601,6 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
     }
     const int64_t r = ws.ids[a];
     const Row c = rows[a];
-    const typename NarrowFast<Op>::Aux aux = NarrowFast<Op>::make_aux(c);
 
     T* base[NB];
 #pragma unroll
@@ -589,7 +625,7 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       if (e0 + u * lane_elems < row_len) {
-        update_access<Op>(raw[u], c, aux, flags);
+        update_access<Op>(raw[u], c, flags);
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
           if ((Op::kWriteMask >> b) & 1) store16<STREAM>(base[b] + u * lane_elems, raw[u][b]);
@@ -620,7 +656,7 @@ __global__ void __launch_bounds__(512)
 single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
                      typename Op::Math* __restrict__ state_steps,
                      const uint8_t* __restrict__ active_mask, int32_t* __restrict__ tickets,
-                     int64_t row_len, uint32_t tiles_per_row, int flags, int bump, Grads grads) {
+                     int64_t row_len, FastDiv by_tiles, int flags, int bump, Grads grads) {
   constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
   constexpr int NB = Op::kBufs;
   using Row = typename Op::Row;
@@ -629,7 +665,8 @@ single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
   using P = Pack<T>;
   constexpr int VEC = P::kVec;
 
-  const uint32_t r32 = blockIdx.x / tiles_per_row;
+  const uint32_t tiles_per_row = by_tiles.divisor;
+  const uint32_t r32 = fast_quotient(blockIdx.x, by_tiles);
   const uint32_t tile = blockIdx.x - r32 * tiles_per_row;
   const int64_t r = r32;
   if (active_mask[r] == 0) return;   // the same byte for the whole CTA
@@ -668,11 +705,10 @@ single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
   }
   __syncthreads();
   const Row c = row_record;
-  const typename NarrowFast<Op>::Aux aux = NarrowFast<Op>::make_aux(c);
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
     if (e0 + u * lane_elems < row_len) {
-      update_access<Op>(raw[u], c, aux, flags);
+      update_access<Op>(raw[u], c, flags);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         if ((Op::kWriteMask >> b) & 1) store16<false>(base[b] + u * lane_elems, raw[u][b]);
@@ -842,13 +878,13 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
       if (grad_parts) {
         single_launch_kernel<VecOp, VecOp::kUnroll, cb200_grad_parts>
             <<<grid, VecOp::kThreads, 0, stream>>>(bufs, hyper, state_steps, active_mask, tickets,
-                                                   row_len, static_cast<uint32_t>(tiles_per_row),
-                                                   flags, bump_steps, *grad_parts);
+                                                   row_len, fast_div(tiles_per_row), flags, bump_steps,
+                                                   *grad_parts);
       } else {
         single_launch_kernel<VecOp, VecOp::kUnroll, DenseGrads>
             <<<grid, VecOp::kThreads, 0, stream>>>(bufs, hyper, state_steps, active_mask, tickets,
-                                                   row_len, static_cast<uint32_t>(tiles_per_row),
-                                                   flags, bump_steps, DenseGrads{});
+                                                   row_len, fast_div(tiles_per_row), flags, bump_steps,
+                                                   DenseGrads{});
       }
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e, "single-launch step");
@@ -910,6 +946,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   }
   const int64_t tile = static_cast<int64_t>(threads) * per_thread * unroll;
   const int64_t tiles_per_row = (row_len + tile - 1) / tile;
+  const FastDiv by_tiles = fast_div(tiles_per_row);
   // Grid: one CTA per tile of every row that can be active.
   const int64_t grid_rows = (active_rows_hint >= 0 && active_rows_hint < n_rows)
                                 ? (active_rows_hint > 0 ? active_rows_hint : 1)
@@ -953,20 +990,20 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
   if (rows_per_cta > 1) {
     // short rows: one access per thread (unroll is 1 here), several rows per CTA
     if (grad_parts) {
-      return stream_hint ? go(stream_kernel<VecOp, 1, true, cb200_grad_parts, true>, *grad_parts)
-                         : go(stream_kernel<VecOp, 1, false, cb200_grad_parts, true>, *grad_parts);
+      return stream_hint ? go(stream_kernel<VecOp, 1, true, cb200_grad_parts, true>, by_tiles, *grad_parts)
+                         : go(stream_kernel<VecOp, 1, false, cb200_grad_parts, true>, by_tiles, *grad_parts);
     } else if (vec) {
-      return stream_hint ? go(stream_kernel<VecOp, 1, true, DenseGrads, true>, DenseGrads{})
-                         : go(stream_kernel<VecOp, 1, false, DenseGrads, true>, DenseGrads{});
+      return stream_hint ? go(stream_kernel<VecOp, 1, true, DenseGrads, true>, by_tiles, DenseGrads{})
+                         : go(stream_kernel<VecOp, 1, false, DenseGrads, true>, by_tiles, DenseGrads{});
     } else {
       return stream_hint ? go(element_kernel<ElemOp, 1, true, true>)
                          : go(element_kernel<ElemOp, 1, false, true>);
     }
   }
   if (grad_parts) {
-    CB200_PICK(CB200_GATHER, *grad_parts);
+    CB200_PICK(CB200_GATHER, by_tiles, *grad_parts);
   } else if (vec) {
-    CB200_PICK(CB200_DENSE, DenseGrads{});
+    CB200_PICK(CB200_DENSE, by_tiles, DenseGrads{});
   } else {
     CB200_PICK(CB200_ELEMENT);
   }

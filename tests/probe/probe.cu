@@ -199,14 +199,15 @@ int adagrad_dtype(int fuse, const AdagradProbe& a) {
 // element (fp64 arithmetic on the two fp32 results); NaN where the row is not covered.
 __global__ void probe_adam_quotient_kernel(const float* m, const float* second, double* rel, int64_t n,
                                            float step_size, float bc2_sqrt, float eps) {
-  AdamRowT<float> c{};
+  // the record as adam_row builds it for these three scalars (the others do not enter q)
+  AdamRowT<float> c = adam_row<float>(1.0f, 0.5f, 0.5f, eps, 0.0f, 1.0f);
   c.step_size = step_size;
   c.bc2_sqrt = bc2_sqrt;
-  c.eps = eps;
-  const float inv = adam_narrow_aux(c);
+  c.inv_bc2 = (bc2_sqrt >= 0x1p-40f && bc2_sqrt <= 2.0f && eps >= 0.0f && eps <= 0x1p100f)
+                  ? __fdiv_rn(1.0f, bc2_sqrt) : __int_as_float(0x7fc00000);
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float fast = adam_fast_quotient(m[i], second[i], c, inv);
+    const float fast = adam_fast_quotient(m[i], second[i], c);
     const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(second[i]), bc2_sqrt), eps);
     const float exact = __fdiv_rn(__fmul_rn(step_size, m[i]), denom);
     rel[i] = fabs(static_cast<double>(fast) - static_cast<double>(exact)) / fabs(static_cast<double>(fast));
@@ -215,14 +216,12 @@ __global__ void probe_adam_quotient_kernel(const float* m, const float* second, 
 
 __global__ void probe_adagrad_quotient_kernel(const float* g, const float* sum, double* rel, int64_t n,
                                               double clr, double eps) {
-  AdagradRow c{};
-  c.clr = clr;
-  c.eps = eps;
-  const AdagradNarrowAux aux = adagrad_narrow_aux(c);
+  // lr = clr with no decay at step 1: adagrad_row leaves clr as given and fills the fast fields
+  const AdagradRow c = adagrad_row<kAdagradFuseAll>(clr, 0.0, 0.0, eps, 1.0f);
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float numerator;
-    const float fast = adagrad_fast_quotient(g[i], sum[i], aux, numerator);
+    float r;
+    const float fast = adagrad_fast_quotient(g[i], sum[i], c, r);
     const double denom = __dadd_rn(static_cast<double>(__fsqrt_rn(sum[i])), eps);
     const double exact = __ddiv_rn(__dmul_rn(clr, static_cast<double>(g[i])), denom);
     rel[i] = fabs(static_cast<double>(fast) - exact) / fabs(static_cast<double>(fast));

@@ -97,6 +97,15 @@ def test_strided_rows_many_leaves_and_many_rows(cuda):
     _C.copy_rows_masked(list(zip(many_dst, many_src)), mask, cuda)
     for d, s in zip(many_dst, many_src):
         assert torch.equal(d[mask], s[mask]) and not d[~mask].any()
+    # empty leaves take no room in a launch's table: 20 leaves with data among 12 empty ones are
+    # two launches (16 + 4), each leaf copied once
+    mixed_src = [torch.randn(n, 0 if k % 8 in (1, 4, 6) else 2 + k, generator=gen, device=cuda) for k in range(32)]
+    mixed_dst = [torch.zeros_like(t) for t in mixed_src]
+    before = _C.launch_count()
+    _C.copy_rows_masked(list(zip(mixed_dst, mixed_src)), mask, cuda)
+    assert _C.launch_count() - before == 2
+    for d, s in zip(mixed_dst, mixed_src):
+        assert torch.equal(d[mask], s[mask]) and not d[~mask].any()
     # more (row, tile) pairs than the grid has CTAs: every CTA strides
     n = 300_000
     src4 = [torch.randn(n, 4, generator=gen, device=cuda) for _ in range(4)]

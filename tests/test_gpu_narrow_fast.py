@@ -199,4 +199,4 @@ def test_the_approximations_stay_inside_the_assumed_bound(cuda):
         ok = torch.isfinite(rel) & (g.abs() * clr > 2.0 ** -120)
         worst = max(worst, float(rel[ok].max()))
     print(f"worst relative error of the fast quotients: 2^{math.log2(worst):.2f}")
-    assert worst <= 2.0 ** -20.5
+    assert worst <= 2.0 ** -20.5, f"worst relative error 2^{math.log2(worst):.2f}"
