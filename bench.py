@@ -674,7 +674,15 @@ def run_ours(args, w, world, rank, local_rank):
 
     # pinned staging on the GPU's own NUMA node where the host allows it (matters once several
     # GPUs pull from the host at the same time)
-    pinned = hostmem.pinned_near(device, (pin_rows, t), state.grads.dtype)
+    if args.host_tuning:
+        # one attempt at the host leg: write-combined staging (the host only writes it) and
+        # every rank's threads on cores of their own
+        cores = sorted(os.sched_getaffinity(0))
+        share = max(1, len(cores) // world)
+        os.sched_setaffinity(0, set(cores[rank * share:(rank + 1) * share] or cores))
+        pinned = hostmem.pinned_write_combined(device, (pin_rows, t), state.grads.dtype)
+    else:
+        pinned = hostmem.pinned_near(device, (pin_rows, t), state.grads.dtype)
     pinned.copy_(torch.empty(pin_rows, t, dtype=torch.float32).normal_(0.0, 1e-3))
     steps_host = hostmem.pinned_near(device, (n_local,), state.optimizer_state["state_steps"].dtype)
     h2d = n_local * t * state.grads.element_size()
@@ -772,6 +780,7 @@ def run_ours(args, w, world, rank, local_rank):
             "e2e": {"value": job_elems * e2e_steps / (e2e_ms * 1e-3), "unit": "param-updates/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "pipelined_blocks": len(blocks), "host": hostmem.describe(device),
+                    "staging": "write-combined, rank-private cores" if args.host_tuning else "pinned",
                     "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(job_launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -978,6 +987,8 @@ def main():
     ap.add_argument("--moment-dtype", choices=("bf16", "f16"), default=None,
                     help="Adam / SGD with fp32 parameters and 2-byte state buffers (an extension; not the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--host-tuning", action="store_true",
+                    help="e2e leg: write-combined staging buffer and rank-private host cores")
     ap.add_argument("--layout", choices=("contiguous", "interleaved"), default="contiguous",
                     help="which replicas a rank owns: a contiguous block, or every world_size-th")
     ap.add_argument("--frozen-pattern", choices=("random", "clustered"), default="random",

@@ -72,6 +72,32 @@ def pinned_near(device: torch.device | int, shape, dtype=torch.float32) -> torch
     return out
 
 
+_WRITE_COMBINED = 0x04   # cudaHostAllocWriteCombined
+_wc_keepalive: list = []
+
+
+def pinned_write_combined(device: torch.device | int, shape, dtype=torch.float32) -> torch.Tensor:
+    """A pinned host tensor in write-combined memory (`cudaHostAlloc(..., cudaHostAllocWriteCombined)`
+    of the CUDA runtime PyTorch has loaded): the device reads it over PCIe without snooping the
+    CPU caches, the host should only ever WRITE it (host reads are uncached and slow).  For
+    staging buffers that the host fills and the GPU consumes.  The allocation lives until the
+    process exits."""
+    import math
+
+    n_bytes = max(1, math.prod(shape) * torch.empty((), dtype=dtype).element_size())
+    runtime = ctypes.CDLL("libcudart.so.12")
+    runtime.cudaHostAlloc.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t, ctypes.c_uint]
+    runtime.cudaHostAlloc.restype = ctypes.c_int
+    ptr = ctypes.c_void_p()
+    with torch.cuda.device(device), prefer_node_of(device):
+        status = runtime.cudaHostAlloc(ctypes.byref(ptr), n_bytes, _WRITE_COMBINED)
+    if status != 0 or not ptr.value:
+        raise RuntimeError(f"cudaHostAlloc(write-combined, {n_bytes} bytes) failed with status {status}")
+    raw = (ctypes.c_char * n_bytes).from_address(ptr.value)
+    _wc_keepalive.append(raw)
+    return torch.frombuffer(raw, dtype=dtype, count=math.prod(shape)).reshape(shape)
+
+
 def describe(device: torch.device | int) -> dict:
     """What the host says about placement (for benchmark records)."""
     nodes = None

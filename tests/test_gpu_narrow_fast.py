@@ -171,7 +171,8 @@ def test_many_ordinary_elements(ops, cuda, dtype, step_form):
 
 def test_the_approximations_stay_inside_the_assumed_bound(cuda):
     """|q~ - q| / |q~| of the fast quotients over 2^24 inputs spread over every binade the bound
-    covers: measured worst case at most 2^-20.5, half of the 2^-19 the intervals are built with."""
+    covers: the measured worst case (2^-21.4 on B200) must stay below 2^-20.5, a third of the
+    2^-19 the intervals are built with."""
     import probe
 
     lib = probe.lib()
@@ -187,8 +188,11 @@ def test_the_approximations_stay_inside_the_assumed_bound(cuda):
         assert lib.cb200_probe_adam_quotient(m.data_ptr(), second.data_ptr(), rel.data_ptr(), n, step_size, bc2, eps,
                                              stream) == 0
         torch.cuda.synchronize()
-        ok = torch.isfinite(rel)
-        assert ok.float().mean() > 0.9          # the bound covers these rows
+        # what the element-level guard admits, with a quotient in the normal range (below it the
+        # absolute term of the interval takes over)
+        q = step_size * m.double() / (second.double().sqrt() / bc2 + eps)
+        ok = torch.isfinite(rel) & (second >= 2.0 ** -100) & (q.abs() > 2.0 ** -100) & (q.abs() < 2.0 ** 100)
+        assert ok.float().mean() > 0.8          # the bound covers these rows
         worst = max(worst, float(rel[ok].max()))
     for clr, eps in [(1e-2, 1e-10), (3.3e-5, 0.0), (7.0, 1e-3), (1e-20, 1e-30)]:
         g = _wild(gen, n, cuda, -20, 60)
@@ -196,7 +200,10 @@ def test_the_approximations_stay_inside_the_assumed_bound(cuda):
         assert lib.cb200_probe_adagrad_quotient(g.data_ptr(), total.data_ptr(), rel.data_ptr(), n, clr, eps,
                                                 stream) == 0
         torch.cuda.synchronize()
-        ok = torch.isfinite(rel) & (g.abs() * clr > 2.0 ** -120)
+        q = clr * g.double() / (total.double().sqrt() + eps)
+        ok = torch.isfinite(rel) & (g.abs() * clr > 2.0 ** -120) & (total >= 2.0 ** -100) \
+            & (q.abs() > 2.0 ** -100) & (q.abs() < 2.0 ** 100)
+        assert ok.float().mean() > 0.8
         worst = max(worst, float(rel[ok].max()))
     print(f"worst relative error of the fast quotients: 2^{math.log2(worst):.2f}")
     assert worst <= 2.0 ** -20.5, f"worst relative error 2^{math.log2(worst):.2f}"

@@ -26,3 +26,15 @@ def test_pinned_near_gives_usable_pinned_memory(cuda):
     host.copy_(src, non_blocking=True)
     torch.cuda.synchronize()
     assert torch.equal(host, src.cpu())
+
+
+@pytest.mark.gpu
+def test_write_combined_staging_is_pinned_and_feeds_the_device(cuda):
+    staging = hostmem.pinned_write_combined(cuda, (5, 7), torch.float32)
+    assert staging.shape == (5, 7) and staging.is_pinned()
+    values = torch.arange(35, dtype=torch.float32).reshape(5, 7)
+    staging.copy_(values)                       # the host only writes it
+    on_device = torch.empty(5, 7, device=cuda)
+    on_device.copy_(staging, non_blocking=True)
+    torch.cuda.synchronize()
+    assert torch.equal(on_device.cpu(), values)
