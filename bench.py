@@ -723,6 +723,33 @@ def run_ours(args, w, world, rank, local_rank):
 
     # ---- correctness of this rank's block, outside every timed region ----
     parity = parity_replay(state, opt, w, device)
+
+    # ---- what the memory system gives this read/write mix with no arithmetic (rank 0, fp32) ----
+    ceiling = None
+    o = state.optimizer_state
+    written = {"adam": ["exp_avgs", "exp_avg_sqs"] + (["max_exp_avg_sqs"] if w.get("amsgrad") else []),
+               "sgd": ["momentum_buffers"] if o.get("momentum_buffers") is not None else [],
+               "adagrad": ["state_sums"]}[w["opt"]]
+    if rank == 0 and args.dtype == "f32" and not w.get("moment_dtype") and not args.apply_gradient:
+        # the state's own buffers, written ones first; their contents are spent after this
+        table = [state.flat_params, *[o[k] for k in written], state.flat_grads]
+        for _ in range(3):
+            _C.stream_ceiling(table, 1 + len(written), o["state_steps"], state.active_mask)
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        for a, b in pairs:
+            if flush_buf is not None:
+                flush_buf.zero_()
+            a.record(stream)
+            _C.stream_ceiling(table, 1 + len(written), o["state_steps"], state.active_mask)
+            b.record(stream)
+        torch.cuda.synchronize(device)
+        ceiling_ms = statistics.median(a.elapsed_time(b) for a, b in pairs)
+        ceiling = {"gbs": active_elems * bpe / (ceiling_ms * 1e-3) / 1e9, "ms": ceiling_ms,
+                   "mix": f"{len(table)} reads / {1 + len(written)} writes",
+                   "how": "cb200_stream_ceiling: the step's launcher, tiles, grid and cache hints with one add "
+                          "per element instead of the update, on the same buffers and mask, median of 10"}
+    if distributed:
+        dist.barrier()
     parity_flag = torch.tensor([1.0 if parity.get("ok", True) else 0.0, float(parity.get("rows_checked", 0))],
                                dtype=torch.float64, device=device)
 
@@ -790,6 +817,8 @@ def run_ours(args, w, world, rank, local_rank):
                          "op_ms_mean": statistics.mean(per_op_ms), "op_ms_median": statistics.median(per_op_ms),
                          "op_ms_p10": _percentile(per_op_ms, 0.1),
                          "op_ms_p90": _percentile(per_op_ms, 0.9),
+                         "pattern_ceiling": ceiling,
+                         "frac_of_pattern_ceiling": (achieved / ceiling["gbs"]) if ceiling else None,
                          "traffic": traffic,
                          "traffic_source": "ncu capture of a 64-row case of the same kernel, scaled by elements"},
             "clocks": clock_summary,

@@ -131,6 +131,8 @@ SIGNATURES = {
         [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
          c_int64, c_int64, _P, c_int, c_int, c_int, c_int64, _P],
     ),
+    # n_read n_write buffers state_steps active_mask n_rows row_len workspace workspace_bytes stream
+    "cb200_stream_ceiling": (c_int, [c_int, c_int, _P, _P, _P, c_int64, c_int64, _P, c_size_t, _P]),
     "cb200_set_launch_geometry": (c_int, [c_int, c_int, c_int]),
     "cb200_launch_count": (c_int64, []),
 }

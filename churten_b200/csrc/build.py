@@ -26,7 +26,7 @@ BUILD = CSRC / "build"
 LIB = PKG / "libchurten_b200.so"
 
 LIB_SOURCES = ["abi.cu", "adam.cu", "sgd.cu", "adagrad.cu", "adam_static.cu", "scatter.cu",
-               "rowcopy.cu", "lr_schedule.cu", "early_stop.cu", "adam_mixed.cu", "sgd_mixed.cu"]
+               "rowcopy.cu", "lr_schedule.cu", "early_stop.cu", "ceiling.cu", "adam_mixed.cu", "sgd_mixed.cu"]
 HEADERS = ["rowmath.cuh", "stream.cuh", "contraction.h", "adam_op.cuh", "sgd_op.cuh", "narrow.cuh", "../../include/churten_b200.h"]
 
 NVCC_FLAGS = [

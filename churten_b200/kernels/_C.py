@@ -591,6 +591,26 @@ def copy_rows_masked(pairs: list[tuple[torch.Tensor, torch.Tensor]], mask: torch
     _lib.check(status, "cb200_copy_rows_masked")
 
 
+def stream_ceiling(buffers: list[torch.Tensor], n_write: int, state_steps: torch.Tensor,
+                   active_mask: torch.Tensor) -> None:
+    """One launch pair of `cb200_stream_ceiling`: reads every dense fp32 `(N, T)` buffer of
+    `buffers` and writes the first `n_write` back (with their contents changed), skipping the
+    rows `active_mask` freezes.  For benchmarks: the memory system's ceiling for that mix."""
+    first = buffers[0]
+    for t in buffers:
+        if not (t.is_cuda and t.dtype is torch.float32 and t.is_contiguous() and t.shape == first.shape):
+            raise ValueError("stream_ceiling: dense fp32 CUDA buffers of one shape")
+    device = first.device
+    with torch.cuda.device(device):
+        stream = torch._C._cuda_getCurrentRawStream(device.index)
+        slot = _slot(device, stream, first.shape[0])
+        table = (ctypes.c_void_p * len(buffers))(*[t.data_ptr() for t in buffers])
+        status = _cb.cb200_stream_ceiling(len(buffers), n_write, table, state_steps.data_ptr(),
+                                          _mask(active_mask).data_ptr(), first.shape[0], first.shape[1],
+                                          slot.ws.data_ptr(), slot.ws.numel(), stream)
+    _lib.check(status, "cb200_stream_ceiling")
+
+
 def launch_count() -> int:
     """Kernels launched by the step entry points in this process."""
     return int(_cb.cb200_launch_count())

@@ -424,6 +424,19 @@ int cb200_adam_step_static_scratch(
  */
 int cb200_set_launch_geometry(int threads, int unroll, int ctas_per_sm);
 
+/*
+ * The access pattern of a step without its arithmetic: reads `n_read` dense fp32
+ * `(n_rows, row_len)` buffers and writes the first `n_write` of them back, through the
+ * launcher, tile shape, grid and cache hints of the step kernels (mixes 4/3 Adam, 5/4 Adam
+ * with AMSGrad, 3/2 SGD with momentum and Adagrad, 2/1 plain SGD).  Rows whose `active_mask`
+ * byte is 0 are skipped; `state_steps` is read, never written.  A measurement aid for
+ * benchmarks: the memory system's ceiling for that read/write mix, the denominator a step's
+ * roofline fraction should be read against.  No counterpart in the reference.
+ */
+int cb200_stream_ceiling(int n_read, int n_write, void* const* buffers, float* state_steps,
+                         const uint8_t* active_mask, int64_t n_rows, int64_t row_len,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* Number of kernels the step entry points have launched in this process. */
 int64_t cb200_launch_count(void);
 

@@ -258,3 +258,30 @@ def test_a_c_program_steps_through_the_abi(tmp_path):
     assert build.returncode == 0, build.stderr
     run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0 and run.stdout.strip() == "ok", (run.returncode, run.stdout, run.stderr)
+
+
+@pytest.mark.parametrize("n_read,n_write", [(4, 3), (5, 4), (3, 2), (2, 1)])
+def test_stream_ceiling_reads_and_writes_what_it_says(cuda, n_read, n_write):
+    """The no-arithmetic stream of the benchmarks: every written buffer gains the sum of the
+    read-only ones on active rows, frozen rows and the read-only buffers stay as they were."""
+    from churten_b200.kernels import _C
+
+    R, T = 6, 4096 + 8
+    gen = torch.Generator(device=cuda).manual_seed(4)
+    bufs = [torch.randn(R, T, device=cuda, generator=gen) for _ in range(n_read)]
+    before = [b.clone() for b in bufs]
+    steps = torch.full((R,), 7.0, device=cuda)
+    mask = torch.tensor([True, False, True, True, False, True], device=cuda)
+    _C.stream_ceiling(bufs, n_write, steps, mask)
+    torch.cuda.synchronize()
+    carried = torch.zeros(R, T, device=cuda)
+    for b in before[n_write:]:
+        carried = carried + b
+    for i in range(n_read):
+        want = before[i].clone()
+        if i < n_write:
+            want[mask] = (before[i] + carried)[mask]
+        assert torch.equal(bufs[i], want), i
+    assert steps.tolist() == [7.0] * R
+    with pytest.raises(RuntimeError, match="mix"):
+        _C.stream_ceiling(bufs[:1], 1, steps, mask)
