@@ -360,6 +360,25 @@ def cpu_baseline_in_child(args) -> dict:
         return {"value": None, "error": repr(exc)}
 
 
+def run_config(args, w, world) -> dict:
+    """The `config` object of a bench line: what was asked for, identical for both arms."""
+    n_local, t = w["rows"], w["row_len"]
+    fits_l2 = n_local * t * _bytes_per_elem(w) <= 2 * 126e6
+    if not fits_l2:
+        l2 = "inputs larger than L2 (no flush needed)"
+    elif args.no_l2_flush:
+        l2 = "working set fits in L2: not flushed (warm figure)"
+    else:
+        l2 = "working set fits in L2: 256 MiB written between timed steps, flush excluded from the time"
+    return {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local, "row_len": t,
+            "cuda_graph": bool(args.graph), "moment_dtype": w.get("moment_dtype"),
+            "apply_gradient": bool(args.apply_gradient),
+            "in_place_grads": bool(args.apply_gradient and args.in_place_grads), "l2": l2,
+            "layout": args.layout, "frozen_pattern": args.frozen_pattern,
+            "parallelism": f"replica-block x{world}, no collective on the step; "
+                           f"loss all-gather ({n_local * world * 4} B) on a side stream"}
+
+
 def _percentile(values, q):
     ordered = sorted(values)
     return ordered[min(len(ordered) - 1, max(0, int(round(q * (len(ordered) - 1)))))]
@@ -369,15 +388,15 @@ def run_reference_arm(args, w, world, rank):
     if rank != 0:
         return
     sample_rows = min(w["rows"], max(1, (1 << 27) // w["row_len"]))  # ~134 M elements per step
-    steps = min(args.steps, 20)
-    res = cpu_reference_rate(w, steps, min(args.warmup, 3), sample_rows)
+    # every step is a bounded sample of the workload (~27 ms of CPU work), so K and W are honoured
+    steps, warmup = min(args.steps, 200), min(max(args.warmup, 3), 50)
+    res = cpu_reference_rate(w, steps, warmup, sample_rows)
     line = {
         "impl": "reference", "metric": "param_updates_per_s", "value": res["value"],
-        "unit": "param-updates/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
+        "unit": "param-updates/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
         "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": w["rows"],
-                   "row_len": w["row_len"]},
+        "config": run_config(args, w, world),
         "cpu_baseline": {"value": res["value"], "unit": "param-updates/s", "cores": res["cores"],
                          "kind": res["kind"], "sample": res["sample"]},
         "e2e": {"value": res["value"], "unit": "param-updates/s", "h2d_bytes_per_step": 0,
@@ -790,20 +809,9 @@ def run_ours(args, w, world, rank, local_rank):
             "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": args.dtype, "data": "synthetic",
-            "config": {"workload": args.workload, "description": w["desc"], "rows_per_gpu": n_local,
-                       "row_len": t, "active_rows_rank0": active_rows, "cuda_graph": bool(args.graph),
-                       "moment_dtype": w.get("moment_dtype"),
-                       "apply_gradient": bool(args.apply_gradient),
-                       "in_place_grads": bool(args.apply_gradient and args.in_place_grads),
-                       "l2": "inputs larger than L2 (no flush needed)"
-                             if not fits_l2 else ("working set fits in L2: not flushed (warm figure)"
-                                                  if flush_buf is None else
-                                                  "working set fits in L2: 256 MiB written between timed steps, "
-                                                  "flush excluded from the time"),
-                       "layout": args.layout, "frozen_pattern": args.frozen_pattern,
-                       "active_rows_by_rank": rows_by_rank, "op_ms_slowest_rank": op_ms,
-                       "parallelism": f"replica-block x{world}, no collective on the step; "
-                                      f"loss all-gather ({n_local * world * 4} B) on a side stream"},
+            "config": run_config(args, w, world),
+            "run": {"active_rows_rank0": active_rows, "active_rows_by_rank": rows_by_rank,
+                    "op_ms_slowest_rank": op_ms},
             "e2e": {"value": job_elems * e2e_steps / (e2e_ms * 1e-3), "unit": "param-updates/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "pipelined_blocks": len(blocks), "host": hostmem.describe(device),
