@@ -430,11 +430,12 @@ def reference_cuda_in_child(workload: str, steps: int) -> dict:
 def parity_replay(state, opt, w, device) -> dict:
     """One extra step of the public front-end, replayed row by row with torch's own fused CUDA
     optimizer kernels: the first, middle and last active replica of this rank's block must come
-    out bit for bit, one frozen replica byte for byte.  fp32 storage only."""
+    out bit for bit, one frozen replica byte for byte.  Every storage type (torch's kernels get
+    the hyper-parameters as the storage type holds them, which is what the operators read)."""
     import torch
 
-    if w.get("dtype", "f32") != "f32" or w.get("moment_dtype"):
-        return {"skipped": "replay covers fp32 storage with fp32 state"}
+    if w.get("moment_dtype"):
+        return {"skipped": "state narrower than the parameters has no torch counterpart"}
     o = state.optimizer_state
     mask = state.active_mask
     active = mask.nonzero().flatten().tolist()
@@ -450,7 +451,7 @@ def parity_replay(state, opt, w, device) -> dict:
     opt.update(state)
     torch.cuda.synchronize(device)
     hyper = lambda key, r: float(o[key][r])
-    same = lambda a, b: bool(torch.equal(a.view(torch.int32), b.view(torch.int32)))
+    same = lambda a, b: bool(torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8)))
     bad = []
     for r in rows:
         b = before[r]
@@ -492,7 +493,7 @@ def parity_replay(state, opt, w, device) -> dict:
                                                               "adagrad": "adagrad_"}[w["opt"]]}
 
 
-def measure_small(name, args, device, peak):
+def measure_small(name, args, device, peak, dtype="f32", rows=0):
     """A few steps of another workload on this GPU (after the headline): median op time from
     CUDA events, GB/s of algorithmic bytes, clocks, and the same parity replay.
 
@@ -505,7 +506,10 @@ def measure_small(name, args, device, peak):
 
     from churten_b200.kernels import _C
 
-    w = dict(WORKLOADS[name], dtype="f32")
+    w = dict(WORKLOADS[name], dtype=dtype)
+    if rows:
+        w["rows"] = rows
+    w["row_len"] += -w["row_len"] % (16 // ELEMENT_BYTES[dtype])   # rows are padded to 16 bytes
     n, t = w["rows"], w["row_len"]
     bpe = _bytes_per_elem(w)
     seed = sorted(WORKLOADS).index(name) + 1
@@ -541,7 +545,7 @@ def measure_small(name, args, device, peak):
     med = statistics.median(ms)
     # every state of the set has the same mask fraction only in expectation: count this one's
     gbs = active * t * bpe / (med * 1e-3) / 1e9
-    out = {"description": w["desc"], "rows": n, "row_len": t, "active_rows": active, "steps": steps,
+    out = {"description": w["desc"], "dtype": dtype, "rows": n, "row_len": t, "active_rows": active, "steps": steps,
            "op_ms_median": med, "op_ms_p10": _percentile(ms, 0.1), "op_ms_p90": _percentile(ms, 0.9),
            "bytes_per_element": bpe, "gbs": gbs, "frac": gbs / peak, "frac_of_nominal_8tbs": gbs / 8000.0,
            "param_updates_per_s": active * t / (med * 1e-3), "launches_per_step": launches / steps,
@@ -840,6 +844,13 @@ def run_ours(args, w, world, rank, local_rank):
             del state, block_states, pinned, gather, loss, update
             torch.cuda.empty_cache()
             line["workloads"] = {name: measure_small(name, args, device, peak) for name in ("c1", "c2", "c3", "c4")}
+            # the 2-byte storage types the operators also dispatch (bounded fast form of the update)
+            line["storage_dtypes"] = {
+                "adam_bf16": measure_small("c5_shard", args, device, peak, dtype="bf16", rows=512),
+                "adam_f16": measure_small("c5_shard", args, device, peak, dtype="f16", rows=512),
+                "adagrad_bf16": measure_small("c4", args, device, peak, dtype="bf16"),
+                "sgd_bf16": measure_small("c3", args, device, peak, dtype="bf16"),
+            }
             torch.cuda.empty_cache()
             line["reference_cuda"] = reference_cuda_in_child(args.workload, min(args.steps, 10))
         if world == 1 and not args.no_cpu_baseline:
