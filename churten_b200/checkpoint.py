@@ -184,7 +184,7 @@ class Snapshot:
 
     # -- files ----------------------------------------------------------------------
     def to_file(self, root_dir_path, file_name: str | None = None,
-                rows: tuple[int, int] | None = None, total_rows: int | None = None) -> Path:
+                rows: tuple[int, int] | slice | None = None, total_rows: int | None = None) -> Path:
         """Write the mirror under `root_dir_path / file_name`.
 
         Alone (`rows=None`) the directory is built aside and swapped in, replacing a
@@ -192,7 +192,9 @@ class Snapshot:
         `total_rows` replicas passes `rows=(lo, hi)`: it writes its block in place;
         `meta.json` is written by the rank whose block starts at row 0.  `total_rows` is
         required with `rows`: every rank must ask for the same file size, whichever writes
-        first or last.
+        first or last.  `rows` may also be a slice with a step (`ShardSpec.rows_slice` of the
+        interleaved layout: this rank's replicas are `rows.start, rows.start + rows.step, ...`);
+        each row then lands at its own replica's offset.
         """
         target = Path(root_dir_path) / (file_name or "state_dict")
         mirror = self.mirror
@@ -204,15 +206,21 @@ class Snapshot:
         else:
             if total_rows is None:
                 raise ValueError("rows=(lo, hi) needs total_rows, the replica count of the whole ensemble")
-            lo, hi = rows
             total, out = int(total_rows), target
-            if hi - lo != n_local or not (0 <= lo <= hi <= total):
+            lo, hi, step = _row_range(rows, total)
+            if len(range(lo, hi, step)) != n_local:
                 raise ValueError(f"rows={rows} does not describe the {n_local} rows of this snapshot")
         out.mkdir(parents=True, exist_ok=True)
+        step = 1 if rows is None else step
         for name, host in mirror.items():
             data = host.reshape(-1).view(torch.uint8)
             row_bytes = data.numel() // n_local if n_local else 0
-            _pwrite(out / _file_of(name), total * row_bytes, lo * row_bytes, data)
+            if step == 1:
+                _pwrite(out / _file_of(name), total * row_bytes, lo * row_bytes, data)
+            else:   # every row at its own replica's place
+                for i, r in enumerate(range(lo, hi, step)):
+                    _pwrite(out / _file_of(name), total * row_bytes, r * row_bytes,
+                            data[i * row_bytes:(i + 1) * row_bytes])
         if lo == 0:
             meta = dict(self._meta, n_rows=total)
             meta["leaves"] = {k: dict(v, shape=[total, *v["shape"][1:]]) for k, v in meta["leaves"].items()}
@@ -229,16 +237,16 @@ class Snapshot:
 
     @classmethod
     def from_file(cls, root_dir_path, file_name: str | None = None,
-                  rows: tuple[int, int] | None = None) -> "Snapshot":
-        """Map a snapshot directory (lazily paged); `rows=(lo, hi)` maps one replica block."""
+                  rows: tuple[int, int] | slice | None = None) -> "Snapshot":
+        """Map a snapshot directory (lazily paged); `rows=(lo, hi)` maps one replica block, a
+        slice with a step every step-th replica from `rows.start` (a strided view of the map)."""
         target = Path(root_dir_path) / (file_name or "state_dict")
         meta = json.loads((target / "meta.json").read_text())
         if meta.get("format") != FORMAT:
             raise ValueError(f"{target} is not a {FORMAT} directory")
         total = meta["n_rows"]
-        lo, hi = rows if rows is not None else (0, total)
-        if not (0 <= lo <= hi <= total):
-            raise ValueError(f"rows={rows} outside the {total} replicas of {target}")
+        lo, hi, step = _row_range(rows, total) if rows is not None else (0, total, 1)
+        n_mine = len(range(lo, hi, step))
         self = cls.__new__(cls)
         self.device = torch.device("cpu")
         self._cuda = self._pinned = False
@@ -246,19 +254,19 @@ class Snapshot:
         self._mirror = {}
         for name, info in meta["leaves"].items():
             dtype = getattr(torch, info["dtype"])
-            shape = [hi - lo, *info["shape"][1:]]
+            shape = [n_mine, *info["shape"][1:]]
             per_row = 1
             for extent in shape[1:]:
                 per_row *= extent
             n_bytes = total * per_row * dtype.itemsize
-            if n_bytes == 0 or hi == lo:
+            if n_bytes == 0 or n_mine == 0:
                 self._mirror[name] = torch.empty(shape, dtype=dtype)
                 continue
             raw = torch.from_file(str(target / _file_of(name)), shared=False, size=n_bytes, dtype=torch.uint8)
-            block = raw[lo * per_row * dtype.itemsize: hi * per_row * dtype.itemsize]
-            self._mirror[name] = block.view(dtype).reshape(shape)
-        self._meta = dict(meta, n_rows=hi - lo)
-        self._meta["leaves"] = {k: dict(v, shape=[hi - lo, *v["shape"][1:]]) for k, v in meta["leaves"].items()}
+            table = raw.view(dtype).reshape(total, per_row)[lo:hi:step]
+            self._mirror[name] = table.reshape(shape)   # a view for a block, a copy for strided rows
+        self._meta = dict(meta, n_rows=n_mine)
+        self._meta["leaves"] = {k: dict(v, shape=[n_mine, *v["shape"][1:]]) for k, v in meta["leaves"].items()}
         return self
 
     def to_state(self, device: str | torch.device = "cpu") -> State:
@@ -314,6 +322,17 @@ def _describe(state: State) -> dict[str, Any]:
     }
 
 
+def _row_range(rows, total: int) -> tuple[int, int, int]:
+    """`(lo, hi)` or a slice -> `(start, stop, step)` inside `[0, total]`."""
+    if isinstance(rows, slice):
+        lo, hi, step = rows.start or 0, total if rows.stop is None else rows.stop, rows.step or 1
+    else:
+        (lo, hi), step = rows, 1
+    if step < 1 or not (0 <= lo <= max(lo, hi) <= total):
+        raise ValueError(f"rows={rows} outside the {total} replicas of the ensemble")
+    return int(lo), int(max(lo, hi)), int(step)
+
+
 def _file_of(leaf_name: str) -> str:
     return leaf_name.replace("/", ".") + ".bin"
 
@@ -341,7 +360,8 @@ class Checkpoint:
     by which time the copy has long landed, so no call waits for the device.
 
     On several ranks pass `rows=(lo, hi)` and `total_rows` (this rank's replica
-    block): every rank writes its block into the same files.
+    block; or `rows=spec.rows_slice` for the interleaved layout): every rank writes its
+    rows into the same files.
 
     Returns the `(N,)` bool mask of improved replicas, on the score's device.
     """
@@ -357,7 +377,7 @@ class Checkpoint:
         verbose: bool = True,
         deferred: bool = False,
         device_stage: bool = False,
-        rows: tuple[int, int] | None = None,
+        rows: tuple[int, int] | slice | None = None,
         total_rows: int | None = None,
     ):
         self.lower_is_better = lower_is_better

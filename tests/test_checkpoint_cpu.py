@@ -182,6 +182,28 @@ def test_a_block_write_needs_the_ensemble_size_and_never_shrinks_the_files(tmp_p
         assert torch.equal(full.mirror[name], leaf), name
 
 
+def test_interleaved_shards_write_each_row_at_its_replicas_place(tmp_path):
+    """Ranks that own every third replica write one checkpoint; it reloads whole, as contiguous
+    blocks, and as the same interleaved shards."""
+    from churten_b200.sharded import ShardSpec, shard_state
+
+    whole = make_state(n=7)
+    for rank in (2, 0, 1):
+        spec = ShardSpec(7, 3, rank, layout="interleaved")
+        Snapshot(shard_state(whole, spec).clone()).to_file(tmp_path, "dealt", rows=spec.rows_slice, total_rows=7)
+    full = Snapshot.from_file(tmp_path, "dealt")
+    for name, leaf in leaves(whole).items():
+        assert torch.equal(full.mirror[name], leaf), name
+    lo, hi = shard_bounds(7, 2, 1)
+    assert torch.equal(Snapshot.from_file(tmp_path, "dealt", rows=(lo, hi)).mirror["params"], whole.params[lo:hi])
+    spec = ShardSpec(7, 3, 1, layout="interleaved")
+    mine = Snapshot.from_file(tmp_path, "dealt", rows=spec.rows_slice)
+    assert torch.equal(mine.mirror["params"], whole.params[1::3])
+    assert mine.to_state().params.shape[0] == spec.n_local
+    with pytest.raises(ValueError):
+        Snapshot(whole.rows(0, 3)).to_file(tmp_path, "dealt", rows=slice(0, 7, 3), total_rows=6)
+
+
 def test_checkpoint_follows_the_reference_scenario(tmp_path):
     state = make_state()
     said = []
