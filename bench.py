@@ -493,6 +493,36 @@ def parity_replay(state, opt, w, device) -> dict:
                                                               "adagrad": "adagrad_"}[w["opt"]]}
 
 
+def pattern_ceiling(state, w, device, active_elems, bpe, flush=None):
+    """What the memory system gives the step's read/write mix with no arithmetic: the state's
+    own fp32 buffers through cb200_stream_ceiling (their contents are spent afterwards)."""
+    import torch
+
+    from churten_b200.kernels import _C
+
+    o = state.optimizer_state
+    written = {"adam": ["exp_avgs", "exp_avg_sqs"] + (["max_exp_avg_sqs"] if w.get("amsgrad") else []),
+               "sgd": ["momentum_buffers"] if o.get("momentum_buffers") is not None else [],
+               "adagrad": ["state_sums"]}[w["opt"]]
+    table = [state.flat_params, *[o[k] for k in written], state.flat_grads]
+    stream = torch.cuda.current_stream(device)
+    for _ in range(3):
+        _C.stream_ceiling(table, 1 + len(written), o["state_steps"], state.active_mask)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+    for a, b in pairs:
+        if flush is not None:
+            flush.zero_()
+        a.record(stream)
+        _C.stream_ceiling(table, 1 + len(written), o["state_steps"], state.active_mask)
+        b.record(stream)
+    torch.cuda.synchronize(device)
+    ms = statistics.median(a.elapsed_time(b) for a, b in pairs)
+    return {"gbs": active_elems * bpe / (ms * 1e-3) / 1e9, "ms": ms,
+            "mix": f"{len(table)} reads / {1 + len(written)} writes",
+            "how": "cb200_stream_ceiling: the step's launcher, tiles, grid and cache hints with one add "
+                   "per element instead of the update, on the same buffers and mask, median of 10"}
+
+
 def measure_small(name, args, device, peak, dtype="f32", rows=0):
     """A few steps of another workload on this GPU (after the headline): median op time from
     CUDA events, GB/s of algorithmic bytes, clocks, and the same parity replay.
@@ -591,6 +621,9 @@ def measure_small(name, args, device, peak, dtype="f32", rows=0):
         del replay
     out["clocks"] = clocks.summary()
     out["parity"] = parity_replay(state, opt, w, device)
+    if dtype == "f32" and not fits_l2:
+        out["pattern_ceiling"] = pattern_ceiling(state, w, device, active * t, bpe)
+        out["frac_of_pattern_ceiling"] = gbs / out["pattern_ceiling"]["gbs"]
     del state, states
     torch.cuda.empty_cache()
     return out
@@ -749,28 +782,8 @@ def run_ours(args, w, world, rank, local_rank):
 
     # ---- what the memory system gives this read/write mix with no arithmetic (rank 0, fp32) ----
     ceiling = None
-    o = state.optimizer_state
-    written = {"adam": ["exp_avgs", "exp_avg_sqs"] + (["max_exp_avg_sqs"] if w.get("amsgrad") else []),
-               "sgd": ["momentum_buffers"] if o.get("momentum_buffers") is not None else [],
-               "adagrad": ["state_sums"]}[w["opt"]]
     if rank == 0 and args.dtype == "f32" and not w.get("moment_dtype") and not args.apply_gradient:
-        # the state's own buffers, written ones first; their contents are spent after this
-        table = [state.flat_params, *[o[k] for k in written], state.flat_grads]
-        for _ in range(3):
-            _C.stream_ceiling(table, 1 + len(written), o["state_steps"], state.active_mask)
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
-        for a, b in pairs:
-            if flush_buf is not None:
-                flush_buf.zero_()
-            a.record(stream)
-            _C.stream_ceiling(table, 1 + len(written), o["state_steps"], state.active_mask)
-            b.record(stream)
-        torch.cuda.synchronize(device)
-        ceiling_ms = statistics.median(a.elapsed_time(b) for a, b in pairs)
-        ceiling = {"gbs": active_elems * bpe / (ceiling_ms * 1e-3) / 1e9, "ms": ceiling_ms,
-                   "mix": f"{len(table)} reads / {1 + len(written)} writes",
-                   "how": "cb200_stream_ceiling: the step's launcher, tiles, grid and cache hints with one add "
-                          "per element instead of the update, on the same buffers and mask, median of 10"}
+        ceiling = pattern_ceiling(state, w, device, active_elems, bpe, flush_buf)
     if distributed:
         dist.barrier()
     parity_flag = torch.tensor([1.0 if parity.get("ok", True) else 0.0, float(parity.get("rows_checked", 0))],
