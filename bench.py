@@ -782,7 +782,8 @@ def run_ours(args, w, world, rank, local_rank):
 
     # ---- what the memory system gives this read/write mix with no arithmetic (rank 0, fp32) ----
     ceiling = None
-    if rank == 0 and args.dtype == "f32" and not w.get("moment_dtype") and not args.apply_gradient:
+    if rank == 0 and active_elems > 0 and args.dtype == "f32" and not w.get("moment_dtype") \
+            and not args.apply_gradient:
         ceiling = pattern_ceiling(state, w, device, active_elems, bpe, flush_buf)
     if distributed:
         dist.barrier()
@@ -811,7 +812,10 @@ def run_ours(args, w, world, rank, local_rank):
 
     if rank == 0:
         peak, peak_kind = _peak_gbs()
-        achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
+        if world == 1:
+            achieved = active_elems * bpe / (statistics.mean(per_op_ms) * 1e-3) / 1e9
+        else:   # per GPU: the job's active elements over the ranks, at the slowest rank's op time
+            achieved = job_elems / world * bpe / (op_ms * 1e-3) / 1e9
         per_elem = TRAFFIC_BYTES_PER_ELEMENT.get(w["opt"] + ("_amsgrad" if w.get("amsgrad") else "") +
                                                  ("_narrow_state" if w.get("moment_dtype") else ""))
         if args.apply_gradient:
