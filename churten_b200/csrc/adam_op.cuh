@@ -28,11 +28,14 @@ struct AdamOp {
   // smaller CTAs: bf16 5.2 against 5.1 TB/s, fp64 6.7 against 6.3 TB/s.
   static constexpr int kThreads = sizeof(T) == 4 ? 256 : 128;
   static constexpr int kUnroll = 1;
-  // resident CTAs of 512 threads the register allocation must allow (launch bound)
+  // resident CTAs of kMaxThreads threads the register allocation must allow (launch bound)
   // fp32 without AMSGrad: 40 registers (45 unbounded, one 4-byte spill) for 6 resident CTAs of
   // 256 threads instead of 5: 7.84 against 7.95 ms on 1024 x 2 Mi elements; 32 registers spill
   // too much (8.1-8.4 ms), and AMSGrad's 47-54 registers do not fit 40 without a slowdown
-  static constexpr int kMinCtas512 = (sizeof(T) == 4 && !AMSGRAD) ? 3 : 0;
+  // fp16 / bf16 without AMSGrad: 40 registers for 12 resident CTAs of 128 threads (small spills):
+  // 6.71 against 6.65 TB/s; with AMSGrad the same bound loses 3 %, so it keeps 60 registers
+  static constexpr int kMaxThreads = (sizeof(T) == 2 && !AMSGRAD) ? 128 : 512;
+  static constexpr int kMinCtas = (sizeof(T) == 4 && !AMSGRAD) ? 3 : (sizeof(T) == 2 && !AMSGRAD) ? 12 : 0;
   using Row = AdamRowT<Math>;
   using Hyper = AdamHyper<Math>;
 

@@ -25,7 +25,8 @@ struct CeilingOp {
   static constexpr unsigned kWriteMask = (1u << NW) - 1u;
   static constexpr int kThreads = 256;
   static constexpr int kUnroll = 1;
-  static constexpr int kMinCtas512 = 0;
+  static constexpr int kMaxThreads = 512;
+  static constexpr int kMinCtas = 0;
   using Row = CeilingRow;
   using Hyper = CeilingHyper;
   __device__ static __forceinline__ Row make_row(const Hyper&, int, float) { return Row{}; }

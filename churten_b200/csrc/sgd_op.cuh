@@ -26,8 +26,9 @@ struct SgdOp {
   static constexpr unsigned kWriteMask = HAS_BUF ? 0x5u : 0x1u;
   static constexpr int kThreads = 256;  // measured best on B200: 6.5-6.9 TB/s with a momentum buffer
   static constexpr int kUnroll = 1;
-  // resident CTAs of 512 threads the register allocation must allow (launch bound)
-  static constexpr int kMinCtas512 = 0;  // 0: no bound beyond the thread count
+  // resident CTAs of kMaxThreads threads the register allocation must allow (launch bound)
+  static constexpr int kMaxThreads = 512;
+  static constexpr int kMinCtas = 0;  // 0: no bound beyond the thread count
   using Row = SgdRowT<Math>;
   using Hyper = SgdHyper<Math>;
 

@@ -550,12 +550,13 @@ prologue_kernel(typename Op::Hyper hyper, typename Op::Math* __restrict__ state_
 // Requires element stride 1, 16-byte aligned rows, row_len % (16 / sizeof(Storage)) == 0.
 // A 16-byte access holds kVec = 4 fp32, 8 fp16/bf16 or 2 fp64 elements.
 // ---------------------------------------------------------------------------
-// Launch bound: any CTA size up to 512 threads; at the optimizer's default tile depth also the
-// number of 512-thread CTAs its register allocation must leave room for (Op::kMinCtas512, 0 = no
+// Launch bound: any CTA size up to Op::kMaxThreads (512, or the default tile's 128 for the 2-byte
+// kernels that want a tight register bound); at the optimizer's default tile depth also the
+// number of such CTAs its register allocation must leave room for (Op::kMinCtas, 0 = no
 // request).  A request of 1 is NOT neutral: the compiler then spends registers freely (Adam: 54
 // instead of 45, 8.4 instead of 7.9 ms).
 template <class Op, int UNROLL, bool STREAM, class Grads, bool PACKED = false>
-__global__ void __launch_bounds__(512, UNROLL == Op::kUnroll ? Op::kMinCtas512 : 0)
+__global__ void __launch_bounds__(Op::kMaxThreads, UNROLL == Op::kUnroll ? Op::kMinCtas : 0)
 stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_per_row,
               int flags, int rows_per_cta, FastDiv by_tiles, Grads grads) {
   constexpr bool kGather = !std::is_same<Grads, DenseGrads>::value;
@@ -916,6 +917,7 @@ inline int run_step(const typename VecOp::Hyper& hyper, typename VecOp::Math* st
 
   const LaunchGeometry geo = geometry();
   int threads = geo.threads > 0 ? geo.threads : VecOp::kThreads;
+  if (vec && threads > VecOp::kMaxThreads) threads = VecOp::kMaxThreads;   // the kernel's launch bound
   const int64_t per_thread = vec ? kVec : 1;
   // Streaming hints once the step's traffic no longer fits in L2.
   const double footprint = static_cast<double>(n_rows) * static_cast<double>(row_len) *

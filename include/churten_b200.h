@@ -418,7 +418,8 @@ int cb200_adam_step_static_scratch(
  * and storage type (fp32: Adam and SGD 256 x 1, Adagrad 128 x 2);
  * `ctas_per_sm` > 0 runs a persistent grid of (SM count x ctas_per_sm) CTAs that
  * stride over the work, -1 restores the default of one CTA per tile.  0 keeps a
- * field as it is.  Process-wide and not synchronised: set it before launching,
+ * field as it is.  (The fp16 / bf16 Adam kernels without AMSGrad and the fp16 / bf16
+ * Adagrad kernels are compiled for at most 128 threads; a larger `threads` is clamped there.)  Process-wide and not synchronised: set it before launching,
  * not concurrently with a step.  No counterpart in the reference (fixed
  * 512-thread blocks over 65536-element chunks, cuda/consolidated.cuh:63-69).
  */
