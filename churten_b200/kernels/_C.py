@@ -335,6 +335,106 @@ class _Call:
         return params.new_zeros(()) if want_result else None
 
 
+class StepPlan:
+    """A step over one fixed set of tensors with everything that cannot change checked once.
+
+    The wrappers below validate layouts, normalise side inputs and look up scratch on every call:
+    about 18 us of Python for a step whose kernel takes 10.  For an ensemble that small the
+    front-ends (`optimizer/_fused.py`) build a plan after the first ordinary call: while the
+    same tensor objects are in place (a tensor's dtype, shape, strides and device do not change
+    under in-place writes) a call is the device guard, the stream's scratch, fresh data pointers
+    and the C call.  Only for dense buffers of the math type with conforming side inputs, and
+    only below the size at which the active-row read-back starts to matter; anything else keeps
+    the ordinary path.  `build` returns None when the tensors do not qualify.
+    """
+
+    __slots__ = ("entry", "op", "device", "index", "n_rows", "row_len", "dtype", "ordered", "layout",
+                 "tail", "stream", "slot")
+
+    @classmethod
+    def build(cls, op: str, entry, params, grads, buffers, state_steps, hypers, active_mask, tail_flags):
+        """`buffers`: the state matrices in the entry point's order (None for an absent optional
+        one); `hypers`: the `(N,)` vectors in its order; `tail_flags`: the ints that follow
+        `strides` up to (not including) the call flags."""
+        if params.dim() != 2 or params.dtype not in _DTYPES or not params.is_cuda:
+            return None
+        code, math = _DTYPES[params.dtype]
+        if params.dtype is not math:           # 2-byte storage reads its side inputs through a cast
+            return None
+        n_rows, row_len = params.shape
+        if n_rows * row_len >= _HINT_MIN_ELEMENTS or n_rows == 0 or row_len == 0:
+            return None
+        device = params.device
+        for t in (params, grads, *[b for b in buffers if b is not None]):
+            if not (isinstance(t, torch.Tensor) and type(t) is torch.Tensor and t.dtype is params.dtype
+                    and t.device == device and t.shape == params.shape and t.is_contiguous()):
+                return None
+        for t in (state_steps, *hypers):
+            if not (type(t) is torch.Tensor and t.dtype is math and t.device == device and t.dim() == 1
+                    and t.numel() == n_rows and t.is_contiguous()):
+                return None
+        if not (type(active_mask) is torch.Tensor and active_mask.dtype is torch.bool and active_mask.device == device
+                and active_mask.dim() == 1 and active_mask.numel() == n_rows and active_mask.is_contiguous()):
+            return None
+        self = cls()
+        self.entry, self.op, self.device, self.index = entry, op, device, device.index
+        self.n_rows, self.row_len, self.dtype = n_rows, row_len, code
+        # argument order of the C entry points: params, grads, state buffers, steps, hypers, mask
+        self.ordered = (params, grads, *buffers, state_steps, *hypers, active_mask)
+        self.layout = (n_rows, row_len, None)
+        self.tail = tuple(int(f) for f in tail_flags)
+        self.stream = self.slot = None
+        return self
+
+    def run(self) -> None:
+        index = self.index
+        guard = None
+        if torch.cuda.current_device() != index:
+            guard = torch.cuda.device(self.device)
+            guard.__enter__()
+        try:
+            stream = torch._C._cuda_getCurrentRawStream(index)
+            if stream != self.stream:
+                self.slot, self.stream = _slot(self.device, stream, self.n_rows), stream
+            ws = self.slot.ws
+            hint = _capture_hint if _capture_hint is not None else -1
+            status = self.entry(
+                self.dtype, *[t.data_ptr() if t is not None else None for t in self.ordered],
+                *self.layout, *self.tail, _lib.WORKSPACE_PREPARED if _single_launch else 0, hint,
+                ws.data_ptr(), ws.numel(), stream)
+        finally:
+            if guard is not None:
+                guard.__exit__(None, None, None)
+        if status:
+            _lib.check(status, self.op)
+
+
+def adam_plan(params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, state_steps, lr, beta1, beta2, eps,
+              weight_decay, active_mask, amsgrad, maximize, decoupled_weight_decay):
+    if amsgrad and max_exp_avg_sqs is None:
+        return None
+    return StepPlan.build("torchstrap::adam_step_", _cb.cb200_adam_step, params, grads,
+                          (exp_avgs, exp_avg_sqs, max_exp_avg_sqs if amsgrad else None), state_steps,
+                          (lr, beta1, beta2, eps, weight_decay), active_mask,
+                          (amsgrad, maximize, decoupled_weight_decay))
+
+
+def sgd_plan(params, grads, momentum_buffers, state_steps, lr, momentum, dampening, weight_decay, active_mask,
+             nesterov, maximize):
+    if nesterov and momentum_buffers is None:
+        return None
+    plan = StepPlan.build("torchstrap::sgd_step_", _cb.cb200_sgd_step, params, grads, (momentum_buffers,),
+                          state_steps, (lr, momentum, dampening, weight_decay), active_mask, (nesterov, maximize))
+    if plan is not None:   # cb200_sgd_step takes the per-row nesterov vector between the mask and the sizes
+        plan.layout = (None, plan.n_rows, plan.row_len, None)
+    return plan
+
+
+def adagrad_plan(params, grads, state_sums, state_steps, lr, lr_decay, weight_decay, eps, active_mask, maximize):
+    return StepPlan.build("torchstrap::adagrad_step_", _cb.cb200_adagrad_step, params, grads, (state_sums,),
+                          state_steps, (lr, lr_decay, weight_decay, eps), active_mask, (maximize,))
+
+
 def adam_step_cuda(
     params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, state_steps,
     lr, beta1, beta2, eps, weight_decay, active_mask,

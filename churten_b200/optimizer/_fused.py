@@ -30,6 +30,7 @@ class FusedSpec:
     flags: tuple[str, ...]             # static flags, in the operator's keyword order
     mixed: Callable | None = None      # the step for fp32 params with fp16 / bf16 state buffers
     mixed_takes_parts: bool = False    # ... and whether it can read the gradients from their parts
+    plan: Callable | None = None       # builds a `StepPlan` for small ensembles (kernels/_C.py)
 
 
 def populate(spec: FusedSpec, state: State, given: dict[str, Any], buffers: tuple[str, ...],
@@ -56,6 +57,15 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None,
     dispatcher-free call, then optionally over the column range `columns` of every buffer
     (`steps_bumped`: an earlier range of the same step has advanced the clocks)."""
     opt = state.optimizer_state
+    plain = grads is None and columns is None and not steps_bumped
+    if plain:
+        # small ensembles: the call plan of the previous step, while the same tensors are in place
+        cached = state.__dict__.get("_step_plan")
+        if cached is not None and cached[0] is spec and cached[1] == opt.structure_version \
+                and cached[2] == defaults and not state.params.requires_grad \
+                and not torch._C._are_functorch_transforms_active() and not torch.compiler.is_compiling():
+            cached[3].run()
+            return state
     flags = {name: bool(opt.get(name, defaults[name])) for name in spec.flags}
     window = (lambda t: t) if columns is None else (lambda t: t[:, columns[0]:columns[1]])
     buffers = []
@@ -87,6 +97,11 @@ def step(spec: FusedSpec, state: State, defaults: dict[str, Any], grads=None,
                 spec.direct(*args, **flags, **extra)
         else:
             spec.direct(*args, **flags, **extra)
+            if plain and spec.plan is not None and not params.requires_grad:
+                # this call went through every check: later steps over the same tensors skip them
+                plan = spec.plan(*args, *[flags[name] for name in spec.flags])
+                object.__setattr__(state, "_step_plan",
+                                   None if plan is None else (spec, opt.structure_version, dict(defaults), plan))
     else:
         spec.op(*args, **flags)
     return state

@@ -15,6 +15,7 @@ __all__ = ["Adagrad", "adagrad_step_"]
 _SPEC = _fused.FusedSpec(
     op=adagrad_step_,
     direct=_C.adagrad_step_cuda,
+    plan=_C.adagrad_plan,
     flag_defaults=dict(maximize=False),
     hypers=("lr", "lr_decay", "weight_decay", "eps"),
     buffers=("state_sums",),

@@ -16,6 +16,7 @@ __all__ = ["Adam", "adam_step_"]
 _SPEC = _fused.FusedSpec(
     op=adam_step_,
     direct=_C.adam_step_cuda,
+    plan=_C.adam_plan,
     mixed=_C.adam_step_mixed_cuda,
     mixed_takes_parts=True,
     flag_defaults=dict(amsgrad=False, maximize=False, decoupled_weight_decay=True),

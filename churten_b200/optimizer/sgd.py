@@ -15,6 +15,7 @@ __all__ = ["SGD", "sgd_step_"]
 _SPEC = _fused.FusedSpec(
     op=sgd_step_,
     direct=_C.sgd_step_cuda,
+    plan=_C.sgd_plan,
     mixed=_C.sgd_step_mixed_cuda,
     mixed_takes_parts=True,
     flag_defaults=dict(nesterov=False, maximize=False),

@@ -131,12 +131,16 @@ class OptimizerState(Mapping):
     def __init__(self, entries: dict[str, Any] | None = None):
         self._entries: dict[str, Any] = dict(entries or {})
         self._meta: set[str] = set()
+        # bumped whenever a key is (re)bound -- never by in-place writes to a tensor: lets the
+        # optimizers keep a per-state call plan for as long as the same tensors are in place
+        self.structure_version = 0
 
     def __getitem__(self, key: str) -> Any:
         return self._entries[key]
 
     def __setitem__(self, key: str, value: Any) -> None:
         self._entries[key] = value
+        self.structure_version += 1
 
     def get(self, key: str, default: Any = None) -> Any:
         # Mapping.get goes through __getitem__ and an exception for a missing key; this is
@@ -155,6 +159,7 @@ class OptimizerState(Mapping):
     def set_meta(self, key: str, value: Any) -> None:
         self._entries[key] = value
         self._meta.add(key)
+        self.structure_version += 1
 
     def is_meta(self, key: str) -> bool:
         return key in self._meta
