@@ -645,10 +645,10 @@ stream_kernel(Bufs<Op::kBufs> bufs, WsView ws, int64_t row_len, int64_t tiles_pe
 // (frozen: exit), thread 0 reads the row's step counter, adds the 1 and builds the row
 // record in shared memory -- the same make_row() the prologue runs, so the record is the
 // same bits -- while the other threads already have the tile's loads in flight.  After the
-// update thread 0 draws a ticket from the row's counter; the CTA that draws the row's last
-// ticket stores the advanced step counter and puts the ticket counter back to zero.  Every
-// CTA of the row has read the old step before it drew its ticket, so the single writer
-// cannot be seen too early; nothing waits or spins.  The counters must be zero when the
+// reading the step, thread 0 draws a ticket from the row's counter; the CTA that draws the row's
+// last ticket stores the advanced step counter, at its end, and puts the ticket counter back
+// to zero.  Every CTA of the row has read the old step before it drew its ticket, so the single
+// writer cannot be seen too early; nothing waits or spins.  The counters must be zero when the
 // launch starts: the caller says so (CB200_WORKSPACE_PREPARED) and each launch leaves them
 // zero.  Same element functions, same tile shape, same results as the two-launch path.
 // ---------------------------------------------------------------------------
@@ -673,12 +673,18 @@ single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
   if (active_mask[r] == 0) return;   // the same byte for the whole CTA
 
   __shared__ Row row_record;
-  __shared__ M row_step;
+  M step = M(0);
+  int ticket = -1;
   if (threadIdx.x == 0) {
-    M step = state_steps[r];
+    step = state_steps[r];
     if (bump) step = add_rn(step, M(1));
-    row_step = step;
     row_record = Op::make_row(hyper, static_cast<int>(r), step);
+    if (bump) {
+      // The ticket is drawn as soon as this CTA has read the old counter (the fence orders the
+      // two); its value is not needed before the end, so the round trip overlaps the tile's work.
+      __threadfence();
+      ticket = atomicAdd(&tickets[r], 1);
+    }
   }
 
   const int64_t lane_elems = static_cast<int64_t>(blockDim.x) * VEC;
@@ -716,13 +722,9 @@ single_launch_kernel(Bufs<Op::kBufs> bufs, typename Op::Hyper hyper,
       }
     }
   }
-  if (bump && threadIdx.x == 0) {
-    __threadfence();   // this CTA's read of the old counter is done before its ticket shows
-    const uint32_t ticket = static_cast<uint32_t>(atomicAdd(&tickets[r], 1));
-    if (ticket == tiles_per_row - 1) {
-      tickets[r] = 0;
-      state_steps[r] = row_step;
-    }
+  if (ticket == static_cast<int>(tiles_per_row) - 1) {   // thread 0 of the row's last CTA to arrive
+    tickets[r] = 0;
+    state_steps[r] = step;
   }
 }
 
