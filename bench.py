@@ -780,6 +780,34 @@ def run_ours(args, w, world, rank, local_rank):
     # ---- correctness of this rank's block, outside every timed region ----
     parity = parity_replay(state, opt, w, device)
 
+    # ---- the allocation-free entry point on the same state (same kernels, scratch inside the library) ----
+    static_scratch = None
+    if world == 1 and w["opt"] == "adam" and args.dtype == "f32" and not w.get("moment_dtype") \
+            and not args.apply_gradient and n_local <= 16384:
+        import ctypes
+
+        from churten_b200 import _lib
+
+        o = state.optimizer_state
+        ptr = lambda x: ctypes.c_void_p(x.data_ptr()) if x is not None else None
+        call_args = (ptr(state.flat_params), ptr(state.flat_grads), ptr(o["exp_avgs"]), ptr(o["exp_avg_sqs"]),
+                     ptr(o.get("max_exp_avg_sqs")), ptr(o["state_steps"]), ptr(o["lr"]), ptr(o["beta1"]),
+                     ptr(o["beta2"]), ptr(o["eps"]), ptr(o["weight_decay"]), ptr(state.active_mask), n_local, t,
+                     None, int(bool(w.get("amsgrad"))), 0, int(bool(o.get("decoupled_weight_decay", True))),
+                     active_rows, ctypes.c_void_p(stream.cuda_stream))
+        entry = _lib.lib().cb200_adam_step_static_scratch
+        for _ in range(2):
+            _lib.check(entry(*call_args), "cb200_adam_step_static_scratch")
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+        for a, b in pairs:
+            a.record(stream)
+            _lib.check(entry(*call_args), "cb200_adam_step_static_scratch")
+            b.record(stream)
+        torch.cuda.synchronize(device)
+        static_ms = statistics.median(a.elapsed_time(b) for a, b in pairs)
+        static_scratch = {"entry": "cb200_adam_step_static_scratch", "op_ms_median": static_ms,
+                          "gbs": active_elems * bpe / (static_ms * 1e-3) / 1e9, "steps": 5}
+
     # ---- what the memory system gives this read/write mix with no arithmetic (rank 0, fp32) ----
     ceiling = None
     if rank == 0 and active_elems > 0 and args.dtype == "f32" and not w.get("moment_dtype") \
@@ -853,6 +881,8 @@ def run_ours(args, w, world, rank, local_rank):
             "clocks": clock_summary,
             "parity": parity,
         }
+        if static_scratch is not None:
+            line["static_scratch"] = static_scratch
         default_line = (world == 1 and args.workload == "c5_shard" and not args.rows and not args.row_len
                         and args.dtype == "f32" and not args.moment_dtype and not args.apply_gradient
                         and not args.graph and args.frozen_pattern == "random")
