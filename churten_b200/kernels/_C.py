@@ -349,7 +349,7 @@ class StepPlan:
     """
 
     __slots__ = ("entry", "op", "device", "index", "n_rows", "row_len", "dtype", "ordered", "layout",
-                 "tail", "stream", "slot")
+                 "tail", "stream", "slot", "parts")
 
     @classmethod
     def build(cls, op: str, entry, params, grads, buffers, state_steps, hypers, active_mask, tail_flags):
@@ -383,10 +383,41 @@ class StepPlan:
         self.ordered = (params, grads, *buffers, state_steps, *hypers, active_mask)
         self.layout = (n_rows, row_len, None)
         self.tail = tuple(int(f) for f in tail_flags)
-        self.stream = self.slot = None
+        self.stream = self.slot = self.parts = None
         return self
 
-    def run(self) -> None:
+    def read_gradients_from(self, table, names: list[tuple[str, tuple, int]], all_names: tuple[str, ...]) -> None:
+        """Turn this plan into one for the `*_from_parts` entry point of the same optimizer:
+        `table` (a `GradPartsTable`) replaces the gradient matrix; `names[k]` = (name, shape,
+        position in the table) of every non-empty parameter tensor, `all_names` every name the
+        gradient mapping must hold.  `run_parts` then only refreshes the table's pointers."""
+        name = self.op.rsplit("::", 1)[1].rstrip("_")          # "adam_step"
+        self.entry = getattr(_cb, "cb200_" + name + "_from_parts")
+        self.ordered = (self.ordered[0], None, *self.ordered[2:])
+        self.parts = (table, ctypes.byref(table), names, all_names, self.ordered[0].dtype)
+
+    def run_parts(self, grads) -> bool:
+        """The step with `grads` (name -> dense `(N, *shape)` tensor) read in place; False, having
+        done nothing, when a gradient does not look like the ones the plan was built for."""
+        table, ref, names, all_names, dtype = self.parts
+        if len(grads) != len(all_names):
+            return False
+        index, pointers = self.index, table.ptr
+        try:
+            for name, shape, k in names:
+                t = grads[name]
+                if t.shape != shape or t.dtype is not dtype or t.get_device() != index or not t.is_contiguous():
+                    return False
+                pointers[k] = t.data_ptr()
+            for name in all_names:
+                if name not in grads:
+                    return False
+        except (KeyError, AttributeError):
+            return False
+        self.run(ref)
+        return True
+
+    def run(self, grads_argument=None) -> None:
         index = self.index
         guard = None
         if torch.cuda.current_device() != index:
@@ -398,10 +429,12 @@ class StepPlan:
                 self.slot, self.stream = _slot(self.device, stream, self.n_rows), stream
             ws = self.slot.ws
             hint = _capture_hint if _capture_hint is not None else -1
+            pointers = [t.data_ptr() if t is not None else None for t in self.ordered]
+            if grads_argument is not None:
+                pointers[1] = grads_argument      # a cb200_grad_parts* instead of the gradient matrix
             status = self.entry(
-                self.dtype, *[t.data_ptr() if t is not None else None for t in self.ordered],
-                *self.layout, *self.tail, _lib.WORKSPACE_PREPARED if _single_launch else 0, hint,
-                ws.data_ptr(), ws.numel(), stream)
+                self.dtype, *pointers, *self.layout, *self.tail,
+                _lib.WORKSPACE_PREPARED if _single_launch else 0, hint, ws.data_ptr(), ws.numel(), stream)
         finally:
             if guard is not None:
                 guard.__exit__(None, None, None)
@@ -642,6 +675,50 @@ def scatter_rows(dst: torch.Tensor, parts: list[tuple[torch.Tensor, int, int]]) 
         if guard is not None:
             guard.__exit__(None, None, None)
     _lib.check(status, "cb200_scatter_rows")
+
+
+class ScatterPlan:
+    """`scatter_rows` over gradients of fixed names and shapes with the tables built once: a call
+    checks that every gradient still looks the same, refreshes the pointers and launches."""
+
+    __slots__ = ("dst", "index", "device", "names", "count", "ptrs", "offsets", "numels")
+
+    def __init__(self, dst: torch.Tensor, named_parts: list[tuple[str, torch.Tensor, int, int]]):
+        k = len(named_parts)
+        self.dst, self.device, self.index, self.count = dst, dst.device, dst.device.index, k
+        self.names = [(name, t.shape, i) for i, (name, t, _, _) in enumerate(named_parts)]
+        self.ptrs = (ctypes.c_void_p * k)()
+        self.offsets = (ctypes.c_int64 * k)(*[p[2] for p in named_parts])
+        self.numels = (ctypes.c_int64 * k)(*[p[3] for p in named_parts])
+
+    def run(self, grads) -> bool:
+        if len(grads) != self.count:
+            return False
+        index, ptrs = self.index, self.ptrs
+        try:
+            for name, shape, i in self.names:
+                t = grads[name]
+                if t.shape != shape or t.dtype is not torch.float32 or t.get_device() != index \
+                        or not t.is_contiguous():
+                    return False
+                ptrs[i] = t.data_ptr()
+        except (KeyError, AttributeError):
+            return False
+        dst = self.dst
+        guard = None
+        if torch.cuda.current_device() != index:
+            guard = torch.cuda.device(self.device)
+            guard.__enter__()
+        try:
+            status = _cb.cb200_scatter_rows(
+                dst.data_ptr(), dst.stride(0), dst.shape[1], dst.shape[0], self.count, ptrs, self.offsets,
+                self.numels, None, torch._C._cuda_getCurrentRawStream(index))
+        finally:
+            if guard is not None:
+                guard.__exit__(None, None, None)
+        if status:
+            _lib.check(status, "cb200_scatter_rows")
+        return True
 
 
 def copy_rows_masked(pairs: list[tuple[torch.Tensor, torch.Tensor]], mask: torch.Tensor | None,

@@ -148,6 +148,13 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     (name -> `(N, *shape)`), leaving `state.grads` untouched.  Returns False, having done
     nothing, when that is not possible here: the caller then scatters and steps."""
     params = state.flat_params
+    opt = state.optimizer_state
+    # small ensembles: the plan of an earlier step over gradients of the same shapes
+    cached = state.__dict__.get("_parts_plan")
+    if cached is not None and cached[0] is spec and cached[1] == opt.structure_version \
+            and not params.requires_grad and not torch._C._are_functorch_transforms_active() \
+            and not torch.compiler.is_compiling() and cached[2].run_parts(grads):
+        return True
     if not params.is_cuda or not params.is_contiguous():
         return False
     windows = state._windows
@@ -186,7 +193,30 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
             return False
         for i, (columns, parts) in enumerate(ranges):
             step(spec, state, spec.flag_defaults, grads=parts, columns=columns, steps_bumped=i > 0)
+    _remember_parts_plan(spec, state, grads, ranges)
     return True
+
+
+def _remember_parts_plan(spec: FusedSpec, state: State, grads, ranges) -> None:
+    """After an ordinary in-place step of a small ensemble: keep what later steps over gradients
+    of the same shapes can reuse (one table, dense gradients, state of the parameters' type)."""
+    plan = None
+    params, opt = state.flat_params, state.optimizer_state
+    if spec.plan is not None and len(ranges) == 1 and not params.requires_grad \
+            and all(isinstance(g, torch.Tensor) and type(g) is torch.Tensor and g.is_contiguous()
+                    for g in grads.values()):
+        flags = {name: bool(opt.get(name, spec.flag_defaults[name])) for name in spec.flags}
+        buffers = [opt.get(name) for name in spec.buffers]
+        if all(b is None or b.dtype is params.dtype for b in buffers):
+            plan = spec.plan(_as_2d(params), _as_2d(params), *[_as_2d(b) if b is not None else None for b in buffers],
+                             _as_1d(opt["state_steps"]), *[_as_1d(opt[name]) for name in spec.hypers],
+                             _as_1d(state.active_mask), *[flags[name] for name in spec.flags])
+        if plan is not None:
+            table = ranges[0][1].table
+            order = sorted((offset, name) for name, (offset, numel) in state._windows.items() if numel > 0)
+            names = [(name, grads[name].shape, k) for k, (_, name) in enumerate(order)]
+            plan.read_gradients_from(table, names, tuple(state._windows))
+    object.__setattr__(state, "_parts_plan", None if plan is None else (spec, opt.structure_version, plan))
 
 
 def any_nonzero(value: float | torch.Tensor) -> bool:

@@ -187,11 +187,12 @@ class _GradViews:
     an aliased view, which is built only when it is needed.
     """
 
-    def __init__(self, grads: torch.Tensor, meta: list[tuple], windows: dict[str, tuple[int, int]]):
+    def __init__(self, grads: torch.Tensor, meta: list[tuple], windows: dict[str, tuple[int, int]], owner=None):
         self._grads = grads
         self._meta = meta
         self._windows = windows
         self._views: dict[str, torch.Tensor] | None = None
+        self._owner = owner     # the State: it keeps the scatter's tables from one step to the next
 
     def _view(self, name: str) -> torch.Tensor:
         if self._views is None:
@@ -201,21 +202,28 @@ class _GradViews:
     def update_(self, grads: Mapping[str, torch.Tensor]) -> "_GradViews":
         dst = self._grads
         rest = grads
+        owner = self._owner
+        plan = owner.__dict__.get("_scatter_plan") if owner is not None else None
+        if plan is not None and not torch._C._are_functorch_transforms_active() and plan.run(grads):
+            return self                                 # same names and shapes as last time
         if dst.is_cuda and dst.dtype is torch.float32 and len(grads) > 1:
             n, index = dst.shape[0], dst.get_device()
-            fused, rest = [], {}
+            fused, rest, named = [], {}, []
             for name, value in grads.items():
                 window = self._windows.get(name)
                 if (window is not None and value.is_cuda and value.dtype is torch.float32
                         and value.is_contiguous() and value.numel() == n * window[1]
                         and value.get_device() == index):
                     fused.append((value, window[0], window[1]))
+                    named.append((name, value, window[0], window[1]))
                 else:
                     rest[name] = value
             if len(fused) > 1:
-                from churten_b200.kernels._C import scatter_rows
+                from churten_b200.kernels._C import ScatterPlan, scatter_rows
 
                 scatter_rows(dst, fused)
+                if owner is not None and not rest and len(fused) <= 64 and type(dst) is torch.Tensor:
+                    object.__setattr__(owner, "_scatter_plan", ScatterPlan(dst, named))
             else:
                 rest = grads
         for name, value in rest.items():
@@ -314,7 +322,7 @@ class State:
 
     @property
     def _consolidated_grads(self) -> _GradViews:
-        return _GradViews(self.grads, self.param_meta, self._windows)
+        return _GradViews(self.grads, self.param_meta, self._windows, owner=self)
 
     # -- optimizer state ------------------------------------------------------------
     def like_tensor(self, value: Any = None, per_param: bool = False,

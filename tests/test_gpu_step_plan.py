@@ -96,3 +96,76 @@ def test_large_or_unusual_states_are_not_planned(cuda):
     SGD.update(half16)
     assert half16.__dict__.get("_step_plan") is None       # 2-byte storage reads side inputs through a cast
     assert half is not None
+
+
+@pytest.mark.parametrize("name,hypers", [("Adam", dict(lr=1e-2, amsgrad=True)), ("SGD", dict(lr=1e-2, momentum=0.9)),
+                                          ("Adagrad", dict(lr=1e-2, initial_accumulator_value=0.1))])
+def test_planned_in_place_gradients_equal_the_scatter_path(cuda, name, hypers):
+    """`apply_gradient(..., materialize=False)` over fresh gradient tensors of the same shapes every
+    step: after the first step a plan refreshes the table's pointers only.  Same bits as scatter +
+    step; a gradient that no longer looks the same falls back without being missed."""
+    import churten_b200.optimizer as O
+    from churten_b200.kernels import _C
+
+    opt = getattr(O, name)
+    planned, scattered = _state(cuda, opt, **hypers), _state(cuda, opt, **hypers)
+    gen = torch.Generator(device=cuda).manual_seed(2)
+
+    def fresh():
+        return {n: torch.randn(shape, device=cuda, generator=gen) for n, shape, _, _ in planned.param_meta}
+
+    for it in range(6):
+        grads = fresh()
+        mask = torch.rand(5, device=cuda, generator=gen) < 0.8
+        for state in (planned, scattered):
+            state.active_mask.copy_(mask)
+        before = _C.launch_count()
+        opt.apply_gradient(planned, grads, materialize=False)
+        assert _C.launch_count() - before == 1                    # one launch: gathered, single-launch form
+        opt.apply_gradient(scattered, {k: v.clone() for k, v in grads.items()})
+        if it >= 1:
+            assert planned.__dict__.get("_parts_plan") is not None
+    # a gradient of another dtype, a non-dense one and a missing one: each takes an ordinary path
+    odd = fresh()
+    first = next(iter(odd))
+    strided = odd[first].transpose(-1, -2).contiguous().transpose(-1, -2)     # same shape, rows not dense
+    assert strided.shape == odd[first].shape and not strided.is_contiguous()
+    for variant in ({**odd, first: odd[first].double()}, {**odd, first: strided},
+                    {k: v for k, v in odd.items() if k != first}):
+        for state in (planned, scattered):
+            dense = {k: v.float().contiguous() for k, v in variant.items()}
+            opt.apply_gradient(state, variant if state is planned else dense, materialize=state is not planned)
+    torch.cuda.synchronize()
+    assert_bits_equal("params", planned.params, scattered.params)
+    for key, value in scattered.optimizer_state.tensors().items():
+        assert_bits_equal(key, planned.optimizer_state[key], value)
+
+
+def test_planned_scatter_equals_per_tensor_copies(cuda):
+    """`apply_gradient(state, grads)` (scatter + step): from the second step on the scatter's tables
+    are reused; `state.grads` and the step's results equal per-tensor copies + the ordinary step."""
+    from churten_b200.kernels import _C
+    from churten_b200.optimizer import Adam
+
+    planned, plain = _state(cuda, Adam, lr=1e-2), _state(cuda, Adam, lr=1e-2)
+    gen = torch.Generator(device=cuda).manual_seed(4)
+    for it in range(5):
+        grads = {n: torch.randn(shape, device=cuda, generator=gen) for n, shape, _, _ in planned.param_meta}
+        before = _C.launch_count()
+        Adam.apply_gradient(planned, grads)
+        assert _C.launch_count() - before == 2                          # scatter + single-launch step
+        for name, (first, count) in plain._windows.items():            # the reference's procedure
+            plain.grads[:, first: first + count].copy_(grads[name].reshape(5, -1))
+        object.__setattr__(plain, "_step_plan", None)
+        Adam.update(plain)
+        if it >= 1:
+            assert planned.__dict__.get("_scatter_plan") is not None
+    torch.cuda.synchronize()
+    assert_bits_equal("params", planned.params, plain.params)
+    assert_bits_equal("exp_avg_sqs", planned.optimizer_state["exp_avg_sqs"], plain.optimizer_state["exp_avg_sqs"])
+    # a subset of the gradients: the others keep their old values in `state.grads`
+    some = dict(list(grads.items())[:2])
+    Adam.apply_gradient(planned, some)
+    torch.cuda.synchronize()
+    assert torch.equal(planned.grads, plain.grads)
+    assert planned.optimizer_state["state_steps"].tolist() == [6.0] * 5
