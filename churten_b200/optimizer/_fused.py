@@ -155,7 +155,7 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
             and not params.requires_grad and not torch._C._are_functorch_transforms_active() \
             and not torch.compiler.is_compiling() and cached[2].run_parts(grads):
         return True
-    if not params.is_cuda or not params.is_contiguous():
+    if not params.is_cuda or not _vector_rows(params):
         return False
     windows = state._windows
     if grads.keys() != windows.keys():
@@ -176,7 +176,7 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     entries.sort(key=lambda e: e[1])
     for name in spec.buffers:
         value = state.optimizer_state.get(name)
-        if value is not None and not value.is_contiguous():
+        if value is not None and not _vector_rows(value):
             return False
         if value is not None and value.dtype is not params.dtype and (
                 not spec.mixed_takes_parts or len(entries) > _lib.MAX_GRAD_PARTS):
@@ -195,6 +195,16 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
             step(spec, state, spec.flag_defaults, grads=parts, columns=columns, steps_bumped=i > 0)
     _remember_parts_plan(spec, state, grads, ranges)
     return True
+
+
+def _vector_rows(t: torch.Tensor) -> bool:
+    """What the gathering kernel asks of a parameter or state matrix: unit element stride and
+    rows that start on 16-byte boundaries.  The rows may lie further apart than they are long
+    (the interleaved shard of an ensemble, `State[r::G]`)."""
+    t = _as_2d(t)
+    per_access = 16 // t.element_size()
+    return (t.stride(1) == 1 or t.shape[1] <= 1) and t.shape[1] % per_access == 0 \
+        and t.stride(0) % per_access == 0 and t.data_ptr() % 16 == 0
 
 
 def _remember_parts_plan(spec: FusedSpec, state: State, grads, ranges) -> None:

@@ -108,6 +108,34 @@ def test_single_replica_and_views_of_larger_tensors(cuda):
     assert_bits_equal("params", in_place.params, scattered.params)
 
 
+@pytest.mark.parametrize("opt_name,hypers", [CASES[0], CASES[2], CASES[4]], ids=["Adam", "SGD", "Adagrad"])
+def test_every_other_replica_of_a_larger_ensemble(cuda, opt_name, hypers, step_form):
+    """A state whose rows are two rows apart (the interleaved shard of an ensemble, `state[r::2]`)
+    reads its gradients in place too: no scatter launch, `grads` untouched, the other replicas
+    untouched, same bits as the dense ensemble stepped with a mask."""
+    from churten_b200.kernels import _C
+
+    cls, (whole, sharded) = _pair(cuda, _wide, opt_name, hypers, n=6)
+    gen = torch.Generator(device=cuda).manual_seed(5)
+    mine = sharded[1::2]
+    assert not mine.flat_params.is_contiguous()
+    untouched = sharded.grads.clone()
+    for step in range(3):
+        grads = _grads_like(whole, gen)
+        whole.active_mask.copy_(torch.tensor([False, True, False, step != 1, False, True], device=cuda))
+        mine.active_mask.copy_(torch.tensor([True, step != 1, True], device=cuda))
+        cls.apply_gradient(whole, grads)
+        before = _C.launch_count()
+        cls.apply_gradient(mine, {k: v[1::2] for k, v in grads.items()}, materialize=False)
+        assert _C.launch_count() - before in _step_launches(step_form)
+    assert_bits_equal("params", sharded.params, whole.params)
+    for key, value in whole.optimizer_state.tensors().items():
+        if key != "state_steps":
+            assert_bits_equal(key, sharded.optimizer_state[key], value)
+    assert torch.equal(sharded.optimizer_state["state_steps"], whole.optimizer_state["state_steps"])
+    assert torch.equal(sharded.grads, untouched)
+
+
 def test_falls_back_to_the_scatter_when_it_must(cuda, step_form):
     from churten_b200.kernels import _C
 
