@@ -25,17 +25,20 @@ struct AdagradOp {
   static constexpr int kBufs = 3;
   static constexpr unsigned kWriteMask = 0x5u;
   // Measured best on B200: the fp64 divide makes this one latency-sensitive.  fp32: 128 x 2,
-  // 6.2 TB/s against 5.2 for 256 x 1.  fp16 / bf16 already carry 8 elements per access:
-  // 128 x 1, 3.8 TB/s (3.8e11 elements/s) against 3.3 for 128 x 2.
+  // 6.2 TB/s against 5.2 for 256 x 1.  fp16 / bf16 (the bounded fast form, fp32 arithmetic for
+  // all but a few elements): 128 x 2 as well, 6.9 TB/s on 256 x 4 Mi bf16 elements against 6.15
+  // for 128 x 1 -- two 16-byte accesses per buffer in flight per thread matter more here than
+  // resident warps.
   static constexpr int kThreads = 128;
-  static constexpr int kUnroll = sizeof(T) == 2 ? 1 : 2;
+  static constexpr int kUnroll = 2;
   // resident CTAs of kMaxThreads threads the register allocation must allow (launch bound)
   // fp32: hold the default tile to 64 registers (68 unbounded) so that 8 CTAs of 128 threads are
   // resident instead of 7: 6.8 against 6.4 TB/s on 256 x 4 Mi elements
-  // fp16 / bf16: 40 registers (58 unbounded) for 12 instead of 8 resident CTAs of 128 threads:
-  // 6.14 against 5.82 TB/s on 256 x 4 Mi bf16 elements (10 CTAs at 48 registers: 5.90)
-  static constexpr int kMaxThreads = sizeof(T) == 2 ? 128 : 512;
-  static constexpr int kMinCtas = sizeof(T) == 4 ? 2 : sizeof(T) == 2 ? 12 : 0;
+  // fp16 / bf16: no bound (64 registers, 8 CTAs of 128 threads).  Holding the 128 x 2 tile to
+  // 48 registers (10 CTAs) spills 32 bytes and gives 6.78 TB/s against 6.91; the 128 x 1 tile
+  // held to 40 registers (12 CTAs) was the best of its shape at 6.15.
+  static constexpr int kMaxThreads = sizeof(T) == 2 ? 128 : 512;   // 2-byte: 64 registers (72 if the bound were 512)
+  static constexpr int kMinCtas = sizeof(T) == 4 ? 2 : 0;
   using Row = AdagradRow;
   using Hyper = AdagradHyper<Math>;
 

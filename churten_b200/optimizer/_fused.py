@@ -176,7 +176,8 @@ def step_from_parts(spec: FusedSpec, state: State, grads) -> bool:
     entries.sort(key=lambda e: e[1])
     for name in spec.buffers:
         value = state.optimizer_state.get(name)
-        if value is not None and not _vector_rows(value):
+        if value is not None and not (_vector_rows(value) if value.dtype is params.dtype
+                                      else value.is_contiguous()):   # narrow state: dense only
             return False
         if value is not None and value.dtype is not params.dtype and (
                 not spec.mixed_takes_parts or len(entries) > _lib.MAX_GRAD_PARTS):
