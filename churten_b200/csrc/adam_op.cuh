@@ -24,18 +24,20 @@ struct AdamOp {
   static constexpr int kBufs = AMSGRAD ? 5 : 4;
   static constexpr unsigned kWriteMask = AMSGRAD ? 0x1du : 0x0du;  // grads are read-only
   // Measured best on B200.  fp32: 256 x 1, 6.9 TB/s (4 buffers), 6.7 TB/s with AMSGrad.
-  // The other storage types carry 8 (or 2) elements per access and do better with
-  // smaller CTAs: bf16 5.2 against 5.1 TB/s, fp64 6.7 against 6.3 TB/s.
+  // The other storage types carry 8 (or 2) elements per access and do better with smaller
+  // CTAs; without AMSGrad they also gain from a second 16-byte access per buffer in flight
+  // (512 x 2 Mi elements: fp64 7.80 against 8.19 ms, bf16 1.983 against 2.001 ms), with
+  // AMSGrad's five buffers they do not.
   static constexpr int kThreads = sizeof(T) == 4 ? 256 : 128;
-  static constexpr int kUnroll = 1;
+  static constexpr int kUnroll = (sizeof(T) != 4 && !AMSGRAD) ? 2 : 1;
   // resident CTAs of kMaxThreads threads the register allocation must allow (launch bound)
   // fp32 without AMSGrad: 40 registers (45 unbounded, one 4-byte spill) for 6 resident CTAs of
   // 256 threads instead of 5: 7.84 against 7.95 ms on 1024 x 2 Mi elements; 32 registers spill
   // too much (8.1-8.4 ms), and AMSGrad's 47-54 registers do not fit 40 without a slowdown
-  // fp16 / bf16 without AMSGrad: 40 registers for 12 resident CTAs of 128 threads (small spills):
-  // 6.71 against 6.65 TB/s; with AMSGrad the same bound loses 3 %, so it keeps 60 registers
+  // fp16 / bf16: no bound (70 registers for the 128 x 2 tile, 7 CTAs of 128 threads); holding
+  // it to 64 registers (8 CTAs) spills 24 bytes and gives the 1 % back
   static constexpr int kMaxThreads = (sizeof(T) == 2 && !AMSGRAD) ? 128 : 512;
-  static constexpr int kMinCtas = (sizeof(T) == 4 && !AMSGRAD) ? 3 : (sizeof(T) == 2 && !AMSGRAD) ? 12 : 0;
+  static constexpr int kMinCtas = (sizeof(T) == 4 && !AMSGRAD) ? 3 : 0;
   using Row = AdamRowT<Math>;
   using Hyper = AdamHyper<Math>;
 
