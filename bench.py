@@ -891,12 +891,13 @@ def run_ours(args, w, world, rank, local_rank):
             del state, block_states, pinned, gather, loss, update
             torch.cuda.empty_cache()
             line["workloads"] = {name: measure_small(name, args, device, peak) for name in ("c1", "c2", "c3", "c4")}
-            # the 2-byte storage types the operators also dispatch (bounded fast form of the update)
+            # the other storage types the operators dispatch (2-byte: bounded fast form of the update)
             line["storage_dtypes"] = {
                 "adam_bf16": measure_small("c5_shard", args, device, peak, dtype="bf16", rows=512),
                 "adam_f16": measure_small("c5_shard", args, device, peak, dtype="f16", rows=512),
                 "adagrad_bf16": measure_small("c4", args, device, peak, dtype="bf16"),
                 "sgd_bf16": measure_small("c3", args, device, peak, dtype="bf16"),
+                "adam_f64": measure_small("c5_shard", args, device, peak, dtype="f64", rows=256),
             }
             torch.cuda.empty_cache()
             line["reference_cuda"] = reference_cuda_in_child(args.workload, min(args.steps, 10))
@@ -914,9 +915,9 @@ def run_ours(args, w, world, rank, local_rank):
 # launch is this figure times its active elements.  A constant from a capture, not a counter of
 # the run that prints it (a run under a profiler is never a bench number).
 TRAFFIC_BYTES_PER_ELEMENT: dict[str, float] = {
-    "adam": 27.54,               # 3.3503 GB over 121,634,816 elements (64 rows x 2 Mi, 58 active)
-    "sgd": 19.30,                # momentum buffer: 1.4172 GB over 73,437,952 elements
-    "adagrad": 19.17,            # 1.2866 GB over 67,108,864 elements
+    "adam": 27.58,               # 3.3543 GB over 121,634,816 elements (64 rows x 2 Mi, 58 active)
+    "sgd": 19.26,                # momentum buffer: 1.4146 GB over 73,437,952 elements
+    "adagrad": 19.22,            # 1.2901 GB over 67,108,864 elements
     "adam_narrow_state": 19.56,  # bf16 moments: 2.3793 GB over 121,634,816 elements
 }
 
