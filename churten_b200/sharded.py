@@ -195,6 +195,9 @@ class MetricGather:
         distributed = dist.is_available() and dist.is_initialized() and self.spec.world_size > 1
         if self._side is not None:
             self._side.wait_stream(torch.cuda.current_stream(self.device))
+            if local_metric.is_cuda:
+                # read on the side stream: its memory must not be handed out again before that
+                local_metric.record_stream(self._side)
             ctx = torch.cuda.stream(self._side)
         else:
             ctx = _NullContext()
