@@ -629,6 +629,54 @@ def measure_small(name, args, device, peak, dtype="f32", rows=0):
     return out
 
 
+def measure_apply_gradient(args, device, peak, rows=256) -> dict:
+    """`Optimizer.apply_gradient` either side of the step, on config 3's CNN (ten parameter
+    tensors per replica): per-parameter gradient tensors scattered into the consolidated matrix
+    and then stepped (the reference's sequence, optimizer/grad_transform.py:28-31), against
+    `materialize=False`, where the step kernel reads them where they are.  Same gradients, two
+    states from the same seed; the results must be the same bits."""
+    import torch
+
+    from churten_b200.kernels import _C
+
+    w = dict(WORKLOADS["c3"], dtype="f32", rows=rows)
+    n, t = rows, w["row_len"]
+    out = {"description": f"SGD+momentum over {rows} replicas of the CNN ({len(w['shapes'])} parameter tensors each, T={t:,})",
+           "rows": n, "row_len": t}
+    stream = torch.cuda.current_stream(device)
+    finals = []
+    for key, in_place in (("scatter_then_step", False), ("in_place", True)):
+        state, opt = build_state(w, n, device, seed=7)
+        parts = {name: state.grads[:, off:off + numel].reshape(shape).contiguous()
+                 for name, shape, off, numel in state.param_meta}
+        state.grads.zero_()
+        call = (lambda: opt.apply_gradient(state, parts, materialize=False)) if in_place \
+            else (lambda: opt.apply_gradient(state, parts))
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize(device)
+        launches0 = _C.launch_count()
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        for e0, e1 in pairs:
+            e0.record(stream)
+            call()
+            e1.record(stream)
+        torch.cuda.synchronize(device)
+        ms = statistics.median(e0.elapsed_time(e1) for e0, e1 in pairs)
+        # bytes the call has to move: the step's 20 per element, plus 8 (read the parts, write
+        # the matrix) when the gradients are materialised first
+        bytes_moved = n * t * (20 + (0 if in_place else 8))
+        out[key] = {"op_ms_median": ms, "launches_per_call": (_C.launch_count() - launches0) / len(pairs),
+                    "gbs": bytes_moved / (ms * 1e-3) / 1e9, "frac": bytes_moved / (ms * 1e-3) / 1e9 / peak,
+                    "param_updates_per_s": n * t / (ms * 1e-3)}
+        finals.append((state.params.clone(), state.optimizer_state["momentum_buffers"].clone()))
+        del state, parts
+        torch.cuda.empty_cache()
+    out["same_bits"] = all(torch.equal(x, y) for x, y in zip(*finals))
+    out["in_place_saves"] = 1.0 - out["in_place"]["op_ms_median"] / out["scatter_then_step"]["op_ms_median"]
+    return out
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -899,6 +947,8 @@ def run_ours(args, w, world, rank, local_rank):
                 "sgd_bf16": measure_small("c3", args, device, peak, dtype="bf16"),
                 "adam_f64": measure_small("c5_shard", args, device, peak, dtype="f64", rows=256),
             }
+            # either side of the step: the gradient scatter, or reading the gradients in place
+            line["apply_gradient"] = measure_apply_gradient(args, device, peak)
             torch.cuda.empty_cache()
             line["reference_cuda"] = reference_cuda_in_child(args.workload, min(args.steps, 10))
         if world == 1 and not args.no_cpu_baseline:
