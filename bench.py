@@ -677,6 +677,94 @@ def measure_apply_gradient(args, device, peak, rows=256) -> dict:
     return out
 
 
+def measure_callbacks(device, n=8192) -> dict:
+    """The per-epoch / per-batch callbacks that own the mask and the rates the step consumes,
+    and the best-row snapshot: the one-launch forms against the same rules written as `(N,)`
+    tensor expressions (what keeping the reference's callbacks on the device amounts to), in
+    microseconds of host wall clock per tick over a synchronised series, with the results
+    compared bit for bit; and the masked row copy into the pinned mirror in GB/s."""
+    import types
+
+    import torch
+
+    from churten_b200 import lr_schedule
+    from churten_b200.checkpoint import Snapshot
+    from churten_b200.freeze import EarlyStopping
+    from churten_b200.kernels import _C
+
+    gen = torch.Generator(device=device).manual_seed(5)
+    ticks = 30
+    out = {"replicas": n}
+
+    def series(tick):
+        for i in range(3):
+            tick(i)
+        torch.cuda.synchronize(device)
+        launches = _C.launch_count()
+        t0 = time.perf_counter()
+        for i in range(3, 3 + ticks):
+            tick(i)
+        torch.cuda.synchronize(device)
+        return (time.perf_counter() - t0) / ticks * 1e6, (_C.launch_count() - launches) / ticks
+
+    # early stopping: scores that stall for a growing share of the replicas
+    scores = torch.rand(3 + ticks, n, device=device, generator=gen).cumsum(0).flip(0) \
+        + 4.0 * torch.rand(3 + ticks, n, device=device, generator=gen)
+    stoppers = {}
+    for label in ("one_launch", "tensor_expressions"):
+        state = types.SimpleNamespace(active_mask=torch.ones(n, dtype=torch.bool, device=device))
+        early = EarlyStopping(patience=3, threshold=1e-3, track_best=False)
+        if label == "tensor_expressions":
+            early._tick_on_device = lambda *a: None
+        us, launches = series(lambda i: early(state, scores[i]))
+        stoppers[label] = (state.active_mask, early.misses_, early.dynamic_threshold_.view(torch.int32))
+        out.setdefault("early_stopping", {})[label + "_us"] = round(us, 1)
+        if label == "one_launch":
+            out["early_stopping"]["launches_per_tick"] = launches
+    out["early_stopping"]["same_bits"] = all(torch.equal(x, y) for x, y in zip(*stoppers.values()))
+    out["early_stopping"]["frozen_at_end"] = int((~stoppers["one_launch"][0]).sum())
+
+    class TensorPath(lr_schedule.LRScheduler):
+        def _launch(self, *a):
+            return False
+
+    rates = {}
+    for label, cls in (("one_launch", lr_schedule.LRScheduler), ("tensor_expressions", TensorPath)):
+        state = types.SimpleNamespace(optimizer_state={"lr": torch.full((n,), 1e-3, device=device)},
+                                      active_mask=stoppers["one_launch"][0])
+        sched = cls("WarmRestartLR")
+        us, launches = series(lambda i: sched(state))
+        rates[label] = state.optimizer_state["lr"]
+        out.setdefault("lr_schedule_warm_restarts", {})[label + "_us"] = round(us, 1)
+        if label == "one_launch":
+            out["lr_schedule_warm_restarts"]["launches_per_tick"] = launches
+    out["lr_schedule_warm_restarts"]["same_bits"] = bool(torch.equal(*rates.values()))
+
+    # best-row snapshot: a quarter of 32 replicas of the headline's Adam state into the pinned mirror
+    w = dict(WORKLOADS["c5_shard"], dtype="f32", rows=32)
+    state, _ = build_state(w, 32, device, seed=11)
+    state.active_mask.fill_(True)
+    snap = Snapshot(state)
+    chosen = torch.arange(32, device=device) % 4 == 0
+    row_bytes = sum(leaf[0].numel() * leaf.element_size() for leaf in snap.mirror.values())
+    snap.update(state, chosen)
+    snap.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = _C.launch_count()
+    e0.record()
+    for _ in range(3):
+        snap.update(state, chosen)
+    e1.record()
+    torch.cuda.synchronize(device)
+    moved = 3 * int(chosen.sum()) * row_bytes
+    out["snapshot"] = {"rows": int(chosen.sum()), "of": 32, "bytes_per_row": row_bytes,
+                       "device_to_pinned_gbs": round(moved / (e0.elapsed_time(e1) * 1e-3) / 1e9, 2),
+                       "launches_per_commit": (_C.launch_count() - launches) / 3}
+    del snap, state
+    torch.cuda.empty_cache()
+    return out
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -949,6 +1037,8 @@ def run_ours(args, w, world, rank, local_rank):
             }
             # either side of the step: the gradient scatter, or reading the gradients in place
             line["apply_gradient"] = measure_apply_gradient(args, device, peak)
+            # the callbacks that own the mask and the rates, and the best-row snapshot
+            line["callbacks"] = measure_callbacks(device)
             torch.cuda.empty_cache()
             line["reference_cuda"] = reference_cuda_in_child(args.workload, min(args.steps, 10))
         if world == 1 and not args.no_cpu_baseline:
