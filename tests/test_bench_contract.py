@@ -32,3 +32,19 @@ def test_reference_arm_prints_the_contract_line_with_the_gpu_arms_config():
                               no_l2_flush=False, layout="contiguous", frozen_pattern="random")
     w = dict(bench.WORKLOADS["c1"], dtype="f32")
     assert line["config"] == bench.run_config(args, w, 1)
+
+
+@pytest.mark.gpu
+def test_sub_records_of_the_default_line_on_small_cases(cuda):
+    """The extra records of the default line, at sizes that take a second: the callbacks'
+    one-launch forms and the two forms of `apply_gradient` agree bit for bit inside the record."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    both = bench.measure_apply_gradient(None, cuda, 6444.1, rows=8)
+    assert both["same_bits"] is True
+    assert both["scatter_then_step"]["launches_per_call"] == 3 and both["in_place"]["launches_per_call"] == 2
+    ticks = bench.measure_callbacks(cuda, n=700)
+    assert ticks["early_stopping"]["same_bits"] and ticks["early_stopping"]["launches_per_tick"] == 1
+    assert ticks["lr_schedule_warm_restarts"]["same_bits"] and ticks["lr_schedule_warm_restarts"]["launches_per_tick"] == 1
+    assert ticks["snapshot"]["launches_per_commit"] == 1 and ticks["snapshot"]["device_to_pinned_gbs"] > 0
