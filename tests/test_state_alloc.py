@@ -196,3 +196,20 @@ def test_row_indexing_follows_tensor_rules():
     assert state.params.data_ptr() == storage
     assert not state.params[idx].any() and state.params[1].any()
     assert state.optimizer_state["lr"].tolist() == [-1.0, 1.0, -1.0, 3.0, 4.0]
+
+
+def test_rows_the_gathering_step_accepts():
+    """The layout test in front of the in-place gradient step: unit element stride, 16-byte
+    aligned rows, rows a whole number of 16-byte accesses long; the rows may lie apart."""
+    from churten_b200.optimizer._fused import _vector_rows
+
+    dense = torch.zeros(6, 64)
+    assert _vector_rows(dense)
+    assert _vector_rows(dense[1::2])                  # every other replica of a larger ensemble
+    assert _vector_rows(dense[:, 16:32])              # an aligned column window
+    assert not _vector_rows(dense[:, 1:33])           # rows start 4 bytes off a 16-byte boundary
+    assert not _vector_rows(dense[:, :30])            # 30 floats are not a whole number of accesses
+    assert not _vector_rows(dense.t())                # element stride is not 1
+    assert not _vector_rows(torch.zeros(6, 64, dtype=torch.bfloat16)[:, :36])   # 36 % 8 != 0
+    assert _vector_rows(torch.zeros(6, 64, dtype=torch.bfloat16)[:, 8:40])
+    assert _vector_rows(torch.zeros(64))              # one replica, seen as one row
