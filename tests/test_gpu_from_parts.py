@@ -176,7 +176,9 @@ def test_other_storage_types_gather_too(cuda, dtype, make, step_form):
     models = [make().to(cuda, dtype) for _ in range(3)]
     gen = torch.Generator(device=cuda).manual_seed(4)
     for cls, hypers in ((opts.SGD, dict(lr=0.125, momentum=0.5)),
-                        (opts.Adam, dict(lr=2.0 ** -7, beta1=0.875, beta2=0.96875, eps=2.0 ** -20))):
+                        (opts.Adam, dict(lr=2.0 ** -7, beta1=0.875, beta2=0.96875, eps=2.0 ** -20)),
+                        (opts.Adagrad, dict(lr=2.0 ** -5, lr_decay=2.0 ** -7, eps=2.0 ** -20,
+                                            initial_accumulator_value=0.125, weight_decay=2.0 ** -6))):
         a, b = State.from_models(models), State.from_models(models)
         for state in (a, b):
             cls.init(state, **hypers)
