@@ -18,7 +18,8 @@
 //    ONE short CTA per item by default.  Frozen rows generate no work items, so
 //    they move zero bytes and the active rows are spread evenly over all SMs
 //    whatever the mask looks like.  A tile is blockDim x UNROLL 16-byte accesses
-//    per buffer (256 x 1 for Adam and SGD, 128 x 2 for Adagrad); every load of a
+//    per buffer (fp32: 256 x 1 for Adam and SGD, 128 x 2 for Adagrad; the other storage
+//    types: 128 x 2, 128 x 1 with AMSGrad); every load of a
 //    tile is issued before the first dependent instruction.  Loads and stores
 //    carry the streaming (evict-first) hint when the working set exceeds L2.
 //    Measured on B200, a 4-read / 3-write stream reaches 6.9-7.0 TB/s this way
