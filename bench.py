@@ -591,6 +591,20 @@ def measure_small(name, args, device, peak, dtype="f32", rows=0):
         words = flush.view(torch.int64)
         after_read = timed(30, lambda i: state, before=lambda: words.sum())
         out["op_ms_median_after_l2_read_flush"] = statistics.median(after_read)
+        # what an event pair reads around ANY kernel on this GPU (a one-element fill, enqueued
+        # behind the same flush so that no host time falls between the two events): the part of
+        # the cold figures above that is not the step
+        one = torch.zeros(1, device=device)
+        floor = []
+        for _ in range(30):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            flush.zero_()
+            e0.record(stream)
+            one.zero_()
+            e1.record(stream)
+            floor.append((e0, e1))
+        torch.cuda.synchronize(device)
+        out["event_pair_floor_us"] = statistics.median(a.elapsed_time(b) for a, b in floor) * 1e3
         del flush, words
         # back-to-back eager steps with a warm L2: what a training loop pays per step, host included
         reps = 300
